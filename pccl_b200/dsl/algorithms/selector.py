@@ -1,0 +1,125 @@
+"""Choice of algorithm per (world size, message size, fabric, device).
+
+``select_algorithm`` is a table lookup.  For the H100 / NVLink 4 profile it
+reproduces the reference's rule (reference:
+pccl/dsl/algorithms/selector.py:23-54): ring unless the world is a power of two
+>= 4 and the message is under 1 MiB, then recursive halving-doubling.  For a
+switched fabric (NVLink 5 + NVSwitch) the crossovers come from the B200 sweep:
+one-shot for latency-bound sizes, two-shot in the middle, NVLS (or two-shot
+when the fabric cannot reduce in-switch) for bandwidth-bound sizes.
+
+``select_algorithm_cost_based`` builds every candidate's plan and prices its
+critical path with the cost model (reference: selector.py:57-114).
+"""
+
+from __future__ import annotations
+
+import json
+import os
+from typing import Dict, List, Optional
+
+from ..nodes import PrimitiveOpType
+from ..superopt.cost_model import (GpuProfile, H100_PROFILE, NVLINK_TOPOLOGY, TopologyProfile,
+                                   critical_path_cost)
+from ..superopt.rule import PatternEdge, PatternNode
+from .base import CollectiveAlgorithm, is_power_of_two
+from .direct import NvlsAllreduce, OneShotAllreduce, TwoShotAllreduce
+from .recursive_hd import RecursiveHalvingDoubling
+from .ring import RingAllreduce
+from .tree import TreeAllreduce
+
+_is_power_of_2 = is_power_of_two
+
+#: message-size crossovers (bytes) on a switched fabric, by world size: (one-shot up to, two-shot up to)
+SWITCHED_CROSSOVERS: Dict[int, tuple] = {
+    2: (512 * 1024, 16 * 1024 * 1024),
+    4: (256 * 1024, 8 * 1024 * 1024),
+    8: (128 * 1024, 4 * 1024 * 1024),
+}
+
+
+def load_tuned_crossovers(path: Optional[str] = None) -> Dict[int, tuple]:
+    """Crossovers measured by the sweep benchmark, if a tuning file exists
+    (``PCCL_TUNING_FILE`` or ``~/.pccl/tuning_b200.json``), else the built-in table."""
+    path = path or os.environ.get("PCCL_TUNING_FILE") or os.path.expanduser("~/.pccl/tuning_b200.json")
+    try:
+        with open(path) as handle:
+            raw = json.load(handle)
+        return {int(k): tuple(v) for k, v in raw.get("allreduce_crossovers", {}).items()} \
+            or SWITCHED_CROSSOVERS
+    except (OSError, ValueError):
+        return SWITCHED_CROSSOVERS
+
+
+def select_algorithm(world_size: int, data_bytes: int,
+                     topology: TopologyProfile = NVLINK_TOPOLOGY,
+                     device: GpuProfile = H100_PROFILE) -> CollectiveAlgorithm:
+    forced = os.environ.get("PCCL_ALGO")
+    if forced:
+        from . import ALGORITHMS
+        if forced in ALGORITHMS:
+            return ALGORITHMS[forced]()
+
+    if getattr(topology, "uniform_all_to_all", False):
+        table = load_tuned_crossovers()
+        nearest = min(table, key=lambda w: abs(w - world_size))
+        one_shot_max, two_shot_max = table[nearest]
+        if data_bytes <= one_shot_max:
+            return OneShotAllreduce()
+        if data_bytes <= two_shot_max or not topology.in_switch_reduction:
+            return TwoShotAllreduce()
+        return NvlsAllreduce()
+
+    if not is_power_of_two(world_size) or world_size <= 2:
+        return RingAllreduce()
+    if data_bytes >= 1024 * 1024:
+        return RingAllreduce()
+    return RecursiveHalvingDoubling()
+
+
+def _as_pattern(graph) -> tuple:
+    index = {nid: i for i, nid in enumerate(graph.nodes)}
+    nodes = [PatternNode(op_type=n.op_type or PrimitiveOpType.NOOP, rank=0, channel=n.channel)
+             for n in graph.nodes.values()]
+    edges = [PatternEdge(index[nid], index[nxt]) for nid, n in graph.nodes.items()
+             for nxt in n.next_ops if nxt in index]
+    return nodes, edges
+
+
+def select_algorithm_cost_based(rank: int, world_size: int, tensor_size: int, data_bytes: int,
+                                topology: TopologyProfile = NVLINK_TOPOLOGY,
+                                device: GpuProfile = H100_PROFILE, dtype: str = "bfloat16",
+                                executor: str = "tma") -> CollectiveAlgorithm:
+    candidates: List[CollectiveAlgorithm] = [RingAllreduce()]
+    if is_power_of_two(world_size) and world_size >= 2:
+        candidates += [RecursiveHalvingDoubling(), TreeAllreduce()]
+    if getattr(topology, "uniform_all_to_all", False) and tensor_size % world_size == 0:
+        candidates += [OneShotAllreduce(), TwoShotAllreduce()]
+        if topology.in_switch_reduction:
+            candidates.append(NvlsAllreduce())
+    if len(candidates) == 1:
+        return candidates[0]
+
+    best, best_cost = candidates[0], float("inf")
+    for algorithm in candidates:
+        try:
+            native = algorithm.name in ("oneshot", "twoshot", "nvls")
+            graph = algorithm.build_allreduce(rank=rank, world_size=world_size,
+                                              tensor_size=tensor_size, dtype=dtype,
+                                              executor="sm" if native else executor)
+            cost = critical_path_cost(*_as_pattern(graph), device,
+                                      _bytes_per_step(algorithm.name, data_bytes, world_size))
+        except Exception:
+            continue
+        if cost < best_cost:
+            best, best_cost = algorithm, cost
+    return best
+
+
+def _bytes_per_step(name: str, data_bytes: int, world_size: int) -> int:
+    """Bytes one data primitive of the plan moves.  The reference prices every
+    primitive at the full message; chunked algorithms are priced per chunk here
+    only for the switch-native additions, so H100 choices stay unchanged."""
+    if name == "twoshot" or name == "nvls":
+        return max(1, data_bytes // world_size)
+    return data_bytes
