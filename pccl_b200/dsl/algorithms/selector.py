@@ -20,7 +20,7 @@ from typing import Dict, List, Optional
 
 from ..nodes import PrimitiveOpType
 from ..superopt.cost_model import (GpuProfile, H100_PROFILE, NVLINK_TOPOLOGY, TopologyProfile,
-                                   critical_path_cost)
+                                   critical_path_cost, plan_cost)
 from ..superopt.rule import PatternEdge, PatternNode
 from .base import CollectiveAlgorithm, is_power_of_two
 from .direct import NvlsAllreduce, OneShotAllreduce, TwoShotAllreduce
@@ -100,6 +100,8 @@ def select_algorithm_cost_based(rank: int, world_size: int, tensor_size: int, da
     if len(candidates) == 1:
         return candidates[0]
 
+    switched = getattr(topology, "uniform_all_to_all", False)
+    elem_bytes = max(1, data_bytes // max(1, tensor_size))
     best, best_cost = candidates[0], float("inf")
     for algorithm in candidates:
         try:
@@ -107,19 +109,14 @@ def select_algorithm_cost_based(rank: int, world_size: int, tensor_size: int, da
             graph = algorithm.build_allreduce(rank=rank, world_size=world_size,
                                               tensor_size=tensor_size, dtype=dtype,
                                               executor="sm" if native else executor)
-            cost = critical_path_cost(*_as_pattern(graph), device,
-                                      _bytes_per_step(algorithm.name, data_bytes, world_size))
+            if switched:
+                # Whole-plan pricing, node by node, with fabric-aware signal costs.
+                cost = plan_cost(graph, device, topology, elem_bytes, world_size)
+            else:
+                # The reference's pricing: every primitive at the full message size.
+                cost = critical_path_cost(*_as_pattern(graph), device, data_bytes)
         except Exception:
             continue
         if cost < best_cost:
             best, best_cost = algorithm, cost
     return best
-
-
-def _bytes_per_step(name: str, data_bytes: int, world_size: int) -> int:
-    """Bytes one data primitive of the plan moves.  The reference prices every
-    primitive at the full message; chunked algorithms are priced per chunk here
-    only for the switch-native additions, so H100 choices stay unchanged."""
-    if name == "twoshot" or name == "nvls":
-        return max(1, data_bytes // world_size)
-    return data_bytes

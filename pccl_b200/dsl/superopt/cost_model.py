@@ -113,7 +113,7 @@ H100_PROFILE = GpuProfile(name="h100")
 # "tma" plans execute on the SM path here (TMA never touches peer memory), so
 # they are priced identically.  multimem moves N ranks' worth of data per byte
 # that crosses this GPU's links.
-_B200_BW = {"sm": 700.0, "tma": 700.0, "ce": 740.0, "rdma": 50.0, "multimem": 800.0, "host": 25.0}
+_B200_BW = {"sm": 700.0, "tma": 700.0, "ce": 740.0, "rdma": 50.0, "multimem": 1500.0, "host": 25.0}
 B200_PROFILE = GpuProfile(
     name="b200",
     launch_overhead_us=0.6,
@@ -255,3 +255,52 @@ def cost_delta(source_nodes: List[PatternNode], source_edges: List[PatternEdge],
     """Microseconds saved by the replacement (positive = faster)."""
     return (critical_path_cost(source_nodes, source_edges, profile, data_size_bytes)
             - critical_path_cost(replacement_nodes, replacement_edges, profile, data_size_bytes))
+
+
+def plan_cost(graph, profile: GpuProfile, topology: TopologyProfile, elem_bytes: int = 4,
+              world_size: int = 1) -> float:
+    """Critical-path time (µs) of a whole per-rank plan, priced node by node.
+
+    Differences from ``critical_path_cost``, which prices every node of a small
+    pattern at one common size: each data primitive is priced from its own
+    ``size`` / ``count``; ``sm.reduce_multi`` moves one slice per remote source;
+    a ``multimem`` primitive occupies the links with one slice per rank (the
+    switch gathers from, or delivers to, all ``world_size`` ranks), at the
+    profile's multimem rate, which already reflects that its reduce and
+    broadcast halves use opposite link directions;
+    transfers are capped by the fabric's per-GPU bandwidth; a ``wait_notify``
+    costs one fabric latency; and on a switched fabric a run of consecutive
+    notifies (or waits) on one chain costs a single step, because the engine
+    issues them from parallel lanes.
+    """
+    order = graph.topological_sort()
+    finish: Dict[str, float] = {}
+    run_head: Dict[str, str] = {}          # node id -> first node of its signal run
+    link = topology.bandwidth_gb_s if topology is not None else float("inf")
+    parallel_signals = bool(topology is not None and topology.uniform_all_to_all)
+
+    for node in order:
+        op = node.op_type
+        params = node.to_params()
+        start = max((finish[d] for d in node.dependencies if d in finish), default=0.0)
+        if op in _SYNC_OPS:
+            own = topology.latency_us if (op == PrimitiveOpType.WAIT_NOTIFY and topology) \
+                else profile.launch_overhead_us
+            if parallel_signals and len(node.dependencies) == 1:
+                prev = graph.nodes.get(node.dependencies[0])
+                if prev is not None and prev.op_type == op:
+                    own = 0.0                         # rides along with the run's first signal
+        else:
+            executor = infer_executor(op)
+            key = executor.value if executor else "host"
+            amount = params.get("size", params.get("count", 0)) * elem_bytes
+            if op == PrimitiveOpType.SM_REDUCE_MULTI:
+                amount *= max(1, len(params.get("source_ranks", ())) - 1)
+            rate = profile.bandwidth_gb_s.get(key, _DEFAULT_BW)
+            if key == "multimem":
+                amount *= max(1, world_size)
+            else:
+                rate = min(rate, link)
+            own = profile.launch_overhead_us + _us(amount, rate)
+        finish[node.op_id] = start + own
+    return max(finish.values(), default=0.0)

@@ -1,0 +1,168 @@
+"""IR nodes, graph container, builder front-end, pipeline, codegen."""
+
+import json
+
+import pytest
+
+from pccl_b200 import (CommunicationOp, Compiler, DeviceType, ExecutorType, Pipeline,
+                       PrimitiveIRGraph, PrimitiveOpType, Stream, TensorInfo, build_graph,
+                       compile_to_json_string)
+from pccl_b200.dsl import nodes as N
+from pccl_b200.dsl.codegen import RuntimeGraphGenerator, load_plan_graph
+
+
+def test_node_identity_and_executor_inference():
+    n = N.SmReduceNode(source_rank=1, count=8)
+    assert n.op_type is PrimitiveOpType.SM_REDUCE and n.executor is ExecutorType.SM
+    assert n.op_id.startswith("sm_reduce_") and len(n.op_id) == len("sm_reduce_") + 8
+    assert N.TmaCopyNode(source_rank=0).executor is ExecutorType.TMA
+    assert N.MultimemStoreNode(source_rank=0).executor is ExecutorType.MULTIMEM
+    assert N.NotifyNode(target_rank=0).executor is ExecutorType.SM
+    assert N.NotifyNode(target_rank=0, device=DeviceType.CPU).executor is ExecutorType.HOST
+    assert N.OcsBarrierNode(participant_ranks=(0, 1)).device is DeviceType.CPU
+    assert DeviceType.GPU is DeviceType.CUDA
+
+
+def test_param_dictionaries_are_the_json_contract():
+    assert list(N.SmReduceNode(source_rank=1).to_params()) == [
+        "reduce_op", "source_rank", "src_offset", "dst_offset", "remote_offset", "count"]
+    assert list(N.CeCopyNode(source_rank=1).to_params()) == [
+        "source_rank", "src_offset", "dst_offset", "size"]
+    assert list(N.RdmaWriteNode(target_rank=1).to_params()) == [
+        "target_rank", "src_offset", "dst_offset", "size"]
+    assert N.NotifyNode(signal_id=7, target_rank=2).to_params() == {"signal_id": 7, "target_rank": 2}
+    assert N.SmReduceMultiNode(source_ranks=[0, 1], count=4).to_params()["source_ranks"] == [0, 1]
+
+
+@pytest.mark.parametrize("make, message", [
+    (lambda: N.SmReduceNode(source_rank=0, reduce_op="xor"), "invalid reduce_op"),
+    (lambda: N.SmCopyNode(), "source_rank must be non-negative"),
+    (lambda: N.SmPutNode(), "target_rank must be non-negative"),
+    (lambda: N.TmaCopyNode(source_rank=0, size=-1), "size must be non-negative"),
+    (lambda: N.OcsBarrierNode(participant_ranks=()), "participant_ranks"),
+    (lambda: N.OcsBarrierNode(participant_ranks=(0,), epoch_id=3, next_epoch_id=3), "next_epoch_id"),
+])
+def test_validation_messages(make, message):
+    with pytest.raises(ValueError, match=message):
+        make().validate()
+
+
+def test_tensor_info_rules():
+    assert TensorInfo("bfloat16", (4, 8)).numel() == 32
+    assert TensorInfo(dtype="float32", shape=(3,), device="cuda").nbytes() == 12
+    with pytest.raises(ValueError, match="shape must be a tuple"):
+        TensorInfo("float32", [4])
+    with pytest.raises(ValueError, match="unsupported dtype"):
+        TensorInfo("int8", (4,))
+
+
+def test_graph_edges_cycles_and_order():
+    g = PrimitiveIRGraph(graph_name="g")
+    a, b, c = (g.add_node(N.NotifyNode(op_id=i, target_rank=0)) for i in "abc")
+    g.add_edge("a", "b"); g.add_edge("b", "c"); g.add_edge("a", "b")
+    assert b.dependencies == ["a"] and a.next_ops == ["b"]
+    with pytest.raises(ValueError, match="cycle"):
+        g.add_edge("c", "a")
+    assert c.next_ops == [] and "c" not in a.dependencies      # rolled back
+    with pytest.raises(ValueError, match="already exists"):
+        g.add_node(N.NotifyNode(op_id="a", target_rank=0))
+    assert [n.op_id for n in g.topological_sort()] == ["a", "b", "c"]
+    g.remove_node("b")
+    assert a.next_ops == [] and c.dependencies == []
+    with pytest.raises(ValueError, match="empty"):
+        PrimitiveIRGraph().validate()
+
+
+def test_deep_chain_does_not_recurse():
+    g = PrimitiveIRGraph()
+    prev = None
+    for i in range(5000):
+        g.add_node(N.NotifyNode(op_id=f"n{i}", target_rank=0))
+        if prev:
+            g.nodes[f"n{i}"].add_dependency(prev); g.nodes[prev].add_next_op(f"n{i}")
+        prev = f"n{i}"
+    assert g.validate() and len(g.topological_sort()) == 5000
+
+
+def test_streams_are_independent_chains_and_wait_joins_them():
+    with CommunicationOp("op") as op:
+        op.tensor("float32", (64,))
+        with Stream("a"):
+            a1 = op.sm_copy(1, 0, 0, 8)
+            a2 = op.notify(0, 1)
+        with Stream("b"):
+            b1 = op.sm_copy(1, 8, 8, 8)
+            op.wait("a")
+            b2 = op.notify(1, 1)
+        with Stream("a"):
+            a3 = op.wait_notify(0, 1)
+    assert a2.dependencies == [a1.op_id] and b1.dependencies == []
+    assert set(b2.dependencies) == {b1.op_id, a2.op_id}
+    assert a3.dependencies == [a2.op_id]
+    assert op.get_graph().entry_points == [a1.op_id, b1.op_id]
+    with pytest.raises(RuntimeError):
+        Stream("x").__enter__()
+
+
+def test_pipeline_rotates_channels():
+    with CommunicationOp("p") as op:
+        op.tensor("bfloat16", (64,))
+        with Pipeline(depth=2).bind(op) as pipe:
+            made = []
+            for i in range(4):
+                with pipe.stage():
+                    made.append(op.tma_copy(1, i * 8, i * 8, 8))
+    assert [n.channel for n in made] == [0, 1, 0, 1]
+    assert made[2].dependencies == [made[0].op_id] and made[1].dependencies == []
+    with pytest.raises(ValueError):
+        Pipeline(depth=0)
+
+
+def _two_phase_graph():
+    def build(op):
+        op.tensor("float32", (16,))
+        op.sm_copy(1, 0, 0, 8)
+        op.ocs_barrier(barrier_id=3, epoch_id=0, next_epoch_id=1, participant_ranks=(0, 1),
+                       topology_id=5, route_plan_id=9, payload=b"\x01\x02")
+        with Stream("late"):
+            op.sm_copy(1, 8, 8, 8)
+    return build_graph("two_phase", build)
+
+
+def test_v2_document_shape_and_round_trip():
+    def build(op):
+        op.tensor("float32", (16,))
+        op.notify(100, 1); op.wait_notify(100, 1)
+        op.sm_reduce(1, 0, 0, 0, 16)
+    g = build_graph("g", build)
+    g.collective_type = "allreduce"
+    doc = json.loads(compile_to_json_string(g))
+    assert list(doc) == ["version", "tensor_info", "collective_type", "executors", "operations"]
+    assert doc["operations"][0] == {"index": 0, "executor": "cuda_sm", "primitive": "notify",
+                                    "channel": 0, "dependencies": [], "next_ops": [1],
+                                    "params": {"signal_id": 100, "target_rank": 1}}
+    again = RuntimeGraphGenerator().generate(load_plan_graph(doc))
+    assert again == doc
+    assert json.loads(compile_to_json_string(build_graph("g", build), Compiler(enable_superopt=True)))[
+        "operations"][2]["primitive"] == "tma.reduce"
+
+
+def test_v3_manifest_for_barrier_graphs():
+    doc = RuntimeGraphGenerator().generate(_two_phase_graph())
+    assert doc["version"] == 3 and doc["execution_model"] == "phased_ocs"
+    assert "operations" not in doc
+    assert [len(p["operations"]) for p in doc["phases"]] == [1, 1]
+    ctl = doc["control_operations"][0]
+    assert ctl["primitive"] == "ocs.barrier" and ctl["executor"] == "host"
+    assert (ctl["after_phase"], ctl["before_phase"]) == (0, 1)
+    assert ctl["params"]["payload_hex"] == "0102" and ctl["params"]["participant_bitmap"] == 3
+    with pytest.raises(ValueError, match="Superoptimization across OCS barriers"):
+        Compiler(enable_superopt=True).compile(_two_phase_graph())
+
+
+def test_barrier_must_cut_the_whole_graph():
+    g = _two_phase_graph()
+    stray = g.add_node(N.SmCopyNode(op_id="stray", source_rank=1, size=1))
+    with pytest.raises(ValueError, match="must depend on every node"):
+        g.validate()
+    del stray

@@ -1,0 +1,144 @@
+"""Every algorithm template, replayed on the CPU executor against float64 sums;
+reference-emitted golden plans; deadlock and bounds diagnostics."""
+
+import copy
+import gzip
+import json
+import os
+
+import pytest
+import torch
+
+from helpers import build_plans, expected, make_inputs
+from pccl_b200.dsl.algorithms import (ALGORITHMS, NvlsAllreduce, OneShotAllreduce,
+                                      RecursiveHalvingDoubling, RingAllreduce, TreeAllreduce,
+                                      TwoShotAllreduce)
+from pccl_b200.runtime import PlanDeadlock, simulate
+
+KINDS = ("allreduce", "reduce_scatter", "allgather", "alltoall")
+
+
+def _supported():
+    for name, cls in ALGORITHMS.items():
+        for kind in KINDS:
+            try:
+                getattr(cls(), "build_" + kind)(0, 2, 64, "float32", "sm")
+            except NotImplementedError:
+                continue
+            yield name, kind
+
+
+@pytest.mark.parametrize("name,kind", list(_supported()))
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_template_matches_float64_reference(name, kind, world):
+    n = 48 * world
+    plans = build_plans(ALGORITHMS[name](), kind, world, n)
+    xs = make_inputs(kind, world, n)
+    outs, sim = simulate(plans, xs, return_world=True)
+    for out, ref in zip(outs, expected(kind, xs, world, n)):
+        torch.testing.assert_close(out.double(), ref, atol=1e-5, rtol=1e-5)
+    assert sim.leftover_signals() == {}, "plans must be re-runnable without a signal reset"
+
+
+@pytest.mark.parametrize("channels", [1, 2, 4, 8, 16, 32])
+def test_multichannel_ring_and_twoshot(channels):
+    world, n = 4, 4 * 32 * 8
+    for algorithm in (RingAllreduce(), TwoShotAllreduce(), OneShotAllreduce(), NvlsAllreduce()):
+        plans = build_plans(algorithm, "allreduce", world, n, channels=channels)
+        assert max(op["channel"] for op in plans[0]["operations"]) == channels - 1
+        xs = make_inputs("allreduce", world, n)
+        for out in simulate(plans, xs):
+            torch.testing.assert_close(out.double(), sum(x.double() for x in xs), atol=1e-5, rtol=1e-5)
+
+
+def test_bf16_accumulates_in_fp32():
+    world, n = 8, 64 * 8
+    plans = build_plans(TwoShotAllreduce(), "allreduce", world, n, dtype="bfloat16")
+    xs = make_inputs("allreduce", world, n, torch.bfloat16)
+    ref = sum(x.double() for x in xs)
+    for out in simulate(plans, xs):
+        assert out.dtype == torch.bfloat16
+        torch.testing.assert_close(out.double(), ref, atol=0.05, rtol=2 ** -7)
+
+
+@pytest.mark.parametrize("op,fold", [("max", torch.maximum), ("min", torch.minimum)])
+def test_max_min_reduce_ops(op, fold):
+    world, n = 4, 64
+    plans = build_plans(RingAllreduce(), "allreduce", world, n)
+    for plan in plans:
+        for o in plan["operations"]:
+            if "reduce_op" in o["params"]:
+                o["params"]["reduce_op"] = op
+    xs = make_inputs("allreduce", world, n)
+    ref = xs[0]
+    for x in xs[1:]:
+        ref = fold(ref, x)
+    for out in simulate(plans, xs):
+        torch.testing.assert_close(out, ref)
+
+
+def test_avg_is_sum_scaled_once():
+    world, n = 4, 64
+    plans = build_plans(TwoShotAllreduce(), "allreduce", world, n)
+    for plan in plans:
+        for o in plan["operations"]:
+            if "reduce_op" in o["params"]:
+                o["params"]["reduce_op"] = "avg"
+    xs = make_inputs("allreduce", world, n)
+    for out in simulate(plans, xs):
+        torch.testing.assert_close(out.double(), sum(x.double() for x in xs) / world,
+                                   atol=1e-6, rtol=1e-6)
+
+
+def _golden():
+    path = os.path.join(os.path.dirname(__file__), "golden", "reference_plans.json.gz")
+    with gzip.open(path, "rt") as handle:
+        return json.load(handle)
+
+
+@pytest.mark.parametrize("tag", sorted(_golden()))
+def test_reference_emitted_plans_replay_unchanged(tag):
+    plans = _golden()[tag]
+    kind, world = plans[0]["collective_type"], len(plans)
+    n = plans[0]["tensor_info"]["shape"][0]
+    dtype = {"float32": torch.float32, "bfloat16": torch.bfloat16}[plans[0]["tensor_info"]["dtype"]]
+    xs = make_inputs(kind, world, n, dtype)
+    tol = dict(atol=1e-5, rtol=1e-5) if dtype is torch.float32 else dict(atol=0.1, rtol=2 ** -6)
+    for out, ref in zip(simulate(plans, xs), expected(kind, xs, world, n)):
+        torch.testing.assert_close(out.double(), ref, **tol)
+
+
+def test_our_templates_emit_the_reference_primitive_sequences():
+    """Plan compatibility in the other direction: same ops, same params."""
+    golden = _golden()
+    cases = {
+        "ring_ar_w8_sm": (RingAllreduce(), "allreduce", 8, 8192, "bfloat16", "sm", 1),
+        "ring_ar_w2_c2": (RingAllreduce(), "allreduce", 2, 4096, "float32", "tma", 2),
+        "rhd_ar_w8": (RecursiveHalvingDoubling(), "allreduce", 8, 8192, "float32", "tma", 1),
+        "tree_ar_w8": (TreeAllreduce(), "allreduce", 8, 1024, "float32", "sm", 1),
+        "ring_rs_w4": (RingAllreduce(), "reduce_scatter", 4, 4096, "float32", "sm", 1),
+        "ring_ag_w4": (RingAllreduce(), "allgather", 4, 4096, "float32", "sm", 1),
+        "ring_a2a_w4": (RingAllreduce(), "alltoall", 4, 4096, "float32", "sm", 1),
+    }
+    for tag, (alg, kind, world, n, dtype, ex, ch) in cases.items():
+        ours = build_plans(alg, kind, world, n, dtype, ex, ch)
+        for mine, theirs in zip(ours, golden[tag]):
+            mine = copy.deepcopy(mine)
+            mine.pop("algorithm")                     # additive field of this library
+            assert mine == theirs, tag
+
+
+def test_missing_notify_is_reported_as_deadlock():
+    plans = build_plans(RingAllreduce(), "allreduce", 2, 64)
+    victim = next(i for i, o in enumerate(plans[1]["operations"]) if o["primitive"] == "notify")
+    plans[1]["operations"][victim]["primitive"] = "noop"
+    with pytest.raises(PlanDeadlock, match="wait_notify"):
+        simulate(plans, make_inputs("allreduce", 2, 64))
+
+
+def test_out_of_range_access_is_reported():
+    plans = build_plans(RingAllreduce(), "allreduce", 2, 64)
+    data = next(o for o in plans[0]["operations"] if "count" in o["params"])
+    data["params"]["remote_offset"] = 10 ** 6
+    with pytest.raises(IndexError, match="outside rank"):
+        simulate(plans, make_inputs("allreduce", 2, 64))
