@@ -1,0 +1,97 @@
+"""Run-time options in one place.
+
+Every option is an environment variable read by the native engine or the Python
+layers; ``PcclConfig.from_env()`` mirrors them in a dataclass and ``describe()``
+prints the table.  Names shared with the reference keep their meaning
+(reference: include/common/config.h:8-35, csrc/plugins/cuda/cuda_device.cc:290-298,
+csrc/plugins/cuda/nvls_manager.h:29-31, csrc/engine_c.cc:87-104).
+"""
+
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass, fields
+from typing import Dict, Optional
+
+_SIZES = {"k": 1 << 10, "m": 1 << 20, "g": 1 << 30}
+
+
+def _size(text: str) -> int:
+    text = text.strip()
+    if text and text[-1].lower() in _SIZES:
+        return int(text[:-1]) * _SIZES[text[-1].lower()]
+    return int(text)
+
+
+def _flag(text: str) -> bool:
+    return text.strip().lower() not in ("0", "false", "off", "no", "")
+
+
+OPTIONS: Dict[str, tuple] = {
+    # name: (field, parser, default, description)
+    "RANK": ("rank", int, None, "rank of this process (required by the native engine)"),
+    "WORLD_SIZE": ("world_size", int, 1, "number of ranks"),
+    "PCCL_BUFFER_SIZE": ("buffer_size", _size, 1 << 30, "bytes of the plan working buffer"),
+    "PCCL_ARENA_SIZE": ("arena_size", _size, 1 << 30, "bytes of symmetric memory for fused operators"),
+    "PCCL_NUM_BLOCKS": ("num_blocks", int, 96, "upper bound of CTAs per collective launch"),
+    "PCCL_FORCE_BLOCKS": ("force_blocks", int, 0, "exact CTA count per launch (0 = heuristic)"),
+    "PCCL_MIN_BYTES_PER_BLOCK": ("min_bytes_per_block", _size, 64 << 10, "smallest share worth another CTA"),
+    "PCCL_WAIT_TIMEOUT_MS": ("wait_timeout_ms", int, 10000, "time budget of device-side waits per launch"),
+    "PCCL_NVLS_ENABLE": ("nvls_enable", _flag, True, "use NVLS multicast when every rank supports it"),
+    "PCCL_DISABLE_NVLS": ("disable_nvls", _flag, False, "turn NVLS off"),
+    "PCCL_ALGO": ("algo", str, None, "force ring|rhd|tree|oneshot|twoshot|nvls"),
+    "PCCL_CHANNELS": ("channels", int, None, "force the channel count of generated plans"),
+    "PCCL_EXECUTOR": ("executor", str, None, "sm (default) | ce (copy engine) | cpu (gloo replay)"),
+    "PCCL_TUNING_FILE": ("tuning_file", str, None, "JSON with measured algorithm crossovers"),
+    "PCCL_LOG_LEVEL": ("log_level", str, "WARN", "TRACE|DEBUG|INFO|WARN|ERROR|CRITICAL"),
+    "PCCL_JOB_ID": ("job_id", str, None, "namespace of the fd-passing sockets"),
+    "PCCL_DEBUG_ENDPOINT_INIT": ("debug_endpoint_init", _flag, False, "print bootstrap stages"),
+}
+
+
+@dataclass
+class PcclConfig:
+    rank: Optional[int] = None
+    world_size: int = 1
+    buffer_size: int = 1 << 30
+    arena_size: int = 1 << 30
+    num_blocks: int = 96
+    force_blocks: int = 0
+    min_bytes_per_block: int = 64 << 10
+    wait_timeout_ms: int = 10000
+    nvls_enable: bool = True
+    disable_nvls: bool = False
+    algo: Optional[str] = None
+    channels: Optional[int] = None
+    executor: Optional[str] = None
+    tuning_file: Optional[str] = None
+    log_level: str = "WARN"
+    job_id: Optional[str] = None
+    debug_endpoint_init: bool = False
+
+    @classmethod
+    def from_env(cls, env=None) -> "PcclConfig":
+        env = os.environ if env is None else env
+        values = {}
+        for name, (field, parse, default, _) in OPTIONS.items():
+            raw = env.get(name)
+            values[field] = default if raw in (None, "") else parse(raw)
+        return cls(**values)
+
+    def to_env(self) -> Dict[str, str]:
+        """Environment assignments that reproduce this configuration."""
+        out = {}
+        for name, (field, _, default, _) in OPTIONS.items():
+            value = getattr(self, field)
+            if value is not None and value != default:
+                out[name] = str(int(value)) if isinstance(value, bool) else str(value)
+        return out
+
+
+def describe() -> str:
+    width = max(len(n) for n in OPTIONS)
+    return "\n".join(f"{name.ljust(width)}  default={default!s:<12} {text}"
+                     for name, (_, _, default, text) in OPTIONS.items())
+
+
+assert {f.name for f in fields(PcclConfig)} == {v[0] for v in OPTIONS.values()}

@@ -1,0 +1,83 @@
+// Plan loading, validation and lowering.
+//
+// load_plan      JSON text (version-2 device plan) -> Plan (host representation).
+//                Accepts every executor string and primitive name the reference
+//                emits, including bare "notify" / "wait_notify" / "noop"
+//                (reference: csrc/engine/graph_builder.cc:12-107 and the channel
+//                parsers csrc/plugins/cuda/channels/*.h for the field mapping).
+// validate_plan  bounds of every range, peer and signal id; notify/wait balance.
+// lower_plan     Plan -> LoweredProgram: chains of steps in plan order (program.h).
+#pragma once
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include "../common/json.h"
+#include "../executors/sm100/program.h"
+
+namespace pccl {
+
+enum class Primitive {
+  kNoop, kNotify, kWait, kCopy, kReduce, kPut, kReduceMulti, kMmReduce, kMmStore, kMmAllreduce, kCeCopy,
+};
+
+struct PlanOp {
+  int index = 0;
+  Primitive primitive = Primitive::kNoop;
+  std::string primitive_name, executor;
+  int channel = 0;
+  std::vector<int> deps, next;
+  // data parameters, in elements
+  int peer = -1;                  // source_rank / target_rank
+  std::vector<int> sources;       // reduce_multi
+  int64_t off_src = 0, off_dst = 0, off_remote = 0, count = 0;
+  uint8_t red_op = kRedSum;
+  bool avg = false;
+  uint32_t signal_id = 0;
+};
+
+struct Plan {
+  int version = 2;
+  uint8_t dtype = kF32;
+  std::string dtype_name;
+  int64_t numel = 0;
+  std::string collective_type, algorithm;
+  std::vector<PlanOp> ops;
+  bool uses_avg = false;
+  bool has_ce_ops = false;
+  int num_channels = 1;
+};
+
+Plan load_plan(const std::string& json_text);
+
+struct PlanLimits {
+  int rank = 0, world = 1;
+  int64_t buffer_elems = 0;       // elements of the plan dtype that fit the data region
+};
+// Throws pccl::Error describing the first violation.
+void validate_plan(const Plan& plan, const PlanLimits& limits);
+
+struct LowerOptions {
+  int rank = 0, world = 1;
+  bool multicast = false;         // NVLS mapping available
+  uint32_t total_ctas = 16;       // CTA budget for the whole program
+  uint32_t max_ctas_per_chain = 64;
+  uint64_t min_bytes_per_cta = 64 << 10;   // do not spread less than this over another CTA
+  bool force_copy_engine = false; // route pull copies to the copy-engine executor
+};
+
+struct LoweredProgram {
+  std::vector<Step> steps;
+  std::vector<SigRef> sigs;
+  std::vector<ChainDep> deps;
+  std::vector<Chain> chains;
+  uint32_t total_ctas = 0;
+  bool uses_multicast = false;
+  uint64_t max_step_bytes = 0;
+};
+
+LoweredProgram lower_plan(const Plan& plan, const LowerOptions& opt);
+
+const char* primitive_label(Primitive p);
+
+}  // namespace pccl

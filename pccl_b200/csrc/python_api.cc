@@ -1,0 +1,171 @@
+// Python bindings: module pccl_b200.engine_c (also importable as pccl.engine_c).
+// Method names on Engine follow the reference's binding (reference:
+// csrc/python_api.cc:11-33) so the Python wrapper's calls are unchanged; everything
+// else (status, reset, NVLS stages, symmetric tensors, LocalCluster, fused
+// operators) is an addition.
+#include <c10/cuda/CUDAStream.h>
+#include <pybind11/stl.h>
+#include <torch/extension.h>
+
+#include "common/util.h"
+#include "engine/engine.h"
+#include "fused/fused_ops.h"
+
+namespace py = pybind11;
+using namespace pccl;
+
+namespace {
+
+cudaStream_t current_stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
+
+void check_tensor(const torch::Tensor& t, const char* what) {
+  TORCH_CHECK(t.is_cuda(), what, " must be a CUDA tensor");
+  TORCH_CHECK(t.is_contiguous(), what, " must be contiguous");
+}
+
+void exe(const std::string& name, const torch::Tensor& in, torch::Tensor& out, bool sync) {
+  check_tensor(in, "input");
+  check_tensor(out, "output");
+  Engine::instance().exeOp(name, in.data_ptr(), in.nbytes(), out.data_ptr(), out.nbytes(), current_stream(), sync);
+}
+
+// A tensor that aliases symmetric memory; the engine owns the storage.
+torch::Tensor heap_tensor(uint8_t* base, const std::vector<int64_t>& shape, torch::ScalarType dtype, int device) {
+  auto options = torch::TensorOptions().dtype(dtype).device(torch::kCUDA, device);
+  return torch::from_blob(base, shape, [](void*) {}, options);
+}
+
+int64_t numel_of(const std::vector<int64_t>& shape) {
+  int64_t n = 1;
+  for (int64_t e : shape) n *= e;
+  return n;
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "pccl_b200 native engine";
+  m.attr("version") = "0.3.0";
+  py::register_exception<Error>(m, "PCCLError", PyExc_RuntimeError);
+  py::register_exception<TimeoutError>(m, "PCCLTimeoutError", m.attr("PCCLError").ptr());
+
+  py::class_<Engine, std::unique_ptr<Engine, py::nodelete>>(m, "Engine")
+      .def_static("get_instance", &Engine::instance, py::return_value_policy::reference)
+      .def("regOp", &Engine::regOp)
+      .def("regOpFromString", &Engine::regOpFromString)
+      .def("exeOp", [](Engine&, const std::string& n, const torch::Tensor& i, torch::Tensor& o) { exe(n, i, o, true); })
+      .def("exeOpAsync", [](Engine&, const std::string& n, const torch::Tensor& i, torch::Tensor& o) { exe(n, i, o, false); })
+      .def("syncOp", [](Engine& e, const std::string& n) { e.syncOp(n, current_stream()); })
+      .def("resetSignals", &Engine::resetSignals)
+      .def("reset", &Engine::reset)
+      .def("exportEndpoint", &Engine::exportEndpoint)
+      .def("updateEndpoint", &Engine::updateEndpoint)
+      .def("nvlsStage", &Engine::nvlsStage)
+      .def("nvlsDisable", &Engine::nvlsDisable)
+      .def("nvlsActive", &Engine::nvlsActive)
+      .def("rank", &Engine::rank)
+      .def("world", &Engine::world)
+      .def("stats", &Engine::statsJson)
+      .def("setTimeoutMs", [](Engine& e, uint64_t ms) { e.context().set_timeout_ms(ms); })
+      .def("bufferBytes", [](Engine& e) { return e.context().buffer_bytes(); })
+      // View of the plan working buffer: collectives on it run without staging copies.
+      .def("workingBuffer",
+           [](Engine& e, const std::vector<int64_t>& shape, torch::ScalarType dtype, int64_t offset_bytes) {
+             RankContext& c = e.context();
+             const int64_t bytes = numel_of(shape) * static_cast<int64_t>(c10::elementSize(dtype));
+             TORCH_CHECK(offset_bytes >= 0 && offset_bytes + bytes <= static_cast<int64_t>(c.buffer_bytes()),
+                         "working-buffer view exceeds PCCL_BUFFER_SIZE");
+             return heap_tensor(c.heap().data(c.rank()) + offset_bytes, shape, dtype, c.heap().device());
+           },
+           py::arg("shape"), py::arg("dtype"), py::arg("offset_bytes") = 0)
+      // Symmetric allocation from the arena (same offset on every rank when all allocate alike).
+      .def("allocSymmetric",
+           [](Engine& e, const std::vector<int64_t>& shape, torch::ScalarType dtype) {
+             RankContext& c = e.context();
+             const size_t bytes = static_cast<size_t>(numel_of(shape)) * c10::elementSize(dtype);
+             const size_t off = c.arena_alloc(bytes);
+             return py::make_tuple(heap_tensor(c.heap().data(c.rank()) + off, shape, dtype, c.heap().device()),
+                                   static_cast<int64_t>(off));
+           })
+      .def("arenaReset", [](Engine& e) { e.context().arena_reset(); })
+      .def("peerTensor",
+           [](Engine& e, int rank, int64_t heap_offset, const std::vector<int64_t>& shape, torch::ScalarType dtype) {
+             RankContext& c = e.context();
+             return heap_tensor(c.heap().data(rank) + heap_offset, shape, dtype, c.heap().device());
+           });
+
+  py::class_<LocalCluster>(m, "LocalCluster")
+      .def(py::init<int, int, size_t>(), py::arg("world"), py::arg("device") = 0,
+           py::arg("buffer_bytes") = size_t(64) << 20)
+      .def("world", &LocalCluster::world)
+      .def("regOp", &LocalCluster::regOp)
+      .def("setTimeoutMs", &LocalCluster::set_timeout_ms)
+      .def("setCtas", &LocalCluster::set_ctas)
+      .def("reset", &LocalCluster::reset)
+      .def("opInfo",
+           [](LocalCluster& c, const std::string& name, int rank) {
+             const RegisteredOp& op = c.context(rank).op(name);
+             py::dict d;
+             d["chains"] = op.lowered.chains.size();
+             d["steps"] = op.lowered.steps.size();
+             d["ctas"] = op.lowered.total_ctas;
+             d["multicast"] = op.lowered.uses_multicast;
+             return d;
+           })
+      .def("lastStatus",
+           [](LocalCluster& c) {
+             py::list out;
+             for (const DeviceStatus& s : c.last_status()) {
+               py::dict d;
+               d["code"] = s.code; d["rank"] = s.rank; d["chain"] = s.chain; d["step"] = s.step;
+               d["slot"] = s.slot; d["observed"] = s.observed; d["expected"] = s.expected;
+               out.append(d);
+             }
+             return out;
+           })
+      .def("exeOp", [](LocalCluster& c, const std::string& name, const std::vector<torch::Tensor>& in,
+                       std::vector<torch::Tensor>& out) {
+        std::vector<const void*> ip; std::vector<size_t> ib; std::vector<void*> op; std::vector<size_t> ob;
+        for (const auto& t : in) { check_tensor(t, "input"); ip.push_back(t.data_ptr()); ib.push_back(t.nbytes()); }
+        for (auto& t : out) { check_tensor(t, "output"); op.push_back(t.data_ptr()); ob.push_back(t.nbytes()); }
+        c.exeOp(name, ip, ib, op, ob, current_stream());
+      });
+
+  // Host-only helpers usable without a GPU (plan loader / validator / lowering).
+  m.def("lower_plan_summary", [](const std::string& json_text, int rank, int world, int64_t buffer_bytes,
+                                 uint32_t ctas, bool multicast) {
+    Plan plan = load_plan(json_text);
+    PlanLimits lim{rank, world, buffer_bytes / dtype_bytes(plan.dtype)};
+    validate_plan(plan, lim);
+    LowerOptions lo;
+    lo.rank = rank; lo.world = world; lo.total_ctas = ctas; lo.multicast = multicast;
+    LoweredProgram lp = lower_plan(plan, lo);
+    py::dict d;
+    d["chains"] = lp.chains.size();
+    d["steps"] = lp.steps.size();
+    d["ctas"] = lp.total_ctas;
+    d["multicast"] = lp.uses_multicast;
+    py::list chains;
+    for (const Chain& c : lp.chains) {
+      py::list steps;
+      for (uint32_t k = 0; k < c.step_count; ++k) {
+        const Step& s = lp.steps[c.step_begin + k];
+        steps.append(py::make_tuple(static_cast<int>(s.kind), static_cast<int>(s.n_wait), static_cast<int>(s.n_notify),
+                                    static_cast<int>(s.n_dep), s.peer, s.bytes));
+      }
+      py::dict cd;
+      cd["ctas"] = c.num_ctas; cd["barriers"] = c.barriers_per_launch; cd["steps"] = steps;
+      chains.append(cd);
+    }
+    d["chain_list"] = chains;
+    return d;
+  });
+
+  auto common = m.def_submodule("common");
+  py::class_<Environs>(common, "Environs")
+      .def_static("listOpt", &Environs::list_options)
+      .def_static("getEnv", [](const std::string& n) { return Environs::require(n); })
+      .def_static("registerOpt", &Environs::register_option);
+
+  bind_fused_ops(m);
+}

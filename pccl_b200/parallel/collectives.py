@@ -1,0 +1,158 @@
+"""Collectives on top of the engine: pick an algorithm, compile the plan once,
+register it, run it.
+
+    import pccl_b200.parallel as pp
+    pp.init(group)                               # connects the engine
+    x = pp.working_tensor(n, torch.float32)      # lives in the symmetric heap
+    pp.all_reduce(x)                             # in place, no staging copies
+
+Plans are cached per (collective, algorithm, world, dtype, numel, channels).  The
+algorithm comes from ``select_algorithm`` with the B200 profile unless given (or
+forced with ``PCCL_ALGO``); ``PCCL_CHANNELS`` overrides the channel count.
+
+The reference has no such layer: its benchmarks build a template, compile it to
+a file and call register/execute by hand (tests/bench_algo_comparison.py:60-121).
+"""
+
+from __future__ import annotations
+
+import os
+import tempfile
+from typing import Dict, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .. import engine as _engine
+from ..dsl.algorithms import ALGORITHMS, select_algorithm
+from ..dsl.compiler import Compiler
+from ..dsl.superopt.cost_model import B200_PROFILE, NVLINK5_TOPOLOGY, TopologyProfile
+
+_DTYPE_NAME = {torch.float32: "float32", torch.float16: "float16", torch.bfloat16: "bfloat16"}
+for _name, _plan_name in (("float8_e4m3fn", "float8_e4m3"), ("float8_e5m2", "float8_e5m2")):
+    if hasattr(torch, _name):
+        _DTYPE_NAME[getattr(torch, _name)] = _plan_name
+
+_state: Dict[str, object] = {"group": None, "rank": 0, "world": 1, "registered": {}, "dir": None}
+
+
+def init(group: Optional[dist.ProcessGroup] = None):
+    """Connect the engine over ``group`` (default group when None)."""
+    _state["group"] = group
+    if dist.is_initialized():
+        _state["rank"], _state["world"] = dist.get_rank(group), dist.get_world_size(group)
+    os.environ.setdefault("RANK", str(_state["rank"]))
+    os.environ.setdefault("WORLD_SIZE", str(_state["world"]))
+    if dist.is_initialized():
+        _engine.initialize_engine(group)
+    else:
+        _engine.get_engine()
+    return _engine.get_engine()
+
+
+def working_tensor(shape, dtype=torch.float32) -> torch.Tensor:
+    """Tensor that aliases the engine's working buffer (offset 0)."""
+    return _engine.working_buffer(shape, dtype)
+
+
+def _topology() -> TopologyProfile:
+    nvls = getattr(_engine.get_engine(), "nvls_active", lambda: False)()
+    return NVLINK5_TOPOLOGY if nvls else TopologyProfile("nvlink5", 900.0, 0.7, uniform_all_to_all=True)
+
+
+def default_channels(nbytes: int, world: int) -> int:
+    forced = os.environ.get("PCCL_CHANNELS")
+    if forced:
+        return max(1, int(forced))
+    # One channel per ~8 MiB so that the reduce half of channel c+1 overlaps the gather half of c.
+    return max(1, min(16, nbytes // (8 << 20)))
+
+
+def _plan_name(kind: str, algorithm: str, dtype: str, numel: int, channels: int) -> str:
+    return f"{kind}_{algorithm}_{dtype}_{numel}_c{channels}_w{_state['world']}"
+
+
+def ensure_plan(kind: str, numel: int, dtype: torch.dtype, algorithm: Optional[str] = None,
+                channels: Optional[int] = None, reduce_op: str = "sum") -> str:
+    """Compile + register (once) the plan for this collective; returns its name."""
+    world, rank = _state["world"], _state["rank"]
+    dtype_name = _DTYPE_NAME[dtype]
+    nbytes = numel * torch.empty((), dtype=dtype).element_size()
+    if algorithm is None:
+        algorithm = os.environ.get("PCCL_ALGO")
+    if algorithm is None:
+        if kind == "allreduce":
+            algorithm = select_algorithm(world, nbytes, _topology(), B200_PROFILE).name
+        else:
+            algorithm = "nvls" if (_topology().in_switch_reduction and kind != "alltoall"
+                                   and nbytes >= (4 << 20) and world > 2) else "twoshot"
+    if channels is None:
+        channels = default_channels(nbytes, world)
+    # Every channel's slice must split evenly over the ranks, in 16-byte units where possible.
+    while channels > 1 and numel % (channels * world):
+        channels //= 2
+    name = _plan_name(kind, algorithm, dtype_name, numel, channels) + ("" if reduce_op == "sum" else "_" + reduce_op)
+    if name in _state["registered"]:
+        return name
+    template = ALGORITHMS[algorithm]()
+    executor = "multimem" if algorithm == "nvls" else "sm"
+    graph = getattr(template, "build_" + kind)(rank, world, numel, dtype_name, executor, channels)
+    if reduce_op != "sum":
+        for node in graph.nodes.values():
+            if hasattr(node, "reduce_op"):
+                node.reduce_op = reduce_op
+    text = Compiler().compile_to_json(graph)
+    engine = _engine.get_engine()
+    if hasattr(engine, "register_operation_from_string"):
+        ok = engine.register_operation_from_string(name, text)
+    else:
+        if _state["dir"] is None:
+            _state["dir"] = tempfile.mkdtemp(prefix="pccl-plans-")
+        path = os.path.join(_state["dir"], name + ".json")
+        with open(path, "w") as handle:
+            handle.write(text)
+        ok = engine.register_operation(name, path)
+    if not ok:
+        raise _engine.PCCLError(f"could not register plan '{name}'")
+    if dist.is_initialized() and world > 1:
+        dist.barrier(group=_state["group"])      # nobody signals a rank that has not registered yet
+    _state["registered"][name] = (kind, algorithm, channels)
+    return name
+
+
+def all_reduce(tensor: torch.Tensor, op: str = "sum", algorithm: Optional[str] = None,
+               channels: Optional[int] = None, async_op: bool = False) -> torch.Tensor:
+    """In-place all-reduce of ``tensor`` (sum / max / min / avg)."""
+    name = ensure_plan("allreduce", tensor.numel(), tensor.dtype, algorithm, channels, op)
+    run = _engine.execute_operation_async if async_op else _engine.execute_operation
+    run(name, tensor, tensor)
+    return tensor
+
+
+def reduce_scatter(output: torch.Tensor, input: torch.Tensor, op: str = "sum",
+                   algorithm: Optional[str] = None, channels: Optional[int] = None) -> torch.Tensor:
+    name = ensure_plan("reduce_scatter", input.numel(), input.dtype, algorithm, channels, op)
+    _engine.execute_operation(name, input, output)
+    return output
+
+
+def all_gather(output: torch.Tensor, input: torch.Tensor, algorithm: Optional[str] = None,
+               channels: Optional[int] = None) -> torch.Tensor:
+    name = ensure_plan("allgather", output.numel(), output.dtype, algorithm, channels)
+    _engine.execute_operation(name, input, output)
+    return output
+
+
+def all_to_all(output: torch.Tensor, input: torch.Tensor, algorithm: Optional[str] = None,
+               channels: Optional[int] = None) -> torch.Tensor:
+    name = ensure_plan("alltoall", input.numel(), input.dtype, algorithm or "twoshot", channels)
+    _engine.execute_operation(name, input, output)
+    return output
+
+
+def synchronize(name: str = "") -> None:
+    _engine.sync_operation(name)
+
+
+def registered_plans() -> Dict[str, Tuple[str, str, int]]:
+    return dict(_state["registered"])

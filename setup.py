@@ -1,0 +1,38 @@
+"""In-tree build of the native engine:  python setup.py build_ext --inplace
+
+Produces pccl_b200/engine_c*.so next to the Python sources.  Device code is
+compiled for sm_100a only (-gencode arch=compute_100a,code=sm_100a).
+"""
+
+import glob
+import os
+
+from setuptools import setup
+from torch.utils.cpp_extension import BuildExtension, CUDAExtension
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join("pccl_b200", "csrc")
+
+sources = sorted(glob.glob(os.path.join(CSRC, "**", "*.cc"), recursive=True)
+                 + glob.glob(os.path.join(CSRC, "**", "*.cu"), recursive=True))
+
+os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")
+
+setup(
+    name="pccl_b200",
+    version="0.3.0",
+    packages=["pccl_b200", "pccl"],
+    ext_modules=[
+        CUDAExtension(
+            name="pccl_b200.engine_c",
+            sources=sources,
+            include_dirs=[os.path.join(ROOT, CSRC)],
+            extra_compile_args={
+                "cxx": ["-std=c++17", "-O2", "-fvisibility=hidden", "-Wall", "-Wno-unknown-pragmas"],
+                "nvcc": ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr",
+                         "-gencode", "arch=compute_100a,code=sm_100a"],
+            },
+        )
+    ],
+    cmdclass={"build_ext": BuildExtension.with_options(use_ninja=True)},
+)
