@@ -4,6 +4,9 @@
 // else (status, reset, NVLS stages, symmetric tensors, LocalCluster, fused
 // operators) is an addition.
 #include <c10/cuda/CUDAStream.h>
+#include <execinfo.h>
+#include <signal.h>
+#include <unistd.h>
 #include <pybind11/stl.h>
 #include <torch/extension.h>
 
@@ -35,6 +38,15 @@ torch::Tensor heap_tensor(uint8_t* base, const std::vector<int64_t>& shape, torc
   return torch::from_blob(base, shape, [](void*) {}, options);
 }
 
+// PCCL_BACKTRACE=1: print the native stack on SIGSEGV before the default action.
+void segv_backtrace(int sig) {
+  void* frames[64];
+  const int n = backtrace(frames, 64);
+  backtrace_symbols_fd(frames, n, STDERR_FILENO);
+  signal(sig, SIG_DFL);
+  raise(sig);
+}
+
 int64_t numel_of(const std::vector<int64_t>& shape) {
   int64_t n = 1;
   for (int64_t e : shape) n *= e;
@@ -46,6 +58,7 @@ int64_t numel_of(const std::vector<int64_t>& shape) {
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "pccl_b200 native engine";
   m.attr("version") = "0.3.0";
+  if (Environs::get_flag("PCCL_BACKTRACE")) signal(SIGSEGV, segv_backtrace);
   py::register_exception<Error>(m, "PCCLError", PyExc_RuntimeError);
   py::register_exception<TimeoutError>(m, "PCCLTimeoutError", m.attr("PCCLError").ptr());
 
@@ -160,6 +173,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     d["chain_list"] = chains;
     return d;
   });
+
+  // Raises the engine's timeout error from host code (exercises the exception mapping without a GPU).
+  m.def("_raise_timeout", [](const std::string& text) { throw TimeoutError(text); });
 
   auto common = m.def_submodule("common");
   py::class_<Environs>(common, "Environs")

@@ -27,6 +27,10 @@ setup(
             name="pccl_b200.engine_c",
             sources=sources,
             include_dirs=[os.path.join(ROOT, CSRC)],
+            # Link the shared libstdc++ explicitly: on images whose compiler directory holds only
+            # libstdc++.a the driver would otherwise embed a second, uninitialised copy of the
+            # iostream/locale state into the extension.
+            extra_link_args=[p for p in ("/usr/lib/x86_64-linux-gnu/libstdc++.so.6",) if os.path.exists(p)],
             extra_compile_args={
                 "cxx": ["-std=c++17", "-O2", "-fvisibility=hidden", "-Wall", "-Wno-unknown-pragmas"],
                 "nvcc": ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr",
