@@ -1,0 +1,99 @@
+"""Worker of the multi-GPU tests (one process per GPU, launched by torchrun).
+
+Runs every collective through the public API on the engine's multi-process path
+(VMM heap + fd passing + NVLS when available) and checks it against NCCL on the
+same inputs.  Prints ``MULTI_GPU_PASS {json}`` on rank 0 when everything matched.
+"""
+
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    os.environ.setdefault("PCCL_BUFFER_SIZE", str(256 << 20))
+    os.environ.setdefault("PCCL_ARENA_SIZE", str(256 << 20))
+    os.environ.setdefault("PCCL_WAIT_TIMEOUT_MS", "5000")
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    import pccl_b200.parallel as pp
+    engine = pp.init()
+    report = {"world": world, "nvls": bool(engine.nvls_active()), "checked": 0}
+
+    def tol(dtype):
+        return dict(atol=1e-4, rtol=1e-5) if dtype == torch.float32 else dict(atol=0.1, rtol=2 ** -6)
+
+    algos = ["ring", "twoshot", "oneshot", "nvls"] + (["rhd", "tree"] if world & (world - 1) == 0 else [])
+    for dtype in (torch.float32, torch.bfloat16):
+        for numel in (world * 1024, world * 100003, 4 << 20):
+            gen = torch.Generator(device="cuda").manual_seed(1000 + rank)
+            x = torch.randn(numel, device="cuda", generator=gen).to(dtype)
+            ref = x.float().clone()
+            dist.all_reduce(ref)
+            for algo in algos:
+                if algo == "oneshot" and numel > (1 << 20):
+                    continue
+                for channels in (1, 4):
+                    if numel % (channels * world):
+                        continue
+                    y = x.clone()
+                    pp.all_reduce(y, algorithm=algo, channels=channels)
+                    torch.testing.assert_close(y.float(), ref, msg=lambda m: f"allreduce {algo} c{channels} "
+                                               f"{dtype} n={numel} rank {rank}: {m}", **tol(dtype))
+                    report["checked"] += 1
+            # zero-copy: the tensor is the working buffer itself
+            w = pp.working_tensor(numel, dtype)
+            w.copy_(x)
+            pp.all_reduce(w)
+            torch.testing.assert_close(w.float(), ref, **tol(dtype))
+
+            shard = numel // world
+            # reduce-scatter
+            out = torch.empty(shard, device="cuda", dtype=dtype)
+            for algo in ("ring", "twoshot", "nvls"):
+                pp.reduce_scatter(out, x, algorithm=algo)
+                torch.testing.assert_close(out.float(), ref[rank * shard:(rank + 1) * shard], **tol(dtype))
+                report["checked"] += 1
+            # all-gather
+            full = torch.empty(numel, device="cuda", dtype=dtype)
+            expect = torch.empty(numel, device="cuda", dtype=dtype)
+            dist.all_gather_into_tensor(expect, x[:shard].contiguous())
+            for algo in ("ring", "twoshot", "nvls"):
+                full.zero_()
+                pp.all_gather(full, x[:shard].contiguous(), algorithm=algo)
+                assert torch.equal(full, expect), f"allgather {algo} {dtype} n={numel}"
+                report["checked"] += 1
+            # all-to-all
+            got = torch.empty(numel, device="cuda", dtype=dtype)
+            want = torch.empty(numel, device="cuda", dtype=dtype)
+            dist.all_to_all_single(want, x)
+            for algo in ("ring", "twoshot"):
+                pp.all_to_all(got, x, algorithm=algo)
+                assert torch.equal(got, want), f"alltoall {algo} {dtype} n={numel}"
+                report["checked"] += 1
+
+    # max / avg through the API
+    x = torch.randn(world * 4096, device="cuda", generator=torch.Generator(device="cuda").manual_seed(rank))
+    ref = x.clone(); dist.all_reduce(ref, op=dist.ReduceOp.MAX)
+    y = x.clone(); pp.all_reduce(y, op="max", algorithm="twoshot")
+    torch.testing.assert_close(y, ref)
+    ref = x.clone(); dist.all_reduce(ref); ref /= world
+    y = x.clone(); pp.all_reduce(y, op="avg", algorithm="twoshot")
+    torch.testing.assert_close(y, ref, atol=1e-5, rtol=1e-5)
+
+    torch.cuda.synchronize()
+    dist.barrier()
+    if rank == 0:
+        print("MULTI_GPU_PASS " + json.dumps(report), flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
