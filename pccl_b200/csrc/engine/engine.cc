@@ -115,6 +115,11 @@ void RankContext::upload(RegisteredOp& op) {
   const int64_t forced = Environs::get_int("PCCL_FORCE_BLOCKS", 0);
   lo.total_ctas = forced > 0 ? std::min<uint32_t>(static_cast<uint32_t>(forced), cap) : auto_ctas(op.plan, cap);
   lo.min_bytes_per_cta = static_cast<uint64_t>(Environs::get_int("PCCL_MIN_BYTES_PER_BLOCK", 64 << 10));
+  // Templates of this library end with their own barrier; everything else gets one appended.
+  const std::string& algo = op.plan.algorithm;
+  const bool self_fenced = algo == "oneshot" || algo == "twoshot" || algo == "direct" || algo == "nvls";
+  lo.closing_barrier = !self_fenced && !op.plan.collective_type.empty() &&
+                       Environs::get_flag("PCCL_CLOSING_BARRIER", true);
   op.lowered = lower_plan(op.plan, lo);
   const LoweredProgram& lp = op.lowered;
 

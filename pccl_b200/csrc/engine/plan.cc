@@ -191,9 +191,9 @@ void validate_plan(const Plan& plan, const PlanLimits& lim) {
       case Primitive::kNotify:
       case Primitive::kWait:
         check_rank(op, op.peer, op.primitive == Primitive::kNotify ? "target_rank" : "source_rank");
-        if (op.signal_id >= kSignalSlots)
+        if (op.signal_id >= kSignalSlots - kMaxRanks)
           fail(op, "signal_id " + std::to_string(op.signal_id) + " exceeds the " +
-                       std::to_string(kSignalSlots) + " signal slots");
+                       std::to_string(kSignalSlots - kMaxRanks) + " usable signal slots");
         break;
       case Primitive::kCopy: case Primitive::kCeCopy: case Primitive::kPut: case Primitive::kMmStore:
         check_rank(op, op.peer, "peer rank");
@@ -405,6 +405,22 @@ LoweredProgram lower_plan(const Plan& plan, const LowerOptions& opt) {
         state = kHasData;
       }
       step_of_op[oi] = static_cast<int>(chain_steps[c].size()) - 1;
+    }
+  }
+
+  // 2b. Closing barrier on reserved signal slots (top of the signal space, one per sender).
+  if (opt.closing_barrier && opt.world > 1 && !chains.empty()) {
+    PendingStep& post = new_step(0);
+    for (size_t c = 1; c < chains.size(); ++c)
+      if (!chains[c].ops.empty()) post.dep_ops.push_back(chains[c].ops.back());
+    for (int i = 1; i < opt.world; ++i) {
+      const int peer = (opt.rank + i) % opt.world;
+      post.notifies.push_back(SigRef{peer, kSignalSlots - kMaxRanks + static_cast<uint32_t>(opt.rank)});
+    }
+    PendingStep& wait = new_step(0);
+    for (int i = 1; i < opt.world; ++i) {
+      const int peer = (opt.rank + i) % opt.world;
+      wait.waits.push_back(SigRef{peer, kSignalSlots - kMaxRanks + static_cast<uint32_t>(peer)});
     }
   }
 

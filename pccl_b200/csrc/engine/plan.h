@@ -64,6 +64,10 @@ struct LowerOptions {
   uint32_t max_ctas_per_chain = 64;
   uint64_t min_bytes_per_cta = 64 << 10;   // do not spread less than this over another CTA
   bool force_copy_engine = false; // route pull copies to the copy-engine executor
+  // Append an all-pairs barrier after the last step.  Pull-style templates (ring, tree,
+  // halving-doubling) let a rank finish while a neighbour still reads its buffer; the
+  // barrier keeps the next operation's input copy from overwriting data in use.
+  bool closing_barrier = false;
 };
 
 struct LoweredProgram {

@@ -96,4 +96,9 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except Exception as err:  # one greppable line per failing rank, then the usual traceback
+        print(f"MULTI_GPU_FAIL rank {os.environ.get('RANK')}: {type(err).__name__}: "
+              + " | ".join(str(err).splitlines()[:12]), flush=True)
+        raise
