@@ -42,15 +42,25 @@ def _rotated(rank: int, world_size: int, include_self: bool) -> List[int]:
     return [(rank + i) % world_size for i in range(start, world_size)]
 
 
+def _shard_piece(tensor_size: int, world_size: int, c: int, nc: int):
+    """(elements per piece, offset of piece c inside a shard).  For collectives whose
+    result or input is a *contiguous shard per rank* (reduce-scatter, allgather,
+    all-to-all) channels cut every rank's shard into ``nc`` pieces, so that the
+    union over channels is still the contiguous shard the engine reads or writes."""
+    shard = tensor_size // world_size
+    piece = shard // nc
+    return shard, piece, c * piece
+
+
 def _per_channel(name: str, kind: str, algorithm: str, rank: int, world_size: int,
                  tensor_size: int, dtype: str, num_channels: int,
-                 body: Callable[[CommunicationOp, int, int, int], None]) -> PrimitiveIRGraph:
+                 body: Callable[..., None]) -> PrimitiveIRGraph:
     with CommunicationOp(name=f"{name}_c{num_channels}_rank{rank}", device=DeviceType.CUDA) as op:
         op.tensor(dtype=dtype, shape=(tensor_size,))
         for c, base, span, sig in channel_slices(tensor_size, num_channels):
             with Stream(f"ch{c}"):
                 op.set_channel(c)
-                body(op, base, span, sig)
+                body(op, base, span, sig, c, num_channels)
         return finish(op, kind, algorithm)
 
 
@@ -63,7 +73,7 @@ class OneShotAllreduce(CollectiveAlgorithm):
 
     def build_allreduce(self, rank, world_size, tensor_size, dtype="bfloat16", executor="sm",
                         num_channels=1) -> PrimitiveIRGraph:
-        def body(op, base, span, sig):
+        def body(op, base, span, sig, c=0, nc=1):
             all_pairs_barrier(op, rank, world_size, sig + _BARRIER_A)
             # Result goes to scratch behind the tensor: peers are still reading [0, n).
             op.sm_reduce_multi(source_ranks=_rotated(rank, world_size, True),
@@ -87,7 +97,7 @@ class TwoShotAllreduce(CollectiveAlgorithm):
 
     def build_allreduce(self, rank, world_size, tensor_size, dtype="bfloat16", executor="sm",
                         num_channels=1) -> PrimitiveIRGraph:
-        def body(op, base, span, sig):
+        def body(op, base, span, sig, c=0, nc=1):
             piece = span // world_size
             mine = base + rank * piece
             all_pairs_barrier(op, rank, world_size, sig + _BARRIER_A)
@@ -103,9 +113,9 @@ class TwoShotAllreduce(CollectiveAlgorithm):
 
     def build_reduce_scatter(self, rank, world_size, tensor_size, dtype="bfloat16",
                              executor="sm", num_channels=1) -> PrimitiveIRGraph:
-        def body(op, base, span, sig):
-            piece = span // world_size
-            mine = base + rank * piece
+        def body(op, base, span, sig, c=0, nc=1):
+            shard, piece, within = _shard_piece(tensor_size, world_size, c, nc)
+            mine = rank * shard + within
             all_pairs_barrier(op, rank, world_size, sig + _BARRIER_A)
             op.sm_reduce_multi(source_ranks=_rotated(rank, world_size, True),
                                remote_offset=mine, dst_offset=mine, count=piece)
@@ -117,11 +127,11 @@ class TwoShotAllreduce(CollectiveAlgorithm):
                         num_channels=1) -> PrimitiveIRGraph:
         copy = "ce_copy" if executor == "ce" else "sm_copy"
 
-        def body(op, base, span, sig):
-            piece = span // world_size
+        def body(op, base, span, sig, c=0, nc=1):
+            shard, piece, within = _shard_piece(tensor_size, world_size, c, nc)
             all_pairs_barrier(op, rank, world_size, sig + _BARRIER_A)
             for peer in _rotated(rank, world_size, False):
-                off = base + peer * piece
+                off = peer * shard + within
                 getattr(op, copy)(source_rank=peer, src_offset=off, dst_offset=off, size=piece)
             all_pairs_barrier(op, rank, world_size, sig + _BARRIER_B)
         return _per_channel("direct_ag", "allgather", "direct", rank, world_size, tensor_size,
@@ -131,12 +141,12 @@ class TwoShotAllreduce(CollectiveAlgorithm):
                        num_channels=1) -> PrimitiveIRGraph:
         copy = "ce_copy" if executor == "ce" else "sm_copy"
 
-        def body(op, base, span, sig):
-            piece = span // world_size
+        def body(op, base, span, sig, c=0, nc=1):
+            shard, piece, within = _shard_piece(tensor_size, world_size, c, nc)
             all_pairs_barrier(op, rank, world_size, sig + _BARRIER_A)
             for peer in _rotated(rank, world_size, False):
-                getattr(op, copy)(source_rank=peer, src_offset=base + rank * piece,
-                                  dst_offset=base + tensor_size + peer * piece, size=piece)
+                getattr(op, copy)(source_rank=peer, src_offset=rank * shard + within,
+                                  dst_offset=tensor_size + peer * shard + within, size=piece)
             # Trailing barrier: the next collective must not overwrite [0, n)
             # while a slower peer is still pulling from it.
             all_pairs_barrier(op, rank, world_size, sig + _BARRIER_B)
@@ -162,7 +172,7 @@ class NvlsAllreduce(CollectiveAlgorithm):
 
     def build_allreduce(self, rank, world_size, tensor_size, dtype="bfloat16",
                         executor="multimem", num_channels=1) -> PrimitiveIRGraph:
-        def body(op, base, span, sig):
+        def body(op, base, span, sig, c=0, nc=1):
             piece = span // world_size
             mine = base + rank * piece
             all_pairs_barrier(op, rank, world_size, sig + _BARRIER_A)
@@ -176,9 +186,9 @@ class NvlsAllreduce(CollectiveAlgorithm):
 
     def build_reduce_scatter(self, rank, world_size, tensor_size, dtype="bfloat16",
                              executor="multimem", num_channels=1) -> PrimitiveIRGraph:
-        def body(op, base, span, sig):
-            piece = span // world_size
-            mine = base + rank * piece
+        def body(op, base, span, sig, c=0, nc=1):
+            shard, piece, within = _shard_piece(tensor_size, world_size, c, nc)
+            mine = rank * shard + within
             all_pairs_barrier(op, rank, world_size, sig + _BARRIER_A)
             op.multimem_reduce(source_rank=rank, src_offset=mine, dst_offset=mine,
                                remote_offset=mine, count=piece)
@@ -188,9 +198,9 @@ class NvlsAllreduce(CollectiveAlgorithm):
 
     def build_allgather(self, rank, world_size, tensor_size, dtype="bfloat16",
                         executor="multimem", num_channels=1) -> PrimitiveIRGraph:
-        def body(op, base, span, sig):
-            piece = span // world_size
-            mine = base + rank * piece
+        def body(op, base, span, sig, c=0, nc=1):
+            shard, piece, within = _shard_piece(tensor_size, world_size, c, nc)
+            mine = rank * shard + within
             all_pairs_barrier(op, rank, world_size, sig + _BARRIER_A)
             op.multimem_store(source_rank=rank, src_offset=mine, dst_offset=mine, size=piece)
             all_pairs_barrier(op, rank, world_size, sig + _BARRIER_B)

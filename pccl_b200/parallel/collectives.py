@@ -88,6 +88,10 @@ def ensure_plan(kind: str, numel: int, dtype: torch.dtype, algorithm: Optional[s
                                    and nbytes >= (4 << 20) and world > 2) else "twoshot"
     if channels is None:
         channels = default_channels(nbytes, world)
+    if algorithm in ("ring", "rhd", "tree") and kind != "allreduce":
+        # The reference-compatible ring templates interleave channels inside the tensor, which
+        # does not match the contiguous shard the engine reads / writes for these collectives.
+        channels = 1
     # Every channel's slice must split evenly over the ranks, in 16-byte units where possible.
     while channels > 1 and numel % (channels * world):
         channels //= 2

@@ -51,6 +51,18 @@ def test_multichannel_ring_and_twoshot(channels):
             torch.testing.assert_close(out.double(), sum(x.double() for x in xs), atol=1e-5, rtol=1e-5)
 
 
+@pytest.mark.parametrize("kind", ["reduce_scatter", "allgather", "alltoall"])
+@pytest.mark.parametrize("name", ["twoshot", "nvls"])
+def test_multichannel_sharded_collectives_keep_contiguous_shards(name, kind):
+    world, n, channels = 4, 4 * 8 * 16, 8
+    if name == "nvls" and kind == "alltoall":
+        pytest.skip("no in-switch all-to-all")
+    plans = build_plans(ALGORITHMS[name](), kind, world, n, channels=channels)
+    xs = make_inputs(kind, world, n)
+    for out, ref in zip(simulate(plans, xs), expected(kind, xs, world, n)):
+        torch.testing.assert_close(out.double(), ref, atol=1e-5, rtol=1e-5)
+
+
 def test_bf16_accumulates_in_fp32():
     world, n = 8, 64 * 8
     plans = build_plans(TwoShotAllreduce(), "allreduce", world, n, dtype="bfloat16")
