@@ -1,0 +1,95 @@
+// Launchers of the tcgen05 GEMM kernels: tensor-map construction and launch.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "../engine/cuda_driver.h"
+#include "gemm_host.h"
+#include "umma_gemm.cuh"
+
+namespace pccl {
+namespace gemm {
+
+namespace {
+
+uint32_t* g_error = nullptr;
+std::once_flag g_error_once;
+
+// 2-D bf16 tensor map over a row-major matrix: inner dimension = columns, box = kBK x box_rows,
+// 128-byte swizzle (the layout tcgen05.mma's SWIZZLE_128B descriptor expects).
+CUtensorMap make_map(const MatrixDesc& m, uint32_t box_rows) {
+  PCCL_CHECK(reinterpret_cast<uintptr_t>(m.ptr) % 16 == 0, "GEMM operand must be 16-byte aligned");
+  PCCL_CHECK(m.ld % 8 == 0, "GEMM operand leading dimension must be a multiple of 8 elements");
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(m.cols), static_cast<cuuint64_t>(m.rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(m.ld) * 2};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  PCCL_CU(DriverApi::get().cuTensorMapEncodeTiled(
+      &map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(m.ptr), dims, strides, box, elem,
+      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+  return map;
+}
+
+int sm_count() {
+  static int sms = [] {
+    int dev = 0, n = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n;
+  }();
+  return sms;
+}
+
+template <class Policy>
+void launch(const MatrixDesc& a, const MatrixDesc& b, const typename Policy::Params& params, int ctas,
+            uint64_t timeout_ms, cudaStream_t stream) {
+  PCCL_CHECK(a.cols == b.cols, "GEMM: A and B disagree on K (" << a.cols << " vs " << b.cols << ")");
+  PCCL_CHECK(a.cols % 8 == 0, "GEMM: K must be a multiple of 8");
+  Problem g;
+  g.M = a.rows; g.N = b.rows; g.K = a.cols;
+  g.tiles_m = (g.M + kBM - 1) / kBM;
+  g.tiles_n = (g.N + kBN - 1) / kBN;
+  g.error = error_word();
+  g.timeout_ns = timeout_ms * 1000000ull;
+  const CUtensorMap ta = make_map(a, kBM), tb = make_map(b, kBN);
+  static std::once_flag attr_once;
+  auto kernel = umma_gemm_kernel<Policy>;
+  PCCL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+  const int tiles = g.tiles_m * g.tiles_n;
+  int grid = ctas > 0 ? ctas : sm_count();
+  if (grid > tiles) grid = tiles;
+  if (grid < 1) return;
+  kernel<<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, g, params);
+  PCCL_CUDA(cudaGetLastError());
+  (void)attr_once;
+}
+
+}  // namespace
+
+uint32_t* error_word() {
+  std::call_once(g_error_once, [] {
+    PCCL_CUDA(cudaMalloc(reinterpret_cast<void**>(&g_error), sizeof(uint32_t)));
+    PCCL_CUDA(cudaMemset(g_error, 0, sizeof(uint32_t)));
+  });
+  return g_error;
+}
+
+uint32_t read_error() {
+  uint32_t v = 0;
+  PCCL_CUDA(cudaMemcpy(&v, error_word(), sizeof v, cudaMemcpyDeviceToHost));
+  return v;
+}
+
+void clear_error() { PCCL_CUDA(cudaMemset(error_word(), 0, sizeof(uint32_t))); }
+
+void gemm_bf16_nt(const MatrixDesc& a, const MatrixDesc& b, void* c, int64_t ldc, cudaStream_t stream, int ctas,
+                  uint64_t timeout_ms) {
+  PCCL_CHECK(ldc % 8 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0, "GEMM: C must be 16-byte aligned rows");
+  StorePolicy::Params p{static_cast<__nv_bfloat16*>(c), ldc};
+  launch<StorePolicy>(a, b, p, ctas, timeout_ms, stream);
+}
+
+}  // namespace gemm
+}  // namespace pccl

@@ -1,0 +1,233 @@
+// Persistent, warp-specialised bf16 GEMM on the 5th-generation tensor cores:
+//     C[M,N] = A[M,K] * B[N,K]^T      (A and B row-major, i.e. both K-major; fp32 accumulate)
+//
+//   warp 0      TMA producer: streams 128x64 A tiles and 256x64 B tiles (128-byte swizzle)
+//               from this GPU's HBM into a 4-stage shared-memory ring (plain, non-multicast
+//               cp.async.bulk.tensor loads completing on mbarriers);
+//   warp 1      MMA issuer: one elected lane issues tcgen05.mma (M128 x N256 x K16) with the
+//               accumulator in tensor memory; two 256-column accumulators alternate so the
+//               epilogue of tile i overlaps the main loop of tile i+1;
+//   warps 2-5   epilogue: tcgen05.ld the accumulator (each warp owns 32 TMEM lanes = 32 rows),
+//               then hand 32-column row segments to the Policy, which converts and stores
+//               them — to local memory, or straight into a peer GPU's memory for the fused
+//               GEMM -> reduce-scatter.
+//
+// A Policy supplies the tile order, an optional "rows ready" wait before a tile's A rows
+// are loaded (all-gather -> GEMM), the row-segment store, and a per-tile completion hook.
+// Every wait is bounded; on a timeout the error word is set, all roles leave their loops,
+// the CTA waits for its outstanding TMA transactions, frees its TMEM and returns.
+// The reference contains no GEMM or tensor-core code; this kernel has no counterpart there.
+#pragma once
+#include <cuda_bf16.h>
+
+#include "../ptx/tcgen05.cuh"
+
+namespace pccl {
+namespace gemm {
+
+constexpr int kBM = 128, kBN = 256, kBK = 64, kStages = 4;
+constexpr int kUmmaK = 16;
+constexpr int kThreads = 192;
+constexpr uint32_t kBytesA = kBM * kBK * 2, kBytesB = kBN * kBK * 2;
+constexpr uint32_t kStageBytes = kBytesA + kBytesB;
+constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024;   // + alignment slack
+constexpr uint32_t kTmemCols = 512;                             // 2 accumulators x 256 columns
+
+struct Problem {
+  int M, N, K;
+  int tiles_m, tiles_n;
+  uint32_t* error;            // device word: 0 ok, else (code << 8 | role)
+  uint64_t timeout_ns;
+};
+
+enum ErrorCode : uint32_t { kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueWait = 3, kErrPolicyWait = 4 };
+
+struct Pipe {
+  uint64_t full[kStages], empty[kStages];
+  uint64_t acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+  uint32_t pad;
+};
+
+__device__ __forceinline__ void raise_error(const Problem& g, uint32_t code, uint32_t role) {
+  atomicCAS(g.error, 0u, code << 8 | role);
+}
+
+template <class Policy>
+__global__ void __launch_bounds__(kThreads, 1)
+umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 const Problem g, const typename Policy::Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ Pipe pipe;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const volatile uint32_t* abort_flag = g.error;
+  const uint64_t deadline = ptx::globaltimer() + g.timeout_ns;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { ptx::mbar_init(&pipe.full[s], 1); ptx::mbar_init(&pipe.empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { ptx::mbar_init(&pipe.acc_full[a], 1); ptx::mbar_init(&pipe.acc_empty[a], 4); }
+    ptx::mbar_init_fence();
+    ptx::tma_prefetch_desc(&tma_a);
+    ptx::tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(&pipe.tmem_base, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = pipe.tmem_base;
+
+  const int num_tiles = g.tiles_m * g.tiles_n;
+  const int k_blocks = (g.K + kBK - 1) / kBK;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      int issued = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int mb, nb;
+        Policy::tile_coords(p, g, tile, &mb, &nb);
+        if (!Policy::before_load(p, g, mb, deadline, abort_flag)) { raise_error(g, kErrPolicyWait, 0); break; }
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!ptx::mbar_wait(&pipe.empty[stage], phase ^ 1u, deadline, abort_flag)) {
+            raise_error(g, kErrProducerWait, 0); ok = false; break;
+          }
+          uint8_t* a_dst = smem + stage * kStageBytes;
+          uint8_t* b_dst = a_dst + kBytesA;
+          ptx::mbar_expect_tx(&pipe.full[stage], kStageBytes);
+          ptx::tma_load_2d(a_dst, &tma_a, &pipe.full[stage], kb * kBK, mb * kBM);
+          ptx::tma_load_2d(b_dst, &tma_b, &pipe.full[stage], kb * kBK, nb * kBN);
+          ++issued;
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      // Leaving early: wait (bounded) until the loads already issued have landed, so no
+      // bulk copy is still writing this CTA's shared memory when it exits.
+      if (!ok || *abort_flag) {
+        const uint64_t drain_deadline = ptx::globaltimer() + 50000000ull;
+        uint32_t s = stage, ph = phase;
+        for (int back = 0; back < kStages && back < issued; ++back) {
+          if (s == 0) { s = kStages; ph ^= 1u; }
+          --s;
+          uint32_t no_abort = 0;
+          ptx::mbar_wait(&pipe.full[s], ph, drain_deadline, &no_abort);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = ptx::umma_idesc_f32(kBM, kBN, true);
+      uint32_t stage = 0, phase = 0;
+      uint32_t local_tile = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+        const uint32_t acc = local_tile & 1u, acc_phase = (local_tile >> 1) & 1u;
+        if (!ptx::mbar_wait(&pipe.acc_empty[acc], acc_phase ^ 1u, deadline, abort_flag)) {
+          raise_error(g, kErrMmaWait, 1); break;
+        }
+        ptx::tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + acc * kBN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!ptx::mbar_wait(&pipe.full[stage], phase, deadline, abort_flag)) {
+            raise_error(g, kErrMmaWait, 1); ok = false; break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t a_addr = ptx::smem_u32(smem + stage * kStageBytes);
+          const uint32_t b_addr = a_addr + kBytesA;
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            // Advancing K by 16 bf16 = 32 bytes inside the 128-byte swizzled row.
+            const uint64_t da = ptx::umma_desc_k_sw128(a_addr + k * kUmmaK * 2);
+            const uint64_t db = ptx::umma_desc_k_sw128(b_addr + k * kUmmaK * 2);
+            ptx::umma_f16(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          ptx::umma_commit(&pipe.empty[stage]);       // frees the stage when these MMAs retire
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) ptx::umma_commit(&pipe.acc_full[acc]);  // accumulator complete
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (warps 2..5)
+    const int quarter = warp & 3;                      // TMEM lanes [32*quarter, +32)
+    uint32_t local_tile = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local_tile) {
+      const uint32_t acc = local_tile & 1u, acc_phase = (local_tile >> 1) & 1u;
+      int mb, nb;
+      Policy::tile_coords(p, g, tile, &mb, &nb);
+      uint32_t ok = 1;
+      if (lane == 0) ok = ptx::mbar_wait(&pipe.acc_full[acc], acc_phase, deadline, abort_flag) ? 1u : 0u;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) { if (lane == 0) raise_error(g, kErrEpilogueWait, 2); break; }
+      ptx::tc_fence_after_sync();
+      const int row = mb * kBM + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + acc * kBN + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < kBN; c += 32) {
+        uint32_t v[32];
+        ptx::tmem_ld_32x32b_x32(taddr + c, v);
+        ptx::tmem_ld_wait();
+        const int col = nb * kBN + c;
+        if (row < g.M && col < g.N) Policy::store_row(p, g, row, col, reinterpret_cast<const float*>(v));
+      }
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&pipe.acc_empty[acc]);
+      Policy::tile_done(p, g, mb, nb, quarter, lane);
+    }
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---- the plain policy: C is a row-major bf16 matrix in local memory -------------------------------
+
+__device__ __forceinline__ uint4 pack8_bf16(const float* f) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    w[i] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+struct StorePolicy {
+  struct Params {
+    __nv_bfloat16* c;
+    int64_t ldc;
+  };
+  // M-fastest order: consecutive CTAs share the B tile (weights) through L2.
+  __device__ static void tile_coords(const Params&, const Problem& g, int tile, int* mb, int* nb) {
+    *mb = tile % g.tiles_m;
+    *nb = tile / g.tiles_m;
+  }
+  __device__ static bool before_load(const Params&, const Problem&, int, uint64_t, const volatile uint32_t*) {
+    return true;
+  }
+  __device__ static void store_row(const Params& p, const Problem& g, int row, int col, const float* v) {
+    __nv_bfloat16* dst = p.c + static_cast<int64_t>(row) * p.ldc + col;
+    if (col + 32 <= g.N) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(dst + 8 * i) = pack8_bf16(v + 8 * i);
+    } else {
+      for (int i = 0; col + i < g.N; ++i) dst[i] = __float2bfloat16_rn(v[i]);
+    }
+  }
+  __device__ static void tile_done(const Params&, const Problem&, int, int, int, int) {}
+};
+
+}  // namespace gemm
+}  // namespace pccl

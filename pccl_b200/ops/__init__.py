@@ -1,1 +1,5 @@
-"""ops (populated below)."""
+"""Fused compute + collective operators built on hand-written tcgen05 kernels."""
+
+from . import gemm
+
+__all__ = ["gemm"]
