@@ -5,6 +5,7 @@
 #include <torch/extension.h>
 
 #include "../common/util.h"
+#include "../engine/engine.h"
 #include "gemm_host.h"
 
 namespace py = pybind11;
@@ -18,6 +19,22 @@ gemm::MatrixDesc as_matrix(const torch::Tensor& t, const char* what) {
   TORCH_CHECK(t.scalar_type() == torch::kBFloat16, what, " must be bfloat16");
   TORCH_CHECK(t.stride(1) == 1, what, " must be row-major (unit stride in the last dimension)");
   return gemm::MatrixDesc{t.data_ptr(), static_cast<int>(t.size(0)), static_cast<int>(t.size(1)), t.stride(0)};
+}
+
+// Heap bases of every connected rank, from the process-wide engine.
+gemm::PeerBases peer_bases() {
+  Engine& e = Engine::instance();
+  gemm::PeerBases b{};
+  b.rank = e.rank();
+  b.world = e.world();
+  for (int r = 0; r < b.world; ++r) b.base[r] = e.context().heap().data(r);
+  return b;
+}
+
+uint32_t* as_u32(torch::Tensor& t, int64_t min_elems, const char* what) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kInt32 && t.is_contiguous() && t.numel() >= min_elems,
+              what, " must be a contiguous CUDA int32 tensor of at least ", min_elems, " elements");
+  return reinterpret_cast<uint32_t*>(t.data_ptr());
 }
 
 }  // namespace
@@ -35,6 +52,34 @@ void bind_fused_ops(py::module_& m) {
           return c;
         },
         py::arg("a"), py::arg("b"), py::arg("out") = py::none(), py::arg("ctas") = 0);
+  // Fused GEMM -> reduce-scatter over the engine's ranks (see fused/gemm_host.h for the contract).
+  f.def("gemm_reduce_scatter",
+        [](const torch::Tensor& x, const torch::Tensor& w, torch::Tensor& out, int64_t recv_off, int64_t flags_off,
+           torch::Tensor& block_counter, int64_t epoch, int ctas) {
+          const gemm::MatrixDesc dx = as_matrix(x, "x"), dw = as_matrix(w, "w");
+          TORCH_CHECK(out.scalar_type() == torch::kBFloat16 && out.stride(1) == 1, "out must be row-major bf16");
+          gemm::gemm_reduce_scatter(peer_bases(), dx, dw, static_cast<uint64_t>(recv_off),
+                                    static_cast<uint64_t>(flags_off),
+                                    as_u32(block_counter, (x.size(0) + 127) / 128, "block_counter"), out.data_ptr(),
+                                    out.stride(0), static_cast<uint32_t>(epoch),
+                                    c10::cuda::getCurrentCUDAStream().stream(), ctas);
+        },
+        py::arg("x"), py::arg("w"), py::arg("out"), py::arg("recv_off"), py::arg("flags_off"),
+        py::arg("block_counter"), py::arg("epoch"), py::arg("ctas") = 0);
+  // Fused all-gather -> GEMM; the gathered activations live in the symmetric heap at gathered_off.
+  f.def("all_gather_gemm",
+        [](int64_t gathered_off, int64_t m, int64_t k, const torch::Tensor& w, torch::Tensor& out, int64_t flags_off,
+           torch::Tensor& ready, int64_t epoch, int copy_ctas, int ctas) {
+          const gemm::MatrixDesc dw = as_matrix(w, "w");
+          TORCH_CHECK(out.scalar_type() == torch::kBFloat16 && out.stride(1) == 1, "out must be row-major bf16");
+          gemm::all_gather_gemm(peer_bases(), static_cast<uint64_t>(gathered_off), static_cast<int>(m),
+                                static_cast<int>(k), dw, static_cast<uint64_t>(flags_off),
+                                as_u32(ready, (m + 127) / 128, "ready"), out.data_ptr(), out.stride(0),
+                                static_cast<uint32_t>(epoch), c10::cuda::getCurrentCUDAStream().stream(), copy_ctas,
+                                ctas);
+        },
+        py::arg("gathered_off"), py::arg("m"), py::arg("k"), py::arg("w"), py::arg("out"), py::arg("flags_off"),
+        py::arg("ready"), py::arg("epoch"), py::arg("copy_ctas") = 20, py::arg("ctas") = 0);
   // Device-side error word of the GEMM family (0 = ok); synchronises.
   f.def("read_error", &gemm::read_error);
   f.def("clear_error", &gemm::clear_error);

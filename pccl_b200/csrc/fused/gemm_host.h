@@ -24,5 +24,28 @@ struct MatrixDesc {
 void gemm_bf16_nt(const MatrixDesc& a, const MatrixDesc& b, void* c, int64_t ldc, cudaStream_t stream,
                   int ctas = 0, uint64_t timeout_ms = 2000);
 
+// Every rank's symmetric heap base as mapped into this process, plus rank / world.
+struct PeerBases {
+  uint8_t* base[8];
+  int rank, world;
+};
+
+// Fused tensor-parallel GEMM -> reduce-scatter.  x[M, K_local], w[N, K_local] local bf16;
+// out[M / world, N] local bf16.  recv_off / flags_off are symmetric-heap offsets of
+// recv[2][world][M / world][N] bf16 and flags[world][M / world / 128] u32 (zeroed once, before
+// the first call, on every rank); block_counter is a local zero-initialised u32[M / 128].
+// epoch = 1, 2, 3, ... must advance by one per call on every rank.
+void gemm_reduce_scatter(const PeerBases& peers, const MatrixDesc& x, const MatrixDesc& w, uint64_t recv_off,
+                         uint64_t flags_off, uint32_t* block_counter, void* out, int64_t ldo, uint32_t epoch,
+                         cudaStream_t stream, int ctas = 0, uint64_t timeout_ms = 2000);
+
+// Fused all-gather -> GEMM.  The gathered activations live at heap offset gathered_off on every
+// rank ([M, K] bf16, M = world * rows_per_rank); each rank has written its own row shard there
+// before the call.  w[N_local, K] local bf16, out[M, N_local] local bf16.  flags_off: symmetric
+// u32[2 * world]; ready: local zero-initialised u32[M / 128].
+void all_gather_gemm(const PeerBases& peers, uint64_t gathered_off, int M, int K, const MatrixDesc& w,
+                     uint64_t flags_off, uint32_t* ready, void* out, int64_t ldc, uint32_t epoch,
+                     cudaStream_t stream, int copy_ctas = 20, int ctas = 0, uint64_t timeout_ms = 2000);
+
 }  // namespace gemm
 }  // namespace pccl

@@ -5,6 +5,7 @@
 
 #include "../engine/cuda_driver.h"
 #include "gemm_host.h"
+#include "tp_policies.cuh"
 #include "umma_gemm.cuh"
 
 namespace pccl {
@@ -44,7 +45,7 @@ int sm_count() {
 
 template <class Policy>
 void launch(const MatrixDesc& a, const MatrixDesc& b, const typename Policy::Params& params, int ctas,
-            uint64_t timeout_ms, cudaStream_t stream) {
+            uint64_t timeout_ms, cudaStream_t stream, int aux_ctas = 0) {
   PCCL_CHECK(a.cols == b.cols, "GEMM: A and B disagree on K (" << a.cols << " vs " << b.cols << ")");
   PCCL_CHECK(a.cols % 8 == 0, "GEMM: K must be a multiple of 8");
   Problem g;
@@ -58,9 +59,12 @@ void launch(const MatrixDesc& a, const MatrixDesc& b, const typename Policy::Par
   auto kernel = umma_gemm_kernel<Policy>;
   PCCL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
   const int tiles = g.tiles_m * g.tiles_n;
+  // `grid` counts all CTAs (one per SM at most: CTAs wait on one another through flags);
+  // `aux_ctas` of them do not run GEMM tiles.
   int grid = ctas > 0 ? ctas : sm_count();
-  if (grid > tiles) grid = tiles;
-  if (grid < 1) return;
+  if (grid > sm_count()) grid = sm_count();
+  if (grid - aux_ctas > tiles) grid = tiles + aux_ctas;
+  if (grid - aux_ctas < 1) grid = aux_ctas + 1;
   kernel<<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, g, params);
   PCCL_CUDA(cudaGetLastError());
   (void)attr_once;
@@ -89,6 +93,60 @@ void gemm_bf16_nt(const MatrixDesc& a, const MatrixDesc& b, void* c, int64_t ldc
   PCCL_CHECK(ldc % 8 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0, "GEMM: C must be 16-byte aligned rows");
   StorePolicy::Params p{static_cast<__nv_bfloat16*>(c), ldc};
   launch<StorePolicy>(a, b, p, ctas, timeout_ms, stream);
+}
+
+namespace {
+PeerView to_view(const PeerBases& b) {
+  PeerView v{};
+  for (int r = 0; r < b.world; ++r) v.base[r] = b.base[r];
+  v.rank = b.rank;
+  v.world = b.world;
+  return v;
+}
+}  // namespace
+
+void gemm_reduce_scatter(const PeerBases& peers, const MatrixDesc& x, const MatrixDesc& w, uint64_t recv_off,
+                         uint64_t flags_off, uint32_t* block_counter, void* out, int64_t ldo, uint32_t epoch,
+                         cudaStream_t stream, int ctas, uint64_t timeout_ms) {
+  PCCL_CHECK(x.rows % peers.world == 0, "GEMM->RS: M must divide by the world size");
+  const int rows_per_rank = x.rows / peers.world;
+  PCCL_CHECK(rows_per_rank % kBM == 0, "GEMM->RS: rows per rank must be a multiple of " << kBM);
+  PCCL_CHECK(w.rows % 8 == 0 && ldo % 8 == 0, "GEMM->RS: N and the output stride must be multiples of 8");
+  PCCL_CHECK(epoch >= 1, "GEMM->RS: epoch counts calls from 1");
+  ReduceScatterPolicy::Params p{};
+  p.peers = to_view(peers);
+  p.recv_off = recv_off;
+  p.flags_off = flags_off;
+  p.block_counter = block_counter;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.ldo = ldo;
+  p.rows_per_rank = rows_per_rank;
+  p.blocks_per_rank = rows_per_rank / kBM;
+  p.epoch = epoch;
+  launch<ReduceScatterPolicy>(x, w, p, ctas, timeout_ms, stream);
+}
+
+void all_gather_gemm(const PeerBases& peers, uint64_t gathered_off, int M, int K, const MatrixDesc& w,
+                     uint64_t flags_off, uint32_t* ready, void* out, int64_t ldc, uint32_t epoch,
+                     cudaStream_t stream, int copy_ctas, int ctas, uint64_t timeout_ms) {
+  PCCL_CHECK(M % peers.world == 0 && (M / peers.world) % kBM == 0,
+             "AG->GEMM: rows per rank must be a multiple of " << kBM);
+  PCCL_CHECK(epoch >= 1, "AG->GEMM: epoch counts calls from 1");
+  AllGatherPolicy::Params p{};
+  p.peers = to_view(peers);
+  p.gathered_off = gathered_off;
+  p.flags_off = flags_off;
+  p.ready = ready;
+  p.c = static_cast<__nv_bfloat16*>(out);
+  p.ldc = ldc;
+  p.rows_per_rank = M / peers.world;
+  p.blocks_per_rank = p.rows_per_rank / kBM;
+  p.copy_ctas = peers.world > 1 ? copy_ctas : 0;
+  p.epoch = epoch;
+  MatrixDesc a{peers.base[peers.rank] + gathered_off, M, K, K};
+  const int sms = sm_count();
+  int grid = ctas > 0 ? ctas : sms;
+  launch<AllGatherPolicy>(a, w, p, grid, timeout_ms, stream, p.copy_ctas);
 }
 
 }  // namespace gemm

@@ -1,0 +1,249 @@
+// Tensor-parallel GEMMs fused with their collective, as policies of umma_gemm_kernel.
+//
+//   ReduceScatterPolicy   Y = sum_r X_r W_r^T, scattered over rows (tokens).  Every rank computes
+//       its full partial product; the epilogue stores each bf16 row segment straight into the
+//       *owning* rank's receive slot for this source over NVLink (tiles ordered so the most
+//       remote owner comes first and the own rows last), and posts one flag per finished
+//       128-row block.  After its GEMM tiles a CTA turns reducer: it waits for the flags of all
+//       sources of a block and sums the W slots in rank order (fp32, deterministic).
+//   AllGatherPolicy       Y_r = gather(X) W_r^T.  A few auxiliary CTAs pull the peers' row shards
+//       into the *local* gathered matrix with SM loads and publish a ready flag per 128-row
+//       block; the GEMM CTAs start with the local shard and wait for a block's flag before
+//       its TMA loads (which therefore only ever read this GPU's memory).
+//
+// Flags count calls (the host passes the call number `epoch`), so nothing is reset between
+// calls; receive slots are double-buffered by epoch parity.  All waits are bounded.
+// The unfused baseline is cuBLAS + NCCL; the reference has neither operator.
+#pragma once
+#include <cuda_bf16.h>
+
+#include "../executors/sm100/program.h"
+#include "umma_gemm.cuh"
+
+namespace pccl {
+namespace gemm {
+
+struct PeerView {
+  uint8_t* base[kMaxRanks];     // every rank's symmetric heap as mapped here
+  int rank, world;
+};
+
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t want, uint64_t deadline,
+                                             const volatile uint32_t* abort_flag) {
+  uint32_t spins = 0;
+  while (static_cast<int32_t>(ptx::ld_acquire_sys(flag) - want) < 0) {
+    if ((++spins & 63u) == 0u) {
+      if (*abort_flag || ptx::globaltimer() > deadline) return false;
+      __nanosleep(64);
+    }
+  }
+  return true;
+}
+
+// ------------------------------------------------------------------------------------------------
+struct ReduceScatterPolicy {
+  struct Params {
+    PeerView peers;
+    uint64_t recv_off;          // heap offset of recv[2][world][rows_per_rank][N] bf16
+    uint64_t flags_off;         // heap offset of flags[world][blocks_per_rank] u32
+    uint32_t* block_counter;    // local, [tiles_m]: epilogue warps finished per 128-row block (monotonic)
+    __nv_bfloat16* out;         // local result [rows_per_rank][N]
+    int64_t ldo;
+    int rows_per_rank, blocks_per_rank;
+    uint32_t epoch;             // 1, 2, 3, ... per call
+  };
+
+  // Owners in the order rank+1, rank+2, ..., rank; inside an owner, n-tiles of one row block
+  // are consecutive so that the block's flag is posted as early as possible.
+  __device__ static void tile_coords(const Params& p, const Problem& g, int tile, int* mb, int* nb) {
+    const int per_owner = p.blocks_per_rank * g.tiles_n;
+    const int owner = (p.peers.rank + 1 + tile / per_owner) % p.peers.world;
+    const int within = tile % per_owner;
+    *mb = owner * p.blocks_per_rank + within / g.tiles_n;
+    *nb = within % g.tiles_n;
+  }
+  __device__ static bool before_load(const Params&, const Problem&, int, uint64_t, const volatile uint32_t*) {
+    return true;
+  }
+  __device__ static uint8_t* slot(const Params& p, const Problem& g, int owner, int src, int local_row) {
+    const uint64_t slot_bytes = static_cast<uint64_t>(p.rows_per_rank) * g.N * 2;
+    const uint64_t parity = p.epoch & 1u;
+    return p.peers.base[owner] + p.recv_off + (parity * p.peers.world + src) * slot_bytes +
+           static_cast<uint64_t>(local_row) * g.N * 2;
+  }
+  __device__ static void store_row(const Params& p, const Problem& g, int row, int col, const float* v) {
+    const int owner = row / p.rows_per_rank, local_row = row % p.rows_per_rank;
+    uint8_t* dst = slot(p, g, owner, p.peers.rank, local_row) + static_cast<uint64_t>(col) * 2;
+    if (col + 32 <= g.N) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) ptx::st_v4(dst + 16 * i, pack8_bf16(v + 8 * i));
+    } else {
+      for (int i = 0; col + i < g.N; ++i) reinterpret_cast<__nv_bfloat16*>(dst)[i] = __float2bfloat16_rn(v[i]);
+    }
+  }
+  __device__ static void tile_done(const Params& p, const Problem& g, int mb, int, int, int lane) {
+    // Make this warp's (possibly remote) stores visible, then count; the warp that completes
+    // the block posts the flag at the owner.
+    __syncwarp();
+    if (lane == 0) {
+      ptx::fence_sys();
+      const uint32_t target = p.epoch * static_cast<uint32_t>(g.tiles_n) * 4u;
+      const uint32_t seen = atomicAdd(p.block_counter + mb, 1u) + 1u;
+      if (seen == target) {
+        ptx::fence_sys();
+        const int owner = mb / p.blocks_per_rank, local_block = mb % p.blocks_per_rank;
+        uint32_t* flag = reinterpret_cast<uint32_t*>(p.peers.base[owner] + p.flags_off) +
+                         p.peers.rank * p.blocks_per_rank + local_block;
+        ptx::red_release_sys_add(flag, 1u);
+      }
+    }
+  }
+  __device__ static int aux_ctas(const Params&) { return 0; }
+  __device__ static void aux_main(const Params&, const Problem&, int, int, uint64_t, const volatile uint32_t*) {}
+
+  // Reducer phase: item = (local row block, n tile); sum the world slots in rank order.
+  __device__ static void finish(const Params& p, const Problem& g, int cta, int num_ctas, uint64_t deadline,
+                                const volatile uint32_t* abort_flag) {
+    __shared__ uint32_t ok_flag;
+    const int me = p.peers.rank, world = p.peers.world;
+    const uint32_t* flags = reinterpret_cast<const uint32_t*>(p.peers.base[me] + p.flags_off);
+    const int items = p.blocks_per_rank * g.tiles_n;
+    for (int item = cta; item < items; item += num_ctas) {
+      const int block = item / g.tiles_n, nb = item % g.tiles_n;
+      if (threadIdx.x == 0) ok_flag = 1;
+      __syncthreads();
+      if (static_cast<int>(threadIdx.x) < world) {
+        if (!wait_flag_ge(flags + threadIdx.x * p.blocks_per_rank + block, p.epoch, deadline, abort_flag)) {
+          ok_flag = 0;
+          raise_error(g, kErrPolicyWait, 3);
+        }
+      }
+      __syncthreads();
+      if (!ok_flag) return;
+      const int row0 = block * kBM, col0 = nb * kBN;
+      const int rows = min(kBM, p.rows_per_rank - row0), cols = min(kBN, g.N - col0);
+      const int vec_per_row = cols / 8;                    // 8 bf16 per 16 bytes (N % 8 == 0)
+      for (int i = threadIdx.x; i < rows * vec_per_row; i += blockDim.x) {
+        const int r = row0 + i / vec_per_row, c = col0 + (i % vec_per_row) * 8;
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int s = 0; s < world; ++s) {
+          const uint4 raw = ptx::ld_local_v4(slot(p, g, me, s, r) + static_cast<uint64_t>(c) * 2);
+          const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc[2 * j] += __uint_as_float(w[j] << 16);
+            acc[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u);
+          }
+        }
+        *reinterpret_cast<uint4*>(p.out + static_cast<int64_t>(r) * p.ldo + c) = pack8_bf16(acc);
+      }
+    }
+  }
+};
+
+// ------------------------------------------------------------------------------------------------
+struct AllGatherPolicy {
+  struct Params {
+    PeerView peers;
+    uint64_t gathered_off;      // heap offset of the gathered A [world * rows_per_rank][K] bf16 (per rank)
+    uint64_t flags_off;         // heap offset of u32 flags: [0, world) "shard of rank s is in place" (posted
+                                // by s at every peer), [world, 2*world) "rank s finished reading my shard"
+    uint32_t* ready;            // local, [tiles_m]: gathered row block is complete (epoch counting)
+    __nv_bfloat16* c;           // local result [M][N]
+    int64_t ldc;
+    int rows_per_rank, blocks_per_rank, copy_ctas;
+    uint32_t epoch;
+  };
+
+  // Shards in the order own, rank+1, rank+2, ...; M-fastest inside a shard.
+  __device__ static void tile_coords(const Params& p, const Problem& g, int tile, int* mb, int* nb) {
+    const int per_shard = p.blocks_per_rank * g.tiles_n;
+    const int shard = (p.peers.rank + tile / per_shard) % p.peers.world;
+    const int within = tile % per_shard;
+    *mb = shard * p.blocks_per_rank + within % p.blocks_per_rank;
+    *nb = within / p.blocks_per_rank;
+  }
+  __device__ static bool before_load(const Params& p, const Problem&, int mb, uint64_t deadline,
+                                     const volatile uint32_t* abort_flag) {
+    if (mb / p.blocks_per_rank == p.peers.rank) return true;          // the local shard is already there
+    const bool ok = wait_flag_ge(p.ready + mb, p.epoch, deadline, abort_flag);
+    // The rows were written by generic-proxy stores of other CTAs; TMA reads through the async proxy.
+    asm volatile("fence.proxy.async.global;" ::: "memory");
+    return ok;
+  }
+  __device__ static void store_row(const Params& p, const Problem& g, int row, int col, const float* v) {
+    __nv_bfloat16* dst = p.c + static_cast<int64_t>(row) * p.ldc + col;
+    if (col + 32 <= g.N) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(dst + 8 * i) = pack8_bf16(v + 8 * i);
+    } else {
+      for (int i = 0; col + i < g.N; ++i) dst[i] = __float2bfloat16_rn(v[i]);
+    }
+  }
+  __device__ static void tile_done(const Params&, const Problem&, int, int, int, int) {}
+  __device__ static int aux_ctas(const Params& p) { return p.copy_ctas; }
+
+  // Copier CTAs.  CTA 0 first announces "my shard is in place" to every peer.  Then the copiers
+  // walk the peers' shards (nearest successor first), block by block: pull 128 rows x K into the
+  // local gathered matrix, fence, publish ready[mb].  Finally each source is told that its shard
+  // has been read, and CTA 0 waits until every peer has read this rank's shard, so the caller
+  // may overwrite its input when the kernel is done.
+  __device__ static void aux_main(const Params& p, const Problem& g, int cta, int num_ctas, uint64_t deadline,
+                                  const volatile uint32_t* abort_flag) {
+    __shared__ uint32_t ok_flag;
+    const int me = p.peers.rank, world = p.peers.world;
+    uint32_t* my_flags = reinterpret_cast<uint32_t*>(p.peers.base[me] + p.flags_off);
+    if (cta == 0 && static_cast<int>(threadIdx.x) < world && static_cast<int>(threadIdx.x) != me) {
+      uint32_t* there = reinterpret_cast<uint32_t*>(p.peers.base[threadIdx.x] + p.flags_off) + me;
+      ptx::fence_sys();
+      ptx::red_release_sys_add(there, 1u);
+    }
+    const uint64_t row_bytes = static_cast<uint64_t>(g.K) * 2;
+    const int remote_blocks = (world - 1) * p.blocks_per_rank;
+    for (int item = cta; item < remote_blocks; item += num_ctas) {
+      const int src = (me + 1 + item / p.blocks_per_rank) % world;
+      const int mb = src * p.blocks_per_rank + item % p.blocks_per_rank;
+      if (threadIdx.x == 0) {
+        ok_flag = wait_flag_ge(my_flags + src, p.epoch, deadline, abort_flag) ? 1u : 0u;
+        if (!ok_flag) raise_error(g, kErrPolicyWait, 4);
+      }
+      __syncthreads();
+      if (!ok_flag) return;
+      const uint64_t off = p.gathered_off + static_cast<uint64_t>(mb) * kBM * row_bytes;
+      const uint8_t* from = p.peers.base[src] + off;
+      uint8_t* to = p.peers.base[me] + off;
+      const uint64_t rows_here = min(static_cast<int>(kBM), g.M - mb * kBM);
+      const uint64_t vecs = rows_here * row_bytes / 16;
+      constexpr int kU = 8;                                // 16-byte loads in flight per thread
+      for (uint64_t v = threadIdx.x; v < vecs; v += static_cast<uint64_t>(blockDim.x) * kU) {
+        uint4 t[kU];
+#pragma unroll
+        for (int u = 0; u < kU; ++u)
+          if (v + u * blockDim.x < vecs) t[u] = ptx::ld_peer_v4(from + (v + u * blockDim.x) * 16);
+#pragma unroll
+        for (int u = 0; u < kU; ++u)
+          if (v + u * blockDim.x < vecs) ptx::st_v4(to + (v + u * blockDim.x) * 16, t[u]);
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        ptx::fence_gpu();
+        ptx::st_release_sys(p.ready + mb, p.epoch);
+        // One "done" count per block read, posted at the shard's owner.
+        uint32_t* done = reinterpret_cast<uint32_t*>(p.peers.base[src] + p.flags_off) + world + me;
+        ptx::red_release_sys_add(done, 1u);
+      }
+    }
+    if (cta == 0) {
+      // Every peer posts blocks_per_rank "done" counts per call.
+      if (static_cast<int>(threadIdx.x) < world && static_cast<int>(threadIdx.x) != me) {
+        const uint32_t want = p.epoch * static_cast<uint32_t>(p.blocks_per_rank);
+        if (!wait_flag_ge(my_flags + world + threadIdx.x, want, deadline, abort_flag))
+          raise_error(g, kErrPolicyWait, 5);
+      }
+    }
+  }
+  __device__ static void finish(const Params&, const Problem&, int, int, uint64_t, const volatile uint32_t*) {}
+};
+
+}  // namespace gemm
+}  // namespace pccl

@@ -65,6 +65,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const volatile uint32_t* abort_flag = g.error;
   const uint64_t deadline = ptx::globaltimer() + g.timeout_ns;
 
+  // Auxiliary CTAs (e.g. the copiers of all-gather -> GEMM) take no part in the GEMM pipeline.
+  const int aux = Policy::aux_ctas(p);
+  if (static_cast<int>(blockIdx.x) < aux) {
+    Policy::aux_main(p, g, blockIdx.x, aux, deadline, abort_flag);
+    return;
+  }
+  const int cta = blockIdx.x - aux, num_ctas = gridDim.x - aux;
+
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { ptx::mbar_init(&pipe.full[s], 1); ptx::mbar_init(&pipe.empty[s], 1); }
     for (int a = 0; a < 2; ++a) { ptx::mbar_init(&pipe.acc_full[a], 1); ptx::mbar_init(&pipe.acc_empty[a], 4); }
@@ -90,7 +98,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t stage = 0, phase = 0;
       int issued = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = cta; tile < num_tiles && ok; tile += num_ctas) {
         int mb, nb;
         Policy::tile_coords(p, g, tile, &mb, &nb);
         if (!Policy::before_load(p, g, mb, deadline, abort_flag)) { raise_error(g, kErrPolicyWait, 0); break; }
@@ -127,7 +135,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t stage = 0, phase = 0;
       uint32_t local_tile = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+      for (int tile = cta; tile < num_tiles && ok; tile += num_ctas, ++local_tile) {
         const uint32_t acc = local_tile & 1u, acc_phase = (local_tile >> 1) & 1u;
         if (!ptx::mbar_wait(&pipe.acc_empty[acc], acc_phase ^ 1u, deadline, abort_flag)) {
           raise_error(g, kErrMmaWait, 1); break;
@@ -158,7 +166,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     // ---------------------------------------------------------------- epilogue (warps 2..5)
     const int quarter = warp & 3;                      // TMEM lanes [32*quarter, +32)
     uint32_t local_tile = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local_tile) {
+    for (int tile = cta; tile < num_tiles; tile += num_ctas, ++local_tile) {
       const uint32_t acc = local_tile & 1u, acc_phase = (local_tile >> 1) & 1u;
       int mb, nb;
       Policy::tile_coords(p, g, tile, &mb, &nb);
@@ -190,6 +198,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc(tmem_base, kTmemCols);
   }
+  // Work that follows the GEMM on the same CTAs (e.g. the reduction of received partials).
+  Policy::finish(p, g, cta, num_ctas, deadline, abort_flag);
 }
 
 // ---- the plain policy: C is a row-major bf16 matrix in local memory -------------------------------
@@ -227,6 +237,9 @@ struct StorePolicy {
     }
   }
   __device__ static void tile_done(const Params&, const Problem&, int, int, int, int) {}
+  __device__ static int aux_ctas(const Params&) { return 0; }
+  __device__ static void aux_main(const Params&, const Problem&, int, int, uint64_t, const volatile uint32_t*) {}
+  __device__ static void finish(const Params&, const Problem&, int, int, uint64_t, const volatile uint32_t*) {}
 };
 
 }  // namespace gemm

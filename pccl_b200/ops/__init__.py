@@ -1,5 +1,6 @@
 """Fused compute + collective operators built on hand-written tcgen05 kernels."""
 
 from . import gemm
+from .tensor_parallel import AllGatherGemm, GemmReduceScatter
 
-__all__ = ["gemm"]
+__all__ = ["gemm", "GemmReduceScatter", "AllGatherGemm"]

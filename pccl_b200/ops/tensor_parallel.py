@@ -1,0 +1,90 @@
+"""Tensor-parallel linear layers whose collective is fused into the GEMM kernel.
+
+``GemmReduceScatter``  row-parallel linear + sequence-parallel output:
+    ``y[M/W, N] = reduce_scatter_rows(x[M, K/W] @ w[N, K/W].T)``.
+``AllGatherGemm``      sequence-parallel input + column-parallel linear:
+    ``y[M, N/W] = all_gather_rows(x[M/W, K]) @ w[N/W, K].T``.
+
+Both own their symmetric buffers (allocated once from the engine's arena, identical
+offsets on every rank because every rank constructs the same operators in the same
+order) and count calls: flags are never reset, a call number travels to the kernel.
+Construction is collective (it ends with a barrier so that no peer can signal a rank
+whose flags are not zeroed yet).
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from .. import engine as _engine
+
+_BLOCK = 128
+
+
+def _native():
+    return _engine.load_native().fused
+
+
+def _fence(group) -> None:
+    torch.cuda.synchronize()
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.barrier(group=group)
+
+
+class GemmReduceScatter:
+    def __init__(self, m: int, n: int, k_local: int, group=None):
+        self.engine = _engine.get_engine()
+        self.world, self.rank = self.engine.world, self.engine.rank
+        if m % (self.world * _BLOCK):
+            raise ValueError(f"M={m} must be a multiple of world*{_BLOCK}")
+        self.m, self.n, self.k = m, n, k_local
+        rows = m // self.world
+        self.recv = self.engine.empty_symmetric((2, self.world, rows, n), torch.bfloat16)
+        self.flags = self.engine.empty_symmetric((self.world * (rows // _BLOCK),), torch.int32)
+        self.flags.zero_()
+        self.block_counter = torch.zeros(m // _BLOCK, dtype=torch.int32, device="cuda")
+        self.epoch = 0
+        self.group = group
+        _fence(group)
+
+    def __call__(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor = None, ctas: int = 0) -> torch.Tensor:
+        if out is None:
+            out = torch.empty(self.m // self.world, self.n, dtype=torch.bfloat16, device=x.device)
+        self.epoch += 1
+        _native().gemm_reduce_scatter(x, w, out, self.recv.heap_offset, self.flags.heap_offset,
+                                      self.block_counter, self.epoch, ctas)
+        return out
+
+
+class AllGatherGemm:
+    def __init__(self, m: int, n_local: int, k: int, group=None, copy_ctas: int = 20):
+        self.engine = _engine.get_engine()
+        self.world, self.rank = self.engine.world, self.engine.rank
+        if m % (self.world * _BLOCK):
+            raise ValueError(f"M={m} must be a multiple of world*{_BLOCK}")
+        self.m, self.n, self.k = m, n_local, k
+        self.rows = m // self.world
+        self.gathered = self.engine.empty_symmetric((m, k), torch.bfloat16)
+        self.flags = self.engine.empty_symmetric((2 * self.world,), torch.int32)
+        self.flags.zero_()
+        self.ready = torch.zeros(m // _BLOCK, dtype=torch.int32, device="cuda")
+        self.copy_ctas = copy_ctas
+        self.epoch = 0
+        self.group = group
+        _fence(group)
+
+    @property
+    def local_shard(self) -> torch.Tensor:
+        """View of this rank's rows inside the gathered matrix: write activations here to skip the copy."""
+        return self.gathered[self.rank * self.rows:(self.rank + 1) * self.rows]
+
+    def __call__(self, x_shard: torch.Tensor, w: torch.Tensor, out: torch.Tensor = None, ctas: int = 0) -> torch.Tensor:
+        if x_shard.data_ptr() != self.local_shard.data_ptr():
+            self.local_shard.copy_(x_shard)
+        if out is None:
+            out = torch.empty(self.m, self.n, dtype=torch.bfloat16, device=w.device)
+        self.epoch += 1
+        _native().all_gather_gemm(self.gathered.heap_offset, self.m, self.k, w, out, self.flags.heap_offset,
+                                  self.ready, self.epoch, self.copy_ctas, ctas)
+        return out

@@ -20,7 +20,7 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local)
     os.environ.setdefault("PCCL_BUFFER_SIZE", str(256 << 20))
-    os.environ.setdefault("PCCL_ARENA_SIZE", str(256 << 20))
+    os.environ.setdefault("PCCL_ARENA_SIZE", str(1 << 30))
     os.environ.setdefault("PCCL_WAIT_TIMEOUT_MS", "5000")
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     import pccl_b200.parallel as pp
@@ -87,6 +87,39 @@ def main():
     ref = x.clone(); dist.all_reduce(ref); ref /= world
     y = x.clone(); pp.all_reduce(y, op="avg", algorithm="twoshot")
     torch.testing.assert_close(y, ref, atol=1e-5, rtol=1e-5)
+
+    # ---- fused tensor-parallel GEMMs (tcgen05 kernels with the collective in the epilogue) ----
+    from pccl_b200.ops import AllGatherGemm, GemmReduceScatter, gemm
+    for (m, n, k) in ((world * 256, 512, 192), (world * 1024, 4096, 1792)):
+        gen = torch.Generator(device="cuda").manual_seed(7 + rank)
+        x = torch.randn(m, k, device="cuda", generator=gen).to(torch.bfloat16)
+        w = (torch.randn(n, k, device="cuda", generator=gen) * 0.02).to(torch.bfloat16)
+        full = x.float() @ w.float().t()
+        ref = torch.empty(m // world, n, device="cuda")
+        dist.reduce_scatter_tensor(ref, full)
+        op = GemmReduceScatter(m, n, k)
+        for call in range(3):          # several calls: epoch counting and slot parity
+            y = op(x, w)
+            torch.cuda.synchronize()
+            gemm.check()
+            torch.testing.assert_close(y.float(), ref, atol=0.03, rtol=3e-2,
+                                       msg=lambda t: f"gemm_rs {m}x{n}x{k} call {call} rank {rank}: {t}")
+        report["checked"] += 1
+
+        rows = m // world
+        xs = torch.randn(rows, k, device="cuda", generator=gen).to(torch.bfloat16)
+        wl = (torch.randn(n, k, device="cuda", generator=gen) * 0.02).to(torch.bfloat16)
+        gathered = torch.empty(m, k, device="cuda", dtype=torch.bfloat16)
+        dist.all_gather_into_tensor(gathered, xs)
+        ref = gathered.float() @ wl.float().t()
+        ag = AllGatherGemm(m, n, k)
+        for call in range(3):
+            y = ag(xs, wl)
+            torch.cuda.synchronize()
+            gemm.check()
+            torch.testing.assert_close(y.float(), ref, atol=0.03, rtol=3e-2,
+                                       msg=lambda t: f"ag_gemm {m}x{n}x{k} call {call} rank {rank}: {t}")
+        report["checked"] += 1
 
     torch.cuda.synchronize()
     dist.barrier()
