@@ -18,7 +18,34 @@ std::once_flag g_error_once;
 
 // 2-D bf16 tensor map over a row-major matrix: inner dimension = columns, box = kBK x box_rows,
 // 128-byte swizzle (the layout tcgen05.mma's SWIZZLE_128B descriptor expects).
+CUtensorMap encode_map(const MatrixDesc& m, uint32_t box_rows);
+
+// Encoding a tensor map costs a few microseconds of host time; operands of a layer recur
+// call after call, so the last few maps are kept.
 CUtensorMap make_map(const MatrixDesc& m, uint32_t box_rows) {
+  struct Key {
+    const void* ptr; int rows, cols; int64_t ld; uint32_t box;
+    bool operator==(const Key& o) const {
+      return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box == o.box;
+    }
+  };
+  struct Entry { Key key; CUtensorMap map; };
+  static std::mutex mu;
+  static Entry cache[16];
+  static int used = 0, next = 0;
+  const Key key{m.ptr, m.rows, m.cols, m.ld, box_rows};
+  std::lock_guard<std::mutex> lock(mu);
+  for (int i = 0; i < used; ++i)
+    if (cache[i].key == key) return cache[i].map;
+  Entry& e = cache[next];
+  next = (next + 1) % 16;
+  if (used < 16) ++used;
+  e.key = key;
+  e.map = encode_map(m, box_rows);
+  return e.map;
+}
+
+CUtensorMap encode_map(const MatrixDesc& m, uint32_t box_rows) {
   PCCL_CHECK(reinterpret_cast<uintptr_t>(m.ptr) % 16 == 0, "GEMM operand must be 16-byte aligned");
   PCCL_CHECK(m.ld % 8 == 0, "GEMM operand leading dimension must be a multiple of 8 elements");
   CUtensorMap map;
@@ -48,6 +75,7 @@ void launch(const MatrixDesc& a, const MatrixDesc& b, const typename Policy::Par
             uint64_t timeout_ms, cudaStream_t stream, int aux_ctas = 0) {
   PCCL_CHECK(a.cols == b.cols, "GEMM: A and B disagree on K (" << a.cols << " vs " << b.cols << ")");
   PCCL_CHECK(a.cols % 8 == 0, "GEMM: K must be a multiple of 8");
+  PCCL_CHECK(b.rows % 8 == 0, "GEMM: N must be a multiple of 8");
   Problem g;
   g.M = a.rows; g.N = b.rows; g.K = a.cols;
   g.tiles_m = (g.M + kBM - 1) / kBM;

@@ -71,15 +71,8 @@ struct ReduceScatterPolicy {
     return p.peers.base[owner] + p.recv_off + (parity * p.peers.world + src) * slot_bytes +
            static_cast<uint64_t>(local_row) * g.N * 2;
   }
-  __device__ static void store_row(const Params& p, const Problem& g, int row, int col, const float* v) {
-    const int owner = row / p.rows_per_rank, local_row = row % p.rows_per_rank;
-    uint8_t* dst = slot(p, g, owner, p.peers.rank, local_row) + static_cast<uint64_t>(col) * 2;
-    if (col + 32 <= g.N) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) ptx::st_v4(dst + 16 * i, pack8_bf16(v + 8 * i));
-    } else {
-      for (int i = 0; col + i < g.N; ++i) reinterpret_cast<__nv_bfloat16*>(dst)[i] = __float2bfloat16_rn(v[i]);
-    }
+  __device__ static uint8_t* row_ptr(const Params& p, const Problem& g, int row) {
+    return slot(p, g, row / p.rows_per_rank, p.peers.rank, row % p.rows_per_rank);
   }
   __device__ static void tile_done(const Params& p, const Problem& g, int mb, int, int, int lane) {
     // Make this warp's (possibly remote) stores visible, then count; the warp that completes
@@ -171,14 +164,8 @@ struct AllGatherPolicy {
     asm volatile("fence.proxy.async.global;" ::: "memory");
     return ok;
   }
-  __device__ static void store_row(const Params& p, const Problem& g, int row, int col, const float* v) {
-    __nv_bfloat16* dst = p.c + static_cast<int64_t>(row) * p.ldc + col;
-    if (col + 32 <= g.N) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(dst + 8 * i) = pack8_bf16(v + 8 * i);
-    } else {
-      for (int i = 0; col + i < g.N; ++i) dst[i] = __float2bfloat16_rn(v[i]);
-    }
+  __device__ static uint8_t* row_ptr(const Params& p, const Problem&, int row) {
+    return reinterpret_cast<uint8_t*>(p.c + static_cast<int64_t>(row) * p.ldc);
   }
   __device__ static void tile_done(const Params&, const Problem&, int, int, int, int) {}
   __device__ static int aux_ctas(const Params& p) { return p.copy_ctas; }
@@ -214,7 +201,7 @@ struct AllGatherPolicy {
       uint8_t* to = p.peers.base[me] + off;
       const uint64_t rows_here = min(static_cast<int>(kBM), g.M - mb * kBM);
       const uint64_t vecs = rows_here * row_bytes / 16;
-      constexpr int kU = 8;                                // 16-byte loads in flight per thread
+      constexpr int kU = 16;                               // 16-byte loads in flight per thread
       for (uint64_t v = threadIdx.x; v < vecs; v += static_cast<uint64_t>(blockDim.x) * kU) {
         uint4 t[kU];
 #pragma unroll

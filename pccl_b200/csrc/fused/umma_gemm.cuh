@@ -30,7 +30,9 @@ constexpr int kUmmaK = 16;
 constexpr int kThreads = 192;
 constexpr uint32_t kBytesA = kBM * kBK * 2, kBytesB = kBN * kBK * 2;
 constexpr uint32_t kStageBytes = kBytesA + kBytesB;
-constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024;   // + alignment slack
+constexpr int kEpiCols = 128;                                   // columns staged per epilogue pass
+constexpr uint32_t kEpiWarpBytes = 32 * kEpiCols * 2;           // 32 rows x 256 B per epilogue warp
+constexpr uint32_t kSmemBytes = kStages * kStageBytes + 4 * kEpiWarpBytes + 1024;   // + alignment slack
 constexpr uint32_t kTmemCols = 512;                             // 2 accumulators x 256 columns
 
 struct Problem {
@@ -52,6 +54,8 @@ struct Pipe {
 __device__ __forceinline__ void raise_error(const Problem& g, uint32_t code, uint32_t role) {
   atomicCAS(g.error, 0u, code << 8 | role);
 }
+
+__device__ __forceinline__ uint4 pack8_bf16(const float* f);
 
 template <class Policy>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -175,15 +179,35 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) { if (lane == 0) raise_error(g, kErrEpilogueWait, 2); break; }
       ptx::tc_fence_after_sync();
-      const int row = mb * kBM + quarter * 32 + lane;
+      const int row_base = mb * kBM + quarter * 32;
       const uint32_t taddr = tmem_base + acc * kBN + (static_cast<uint32_t>(quarter * 32) << 16);
+      // Staging buffer of this warp: 32 rows x 16 chunks of 16 bytes, chunk index XOR-swizzled by
+      // the row so that both the row-wise writes and the chunk-wise reads spread over banks.
+      uint8_t* stage_buf = smem + kStages * kStageBytes + (warp - 2) * kEpiWarpBytes;
 #pragma unroll 1
-      for (int c = 0; c < kBN; c += 32) {
-        uint32_t v[32];
-        ptx::tmem_ld_32x32b_x32(taddr + c, v);
-        ptx::tmem_ld_wait();
-        const int col = nb * kBN + c;
-        if (row < g.M && col < g.N) Policy::store_row(p, g, row, col, reinterpret_cast<const float*>(v));
+      for (int c0 = 0; c0 < kBN; c0 += kEpiCols) {
+#pragma unroll
+        for (int q = 0; q < kEpiCols / 32; ++q) {
+          uint32_t v[32];
+          ptx::tmem_ld_32x32b_x32(taddr + c0 + q * 32, v);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int chunk = (q * 4 + i) ^ (lane & 15);
+            *reinterpret_cast<uint4*>(stage_buf + lane * (kEpiCols * 2) + chunk * 16) =
+                pack8_bf16(reinterpret_cast<const float*>(v) + 8 * i);
+          }
+        }
+        __syncwarp();
+        // Half a warp writes one row's 256 contiguous bytes; two rows per instruction.
+#pragma unroll 4
+        for (int it = 0; it < 16; ++it) {
+          const int r = it * 2 + (lane >> 4), j = lane & 15;
+          const int row = row_base + r, col = nb * kBN + c0 + j * 8;
+          const uint4 val = *reinterpret_cast<const uint4*>(stage_buf + r * (kEpiCols * 2) + ((j ^ (r & 15)) * 16));
+          if (row < g.M && col < g.N) ptx::st_v4(Policy::row_ptr(p, g, row) + static_cast<int64_t>(col) * 2, val);
+        }
+        __syncwarp();
       }
       ptx::tc_fence_before_sync();
       __syncwarp();
@@ -227,14 +251,9 @@ struct StorePolicy {
   __device__ static bool before_load(const Params&, const Problem&, int, uint64_t, const volatile uint32_t*) {
     return true;
   }
-  __device__ static void store_row(const Params& p, const Problem& g, int row, int col, const float* v) {
-    __nv_bfloat16* dst = p.c + static_cast<int64_t>(row) * p.ldc + col;
-    if (col + 32 <= g.N) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(dst + 8 * i) = pack8_bf16(v + 8 * i);
-    } else {
-      for (int i = 0; col + i < g.N; ++i) dst[i] = __float2bfloat16_rn(v[i]);
-    }
+  // Address of column 0 of output row `row` (bf16 elements follow contiguously; N % 8 == 0).
+  __device__ static uint8_t* row_ptr(const Params& p, const Problem&, int row) {
+    return reinterpret_cast<uint8_t*>(p.c + static_cast<int64_t>(row) * p.ldc);
   }
   __device__ static void tile_done(const Params&, const Problem&, int, int, int, int) {}
   __device__ static int aux_ctas(const Params&) { return 0; }
