@@ -53,14 +53,14 @@ struct ReduceScatterPolicy {
     uint32_t epoch;             // 1, 2, 3, ... per call
   };
 
-  // Owners in the order rank+1, rank+2, ..., rank; inside an owner, n-tiles of one row block
-  // are consecutive so that the block's flag is posted as early as possible.
+  // Row blocks are visited round-robin over the owners (rank+1, rank+2, ..., rank), so NVLink
+  // traffic is spread over the whole GEMM and every owner receives its blocks in order; the
+  // n-tiles of one row block are consecutive so that the block's flag is posted early.
   __device__ static void tile_coords(const Params& p, const Problem& g, int tile, int* mb, int* nb) {
-    const int per_owner = p.blocks_per_rank * g.tiles_n;
-    const int owner = (p.peers.rank + 1 + tile / per_owner) % p.peers.world;
-    const int within = tile % per_owner;
-    *mb = owner * p.blocks_per_rank + within / g.tiles_n;
-    *nb = within % g.tiles_n;
+    const int block_seq = tile / g.tiles_n;
+    const int owner = (p.peers.rank + 1 + block_seq % p.peers.world) % p.peers.world;
+    *mb = owner * p.blocks_per_rank + block_seq / p.peers.world;
+    *nb = tile % g.tiles_n;
   }
   __device__ static bool before_load(const Params&, const Problem&, int, uint64_t, const volatile uint32_t*) {
     return true;
@@ -71,24 +71,25 @@ struct ReduceScatterPolicy {
     return p.peers.base[owner] + p.recv_off + (parity * p.peers.world + src) * slot_bytes +
            static_cast<uint64_t>(local_row) * g.N * 2;
   }
-  __device__ static uint8_t* row_ptr(const Params& p, const Problem& g, int row) {
-    return slot(p, g, row / p.rows_per_rank, p.peers.rank, row % p.rows_per_rank);
+  static constexpr bool kSignalsTiles = true;
+  // A 128-row block never straddles two owners, so its rows are contiguous in one slot.
+  __device__ static uint8_t* tile_base(const Params& p, const Problem& g, int mb) {
+    return slot(p, g, mb / p.blocks_per_rank, p.peers.rank, (mb % p.blocks_per_rank) * kBM);
   }
-  __device__ static void tile_done(const Params& p, const Problem& g, int mb, int, int, int lane) {
-    // Make this warp's (possibly remote) stores visible, then count; the warp that completes
-    // the block posts the flag at the owner.
-    __syncwarp();
-    if (lane == 0) {
+  __device__ static int64_t row_pitch(const Params&, const Problem& g) { return static_cast<int64_t>(g.N) * 2; }
+  // Called by the signal warp's lane 0 once all four epilogue warps have stored tile (mb, nb)
+  // (it acquired their mbarrier arrivals, so the fence below covers their stores).  The call
+  // that completes the row block posts the flag at the owner.
+  __device__ static void tile_done(const Params& p, const Problem& g, int mb, int) {
+    ptx::fence_sys();
+    const uint32_t target = p.epoch * static_cast<uint32_t>(g.tiles_n);
+    const uint32_t seen = atomicAdd(p.block_counter + mb, 1u) + 1u;
+    if (seen == target) {
       ptx::fence_sys();
-      const uint32_t target = p.epoch * static_cast<uint32_t>(g.tiles_n) * 4u;
-      const uint32_t seen = atomicAdd(p.block_counter + mb, 1u) + 1u;
-      if (seen == target) {
-        ptx::fence_sys();
-        const int owner = mb / p.blocks_per_rank, local_block = mb % p.blocks_per_rank;
-        uint32_t* flag = reinterpret_cast<uint32_t*>(p.peers.base[owner] + p.flags_off) +
-                         p.peers.rank * p.blocks_per_rank + local_block;
-        ptx::red_release_sys_add(flag, 1u);
-      }
+      const int owner = mb / p.blocks_per_rank, local_block = mb % p.blocks_per_rank;
+      uint32_t* flag = reinterpret_cast<uint32_t*>(p.peers.base[owner] + p.flags_off) +
+                       p.peers.rank * p.blocks_per_rank + local_block;
+      ptx::red_release_sys_add(flag, 1u);
     }
   }
   __device__ static int aux_ctas(const Params&) { return 0; }
@@ -116,19 +117,41 @@ struct ReduceScatterPolicy {
       const int row0 = block * kBM, col0 = nb * kBN;
       const int rows = min(kBM, p.rows_per_rank - row0), cols = min(kBN, g.N - col0);
       const int vec_per_row = cols / 8;                    // 8 bf16 per 16 bytes (N % 8 == 0)
-      for (int i = threadIdx.x; i < rows * vec_per_row; i += blockDim.x) {
-        const int r = row0 + i / vec_per_row, c = col0 + (i % vec_per_row) * 8;
-        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int s = 0; s < world; ++s) {
-          const uint4 raw = ptx::ld_local_v4(slot(p, g, me, s, r) + static_cast<uint64_t>(c) * 2);
-          const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+      // Four vectors per thread and iteration, all slots loaded before the first add, so that
+      // up to 4 * world independent 16-byte loads are in flight per thread.
+      constexpr int kRV = 4;
+      const int total = rows * vec_per_row;
+      for (int i = threadIdx.x; i < total; i += blockDim.x * kRV) {
+        uint4 raw[kRV][kMaxRanks];
+        int r[kRV], c[kRV];
+        bool live[kRV];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            acc[2 * j] += __uint_as_float(w[j] << 16);
-            acc[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u);
-          }
+        for (int u = 0; u < kRV; ++u) {
+          const int idx = i + u * blockDim.x;
+          live[u] = idx < total;
+          r[u] = row0 + idx / vec_per_row;
+          c[u] = col0 + (idx % vec_per_row) * 8;
+#pragma unroll
+          for (int s = 0; s < kMaxRanks; ++s)
+            if (live[u] && s < world)
+              raw[u][s] = ptx::ld_local_v4(slot(p, g, me, s, r[u]) + static_cast<uint64_t>(c[u]) * 2);
         }
-        *reinterpret_cast<uint4*>(p.out + static_cast<int64_t>(r) * p.ldo + c) = pack8_bf16(acc);
+#pragma unroll
+        for (int u = 0; u < kRV; ++u) {
+          if (!live[u]) continue;
+          float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+          for (int s = 0; s < kMaxRanks; ++s) {
+            if (s >= world) break;
+            const uint32_t w[4] = {raw[u][s].x, raw[u][s].y, raw[u][s].z, raw[u][s].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              acc[2 * j] += __uint_as_float(w[j] << 16);
+              acc[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u);
+            }
+          }
+          *reinterpret_cast<uint4*>(p.out + static_cast<int64_t>(r[u]) * p.ldo + c[u]) = pack8_bf16(acc);
+        }
       }
     }
   }
@@ -164,10 +187,12 @@ struct AllGatherPolicy {
     asm volatile("fence.proxy.async.global;" ::: "memory");
     return ok;
   }
-  __device__ static uint8_t* row_ptr(const Params& p, const Problem&, int row) {
-    return reinterpret_cast<uint8_t*>(p.c + static_cast<int64_t>(row) * p.ldc);
+  static constexpr bool kSignalsTiles = false;
+  __device__ static uint8_t* tile_base(const Params& p, const Problem&, int mb) {
+    return reinterpret_cast<uint8_t*>(p.c + static_cast<int64_t>(mb) * kBM * p.ldc);
   }
-  __device__ static void tile_done(const Params&, const Problem&, int, int, int, int) {}
+  __device__ static int64_t row_pitch(const Params& p, const Problem&) { return p.ldc * 2; }
+  __device__ static void tile_done(const Params&, const Problem&, int, int) {}
   __device__ static int aux_ctas(const Params& p) { return p.copy_ctas; }
 
   // Copier CTAs.  CTA 0 first announces "my shard is in place" to every peer.  Then the copiers

@@ -7,6 +7,8 @@
 //   warp 1      MMA issuer: one elected lane issues tcgen05.mma (M128 x N256 x K16) with the
 //               accumulator in tensor memory; two 256-column accumulators alternate so the
 //               epilogue of tile i overlaps the main loop of tile i+1;
+//   warp 6      signal warp (policies that publish per-tile completion): waits until the four
+//               epilogue warps have stored a tile, then fences and posts, off their critical path;
 //   warps 2-5   epilogue: tcgen05.ld the accumulator (each warp owns 32 TMEM lanes = 32 rows),
 //               then hand 32-column row segments to the Policy, which converts and stores
 //               them — to local memory, or straight into a peer GPU's memory for the fused
@@ -27,7 +29,7 @@ namespace gemm {
 
 constexpr int kBM = 128, kBN = 256, kBK = 64, kStages = 4;
 constexpr int kUmmaK = 16;
-constexpr int kThreads = 192;
+constexpr int kThreads = 224;                                  // 7 warps: TMA, MMA, 4 epilogue, signal
 constexpr uint32_t kBytesA = kBM * kBK * 2, kBytesB = kBN * kBK * 2;
 constexpr uint32_t kStageBytes = kBytesA + kBytesB;
 constexpr int kEpiCols = 128;                                   // columns staged per epilogue pass
@@ -47,6 +49,7 @@ enum ErrorCode : uint32_t { kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueW
 struct Pipe {
   uint64_t full[kStages], empty[kStages];
   uint64_t acc_full[2], acc_empty[2];
+  uint64_t stored[2];          // the four epilogue warps have written a tile out
   uint32_t tmem_base;
   uint32_t pad;
 };
@@ -79,7 +82,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { ptx::mbar_init(&pipe.full[s], 1); ptx::mbar_init(&pipe.empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { ptx::mbar_init(&pipe.acc_full[a], 1); ptx::mbar_init(&pipe.acc_empty[a], 4); }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(&pipe.acc_full[a], 1);
+      ptx::mbar_init(&pipe.acc_empty[a], 4);
+      ptx::mbar_init(&pipe.stored[a], 4);
+    }
     ptx::mbar_init_fence();
     ptx::tma_prefetch_desc(&tma_a);
     ptx::tma_prefetch_desc(&tma_b);
@@ -166,6 +173,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         if (ok) ptx::umma_commit(&pipe.acc_full[acc]);  // accumulator complete
       }
     }
+  } else if (warp == 6) {
+    // ---------------------------------------------------------------- signal warp
+    if (Policy::kSignalsTiles && lane == 0) {
+      uint32_t local_tile = 0;
+      for (int tile = cta; tile < num_tiles; tile += num_ctas, ++local_tile) {
+        const uint32_t acc = local_tile & 1u, acc_phase = (local_tile >> 1) & 1u;
+        if (!ptx::mbar_wait(&pipe.stored[acc], acc_phase, deadline, abort_flag)) break;
+        int mb, nb;
+        Policy::tile_coords(p, g, tile, &mb, &nb);
+        Policy::tile_done(p, g, mb, nb);
+      }
+    }
   } else {
     // ---------------------------------------------------------------- epilogue (warps 2..5)
     const int quarter = warp & 3;                      // TMEM lanes [32*quarter, +32)
@@ -180,6 +199,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       if (!ok) { if (lane == 0) raise_error(g, kErrEpilogueWait, 2); break; }
       ptx::tc_fence_after_sync();
       const int row_base = mb * kBM + quarter * 32;
+      uint8_t* const tile_dst = Policy::tile_base(p, g, mb);       // row mb*128, column 0 of the destination
+      const int64_t pitch = Policy::row_pitch(p, g);              // bytes between destination rows
       const uint32_t taddr = tmem_base + acc * kBN + (static_cast<uint32_t>(quarter * 32) << 16);
       // Staging buffer of this warp: 32 rows x 16 chunks of 16 bytes, chunk index XOR-swizzled by
       // the row so that both the row-wise writes and the chunk-wise reads spread over banks.
@@ -204,15 +225,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         for (int it = 0; it < 16; ++it) {
           const int r = it * 2 + (lane >> 4), j = lane & 15;
           const int row = row_base + r, col = nb * kBN + c0 + j * 8;
+          uint8_t* dst = tile_dst + static_cast<int64_t>(quarter * 32 + r) * pitch + static_cast<int64_t>(col) * 2;
           const uint4 val = *reinterpret_cast<const uint4*>(stage_buf + r * (kEpiCols * 2) + ((j ^ (r & 15)) * 16));
-          if (row < g.M && col < g.N) ptx::st_v4(Policy::row_ptr(p, g, row) + static_cast<int64_t>(col) * 2, val);
+          if (row < g.M && col < g.N) ptx::st_v4(dst, val);
         }
         __syncwarp();
       }
       ptx::tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&pipe.acc_empty[acc]);
-      Policy::tile_done(p, g, mb, nb, quarter, lane);
+      if (lane == 0) {
+        ptx::mbar_arrive(&pipe.acc_empty[acc]);
+        if (Policy::kSignalsTiles) ptx::mbar_arrive(&pipe.stored[acc]);   // release: the stores above
+      }
     }
   }
 
@@ -251,11 +275,13 @@ struct StorePolicy {
   __device__ static bool before_load(const Params&, const Problem&, int, uint64_t, const volatile uint32_t*) {
     return true;
   }
-  // Address of column 0 of output row `row` (bf16 elements follow contiguously; N % 8 == 0).
-  __device__ static uint8_t* row_ptr(const Params& p, const Problem&, int row) {
-    return reinterpret_cast<uint8_t*>(p.c + static_cast<int64_t>(row) * p.ldc);
+  static constexpr bool kSignalsTiles = false;
+  // Destination of row mb*128, column 0, and the byte pitch between rows (N % 8 == 0).
+  __device__ static uint8_t* tile_base(const Params& p, const Problem&, int mb) {
+    return reinterpret_cast<uint8_t*>(p.c + static_cast<int64_t>(mb) * kBM * p.ldc);
   }
-  __device__ static void tile_done(const Params&, const Problem&, int, int, int, int) {}
+  __device__ static int64_t row_pitch(const Params& p, const Problem&) { return p.ldc * 2; }
+  __device__ static void tile_done(const Params&, const Problem&, int, int) {}
   __device__ static int aux_ctas(const Params&) { return 0; }
   __device__ static void aux_main(const Params&, const Problem&, int, int, uint64_t, const volatile uint32_t*) {}
   __device__ static void finish(const Params&, const Problem&, int, int, uint64_t, const volatile uint32_t*) {}
