@@ -49,9 +49,8 @@ enum ErrorCode : uint32_t { kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueW
 struct Pipe {
   uint64_t full[kStages], empty[kStages];
   uint64_t acc_full[2], acc_empty[2];
-  uint64_t stored[2];          // the four epilogue warps have written a tile out
   uint32_t tmem_base;
-  uint32_t pad;
+  uint32_t stored_count;       // epilogue-warp completions (4 per tile), monotonic: no phase to alias
 };
 
 __device__ __forceinline__ void raise_error(const Problem& g, uint32_t code, uint32_t role) {
@@ -85,8 +84,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(&pipe.acc_full[a], 1);
       ptx::mbar_init(&pipe.acc_empty[a], 4);
-      ptx::mbar_init(&pipe.stored[a], 4);
     }
+    pipe.stored_count = 0;
     ptx::mbar_init_fence();
     ptx::tma_prefetch_desc(&tma_a);
     ptx::tma_prefetch_desc(&tma_b);
@@ -178,8 +177,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     if (Policy::kSignalsTiles && lane == 0) {
       uint32_t local_tile = 0;
       for (int tile = cta; tile < num_tiles; tile += num_ctas, ++local_tile) {
-        const uint32_t acc = local_tile & 1u, acc_phase = (local_tile >> 1) & 1u;
-        if (!ptx::mbar_wait(&pipe.stored[acc], acc_phase, deadline, abort_flag)) break;
+        // Tile `local_tile` is out when 4 * (local_tile + 1) epilogue warps have reported.
+        const uint32_t want = 4u * (local_tile + 1u);
+        const volatile uint32_t* count = &pipe.stored_count;
+        uint32_t spins = 0;
+        bool ok = true;
+        while (static_cast<int32_t>(*count - want) < 0) {
+          if ((++spins & 255u) == 0u && (*abort_flag || ptx::globaltimer() > deadline)) { ok = false; break; }
+        }
+        if (!ok) break;
+        __threadfence_block();                       // acquire the epilogue warps' stores
         int mb, nb;
         Policy::tile_coords(p, g, tile, &mb, &nb);
         Policy::tile_done(p, g, mb, nb);
@@ -235,7 +242,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       __syncwarp();
       if (lane == 0) {
         ptx::mbar_arrive(&pipe.acc_empty[acc]);
-        if (Policy::kSignalsTiles) ptx::mbar_arrive(&pipe.stored[acc]);   // release: the stores above
+        if (Policy::kSignalsTiles) {                 // release the stores above to the signal warp
+          __threadfence_block();
+          atomicAdd_block(&pipe.stored_count, 1u);
+        }
       }
     }
   }

@@ -34,5 +34,6 @@ def check() -> None:
     code = _native().read_error()
     if code:
         _native().clear_error()
-        role = {0: "TMA producer", 1: "MMA issuer", 2: "epilogue"}.get(code & 0xFF, "?")
+        role = {0: "TMA producer", 1: "MMA issuer", 2: "epilogue", 3: "reducer (peer flag)", 4: "copier (peer shard ready)",
+                5: "copier (peers done reading)"}.get(code & 0xFF, str(code & 0xFF))
         raise RuntimeError(f"tcgen05 GEMM kernel gave up waiting (code {code >> 8}, role {role})")
