@@ -1,0 +1,220 @@
+// All-reduce + residual add + RMSNorm in one kernel (tensor-parallel block epilogue).
+//
+//   h = residual + sum_r x_r          (x_r: this layer's partial output on rank r, bf16)
+//   y = h * rsqrt(mean(h^2) + eps) * gamma
+// Every rank ends with the full y and the updated residual h.
+//
+// x lives in symmetric memory.  Tokens are split over the ranks ("two-shot": a rank reduces
+// its T/W tokens and delivers y and h for them to every rank) unless T is too small to split,
+// in which case every rank reduces every token itself ("one-shot", nothing to deliver).
+// With NVLS the reduction is one multimem.ld_reduce per 16 bytes (the switch sums the ranks'
+// copies, fp32 accumulation) and the delivery one multimem.st; without it the kernel pulls the
+// peers' rows with 16-byte loads and pushes results with plain peer stores.
+// Synchronisation: call-counting flags in symmetric memory ("my x is in place", "I have
+// delivered / finished reading"), bounded waits, error word on timeout.
+// The unfused baseline is NCCL all-reduce + torch add + RMSNorm; the reference has no such op.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "../common/util.h"
+#include "../engine/cuda_driver.h"
+#include "../ptx/multimem.cuh"
+#include "../ptx/sync.cuh"
+#include "gemm_host.h"
+
+namespace pccl {
+namespace gemm {
+
+namespace {
+
+constexpr int kThreadsNorm = 256;
+
+struct NormParams {
+  PeerBases peers;
+  uint8_t* mc_base;          // multicast alias of the heap (null without NVLS)
+  uint64_t x_off, y_off, res_off, flags_off;   // symmetric offsets: x, y, h [T][H] bf16; flags u32[2*world]
+  const __nv_bfloat16* gamma;
+  uint32_t* cta_counter;     // local, monotonic
+  uint32_t* error;
+  int tokens, hidden;
+  int one_shot;
+  float eps;
+  uint32_t epoch;
+  uint64_t timeout_ns;
+};
+
+__device__ __forceinline__ bool wait_ge(const uint32_t* flag, uint32_t want, uint64_t deadline,
+                                        const volatile uint32_t* abort_flag) {
+  uint32_t spins = 0;
+  while (static_cast<int32_t>(ptx::ld_acquire_sys(flag) - want) < 0) {
+    if ((++spins & 63u) == 0u) {
+      if (*abort_flag || ptx::globaltimer() > deadline) return false;
+      __nanosleep(64);
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void unpack8(uint4 v, float* f) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    w[i] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+__global__ void __launch_bounds__(kThreadsNorm) ar_residual_rmsnorm_kernel(const NormParams p) {
+  extern __shared__ float h_row[];            // hidden fp32 values of the current token
+  __shared__ float warp_sums[kThreadsNorm / 32];
+  __shared__ uint32_t s_ok;
+  const int me = p.peers.rank, world = p.peers.world;
+  const volatile uint32_t* abort_flag = p.error;
+  const uint64_t deadline = ptx::globaltimer() + p.timeout_ns;
+  uint32_t* my_flags = reinterpret_cast<uint32_t*>(p.peers.base[me] + p.flags_off);
+
+  // 1. "my x is in place" -> every peer; then wait for every peer's.
+  if (blockIdx.x == 0 && static_cast<int>(threadIdx.x) < world && static_cast<int>(threadIdx.x) != me) {
+    ptx::fence_sys();
+    ptx::red_release_sys_add(reinterpret_cast<uint32_t*>(p.peers.base[threadIdx.x] + p.flags_off) + me, 1u);
+  }
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (static_cast<int>(threadIdx.x) < world && static_cast<int>(threadIdx.x) != me) {
+    if (!wait_ge(my_flags + threadIdx.x, p.epoch, deadline, abort_flag)) { s_ok = 0; atomicCAS(p.error, 0u, 0x601u); }
+  }
+  __syncthreads();
+  if (!s_ok) return;
+
+  // 2. tokens of this rank
+  const int per_rank = p.one_shot ? p.tokens : p.tokens / world;
+  const int first = p.one_shot ? 0 : me * per_rank;
+  const int vecs = p.hidden / 8;
+  const uint64_t row_bytes = static_cast<uint64_t>(p.hidden) * 2;
+  const bool use_mc = p.mc_base != nullptr;
+  uint8_t* self = p.peers.base[me];
+
+  for (int t = first + blockIdx.x; t < first + per_rank; t += gridDim.x) {
+    const uint64_t row = static_cast<uint64_t>(t) * row_bytes;
+    float ss = 0.f;
+    for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+      float acc[8];
+      unpack8(ptx::ld_local_v4(self + p.res_off + row + v * 16), acc);
+      if (use_mc) {
+        float f[8];
+        unpack8(ptx::mm_ld_reduce_add_bf16(p.mc_base + p.x_off + row + v * 16), f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += f[i];
+      } else {
+        uint4 raw[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          if (r < world) raw[r] = r == me ? ptx::ld_local_v4(self + p.x_off + row + v * 16)
+                                          : ptx::ld_peer_v4(p.peers.base[r] + p.x_off + row + v * 16);
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          if (r < world) {
+            float f[8];
+            unpack8(raw[r], f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] += f[i];
+          }
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { h_row[v * 8 + i] = acc[i]; ss += acc[i] * acc[i]; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < kThreadsNorm / 32; ++w) total += warp_sums[w];
+    const float scale = rsqrtf(total / static_cast<float>(p.hidden) + p.eps);
+    for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+      float g[8], hv[8], yv[8];
+      unpack8(*reinterpret_cast<const uint4*>(p.gamma + v * 8), g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { hv[i] = h_row[v * 8 + i]; yv[i] = hv[i] * scale * g[i]; }
+      const uint4 hp = pack8(hv), yp = pack8(yv);
+      if (p.one_shot) {
+        ptx::st_v4(self + p.res_off + row + v * 16, hp);
+        ptx::st_v4(self + p.y_off + row + v * 16, yp);
+      } else if (use_mc) {
+        ptx::mm_st_v4(p.mc_base + p.res_off + row + v * 16, hp);
+        ptx::mm_st_v4(p.mc_base + p.y_off + row + v * 16, yp);
+      } else {
+        for (int i = 0; i < world; ++i) {
+          const int r = (me + i) % world;
+          ptx::st_v4(p.peers.base[r] + p.res_off + row + v * 16, hp);
+          ptx::st_v4(p.peers.base[r] + p.y_off + row + v * 16, yp);
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  // 3. "delivered / done reading" -> every peer, once all CTAs of this rank are through;
+  //    the last CTA then waits for every peer's, so that y and h are complete on return.
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    ptx::fence_sys();
+    const uint32_t done = atomicAdd(p.cta_counter, 1u) + 1u;
+    s_ok = done == p.epoch * gridDim.x ? 2u : 1u;
+  }
+  __syncthreads();
+  if (s_ok != 2u) return;
+  if (static_cast<int>(threadIdx.x) < world && static_cast<int>(threadIdx.x) != me) {
+    ptx::fence_sys();
+    ptx::red_release_sys_add(reinterpret_cast<uint32_t*>(p.peers.base[threadIdx.x] + p.flags_off) + world + me, 1u);
+    if (!wait_ge(my_flags + world + threadIdx.x, p.epoch, deadline, abort_flag)) atomicCAS(p.error, 0u, 0x602u);
+  }
+}
+
+}  // namespace
+
+void ar_residual_rmsnorm(const PeerBases& peers, uint8_t* mc_base, uint64_t x_off, uint64_t y_off, uint64_t res_off,
+                         uint64_t flags_off, const void* gamma, uint32_t* cta_counter, int tokens, int hidden,
+                         float eps, uint32_t epoch, cudaStream_t stream, int ctas, uint64_t timeout_ms) {
+  PCCL_CHECK(hidden % 8 == 0 && hidden <= 16384, "AR+RMSNorm: hidden must be a multiple of 8, at most 16384");
+  PCCL_CHECK(epoch >= 1, "AR+RMSNorm: epoch counts calls from 1");
+  NormParams p{};
+  p.peers = peers;
+  p.mc_base = mc_base;
+  p.x_off = x_off; p.y_off = y_off; p.res_off = res_off; p.flags_off = flags_off;
+  p.gamma = static_cast<const __nv_bfloat16*>(gamma);
+  p.cta_counter = cta_counter;
+  p.error = error_word();
+  p.tokens = tokens; p.hidden = hidden;
+  // Splitting tokens pays once every rank has at least a few of them.
+  p.one_shot = (peers.world == 1 || tokens % peers.world != 0 || tokens / peers.world < 4) ? 1 : 0;
+  p.eps = eps;
+  p.epoch = epoch;
+  p.timeout_ns = timeout_ms * 1000000ull;
+  const int mine = p.one_shot ? tokens : tokens / peers.world;
+  int sms = 0, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int grid = ctas > 0 ? ctas : (mine < 2 * sms ? mine : 2 * sms);
+  if (grid < 1) grid = 1;
+  // The grid size is part of the completion count: it must not change between calls of one
+  // operator instance (the Python wrapper fixes tokens per instance).
+  const size_t smem = static_cast<size_t>(hidden) * sizeof(float);
+  if (smem > 48 * 1024)
+    PCCL_CUDA(cudaFuncSetAttribute(ar_residual_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(smem)));
+  ar_residual_rmsnorm_kernel<<<grid, kThreadsNorm, smem, stream>>>(p);
+  PCCL_CUDA(cudaGetLastError());
+}
+
+}  // namespace gemm
+}  // namespace pccl

@@ -80,6 +80,24 @@ void bind_fused_ops(py::module_& m) {
         },
         py::arg("gathered_off"), py::arg("m"), py::arg("k"), py::arg("w"), py::arg("out"), py::arg("flags_off"),
         py::arg("ready"), py::arg("epoch"), py::arg("copy_ctas") = 20, py::arg("ctas") = 0);
+  // Fused all-reduce + residual + RMSNorm over symmetric buffers.
+  f.def("ar_residual_rmsnorm",
+        [](int64_t x_off, int64_t y_off, int64_t res_off, int64_t flags_off, const torch::Tensor& gamma,
+           torch::Tensor& cta_counter, int64_t tokens, int64_t hidden, double eps, int64_t epoch, bool use_nvls,
+           int ctas) {
+          TORCH_CHECK(gamma.is_cuda() && gamma.scalar_type() == torch::kBFloat16 && gamma.is_contiguous() &&
+                          gamma.numel() == hidden, "gamma must be a contiguous bf16 CUDA vector of `hidden` elements");
+          Engine& e = Engine::instance();
+          uint8_t* mc = (use_nvls && e.nvlsActive()) ? e.context().heap().mc_base() : nullptr;
+          gemm::ar_residual_rmsnorm(peer_bases(), mc, static_cast<uint64_t>(x_off), static_cast<uint64_t>(y_off),
+                                    static_cast<uint64_t>(res_off), static_cast<uint64_t>(flags_off),
+                                    gamma.data_ptr(), as_u32(cta_counter, 1, "cta_counter"),
+                                    static_cast<int>(tokens), static_cast<int>(hidden), static_cast<float>(eps),
+                                    static_cast<uint32_t>(epoch), c10::cuda::getCurrentCUDAStream().stream(), ctas);
+        },
+        py::arg("x_off"), py::arg("y_off"), py::arg("res_off"), py::arg("flags_off"), py::arg("gamma"),
+        py::arg("cta_counter"), py::arg("tokens"), py::arg("hidden"), py::arg("eps"), py::arg("epoch"),
+        py::arg("use_nvls") = true, py::arg("ctas") = 0);
   // Device-side error word of the GEMM family (0 = ok); synchronises.
   f.def("read_error", &gemm::read_error);
   f.def("clear_error", &gemm::clear_error);

@@ -47,5 +47,12 @@ void all_gather_gemm(const PeerBases& peers, uint64_t gathered_off, int M, int K
                      uint64_t flags_off, uint32_t* ready, void* out, int64_t ldc, uint32_t epoch,
                      cudaStream_t stream, int copy_ctas = 20, int ctas = 0, uint64_t timeout_ms = 2000);
 
+// Fused all-reduce + residual add + RMSNorm.  x, y and the residual h are [tokens][hidden] bf16
+// at the given symmetric-heap offsets on every rank; flags_off: symmetric u32[2 * world] (zeroed
+// once); cta_counter: local zero-initialised u32; mc_base: multicast alias of the heap or null.
+void ar_residual_rmsnorm(const PeerBases& peers, uint8_t* mc_base, uint64_t x_off, uint64_t y_off, uint64_t res_off,
+                         uint64_t flags_off, const void* gamma, uint32_t* cta_counter, int tokens, int hidden,
+                         float eps, uint32_t epoch, cudaStream_t stream, int ctas = 0, uint64_t timeout_ms = 2000);
+
 }  // namespace gemm
 }  // namespace pccl

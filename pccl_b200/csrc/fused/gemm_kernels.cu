@@ -170,6 +170,8 @@ void all_gather_gemm(const PeerBases& peers, uint64_t gathered_off, int M, int K
   p.rows_per_rank = M / peers.world;
   p.blocks_per_rank = p.rows_per_rank / kBM;
   p.copy_ctas = peers.world > 1 ? copy_ctas : 0;
+  const int remote_blocks = (peers.world - 1) * p.blocks_per_rank;
+  p.copy_parts = p.copy_ctas > remote_blocks ? (p.copy_ctas + remote_blocks - 1) / remote_blocks : 1;
   p.epoch = epoch;
   MatrixDesc a{peers.base[peers.rank] + gathered_off, M, K, K};
   const int sms = sm_count();

@@ -168,6 +168,7 @@ struct AllGatherPolicy {
     __nv_bfloat16* c;           // local result [M][N]
     int64_t ldc;
     int rows_per_rank, blocks_per_rank, copy_ctas;
+    int copy_parts;             // copier CTAs that share one 128-row block (keeps all copiers busy for small M)
     uint32_t epoch;
   };
 
@@ -182,7 +183,7 @@ struct AllGatherPolicy {
   __device__ static bool before_load(const Params& p, const Problem&, int mb, uint64_t deadline,
                                      const volatile uint32_t* abort_flag) {
     if (mb / p.blocks_per_rank == p.peers.rank) return true;          // the local shard is already there
-    const bool ok = wait_flag_ge(p.ready + mb, p.epoch, deadline, abort_flag);
+    const bool ok = wait_flag_ge(p.ready + mb, p.epoch * static_cast<uint32_t>(p.copy_parts), deadline, abort_flag);
     // The rows were written by generic-proxy stores of other CTAs; TMA reads through the async proxy.
     asm volatile("fence.proxy.async.global;" ::: "memory");
     return ok;
@@ -212,9 +213,11 @@ struct AllGatherPolicy {
     }
     const uint64_t row_bytes = static_cast<uint64_t>(g.K) * 2;
     const int remote_blocks = (world - 1) * p.blocks_per_rank;
-    for (int item = cta; item < remote_blocks; item += num_ctas) {
-      const int src = (me + 1 + item / p.blocks_per_rank) % world;
-      const int mb = src * p.blocks_per_rank + item % p.blocks_per_rank;
+    const int items = remote_blocks * p.copy_parts;
+    for (int item = cta; item < items; item += num_ctas) {
+      const int block_item = item / p.copy_parts, part = item % p.copy_parts;
+      const int src = (me + 1 + block_item / p.blocks_per_rank) % world;
+      const int mb = src * p.blocks_per_rank + block_item % p.blocks_per_rank;
       if (threadIdx.x == 0) {
         ok_flag = wait_flag_ge(my_flags + src, p.epoch, deadline, abort_flag) ? 1u : 0u;
         if (!ok_flag) raise_error(g, kErrPolicyWait, 4);
@@ -225,7 +228,11 @@ struct AllGatherPolicy {
       const uint8_t* from = p.peers.base[src] + off;
       uint8_t* to = p.peers.base[me] + off;
       const uint64_t rows_here = min(static_cast<int>(kBM), g.M - mb * kBM);
-      const uint64_t vecs = rows_here * row_bytes / 16;
+      const uint64_t block_vecs = rows_here * row_bytes / 16;
+      const uint64_t per_part = (block_vecs + p.copy_parts - 1) / p.copy_parts;
+      from += part * per_part * 16;
+      to += part * per_part * 16;
+      const uint64_t vecs = part * per_part >= block_vecs ? 0 : min(per_part, block_vecs - part * per_part);
       constexpr int kU = 16;                               // 16-byte loads in flight per thread
       for (uint64_t v = threadIdx.x; v < vecs; v += static_cast<uint64_t>(blockDim.x) * kU) {
         uint4 t[kU];
@@ -239,16 +246,16 @@ struct AllGatherPolicy {
       __syncthreads();
       if (threadIdx.x == 0) {
         ptx::fence_gpu();
-        ptx::st_release_sys(p.ready + mb, p.epoch);
-        // One "done" count per block read, posted at the shard's owner.
+        ptx::red_release_gpu_add(p.ready + mb, 1u);
+        // One "done" count per part read, posted at the shard's owner.
         uint32_t* done = reinterpret_cast<uint32_t*>(p.peers.base[src] + p.flags_off) + world + me;
         ptx::red_release_sys_add(done, 1u);
       }
     }
     if (cta == 0) {
-      // Every peer posts blocks_per_rank "done" counts per call.
+      // Every peer posts blocks_per_rank * copy_parts "done" counts per call.
       if (static_cast<int>(threadIdx.x) < world && static_cast<int>(threadIdx.x) != me) {
-        const uint32_t want = p.epoch * static_cast<uint32_t>(p.blocks_per_rank);
+        const uint32_t want = p.epoch * static_cast<uint32_t>(p.blocks_per_rank * p.copy_parts);
         if (!wait_flag_ge(my_flags + world + threadIdx.x, want, deadline, abort_flag))
           raise_error(g, kErrPolicyWait, 5);
       }

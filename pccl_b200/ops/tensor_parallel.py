@@ -88,3 +88,36 @@ class AllGatherGemm:
         _native().all_gather_gemm(self.gathered.heap_offset, self.m, self.k, w, out, self.flags.heap_offset,
                                   self.ready, self.epoch, self.copy_ctas, ctas)
         return out
+
+
+class AllReduceResidualRMSNorm:
+    """``h = residual + all_reduce(x); y = rmsnorm(h) * gamma`` in one kernel.
+
+    ``self.x`` (this rank's partial, written by the caller), ``self.residual`` (read and
+    updated in place) and ``self.y`` (result) are ``[tokens, hidden]`` bf16 tensors in
+    symmetric memory owned by the operator.
+    """
+
+    def __init__(self, tokens: int, hidden: int, eps: float = 1e-5, group=None, use_nvls: bool = True):
+        self.engine = _engine.get_engine()
+        self.world, self.rank = self.engine.world, self.engine.rank
+        self.tokens, self.hidden, self.eps, self.use_nvls = tokens, hidden, eps, use_nvls
+        self.x = self.engine.empty_symmetric((tokens, hidden), torch.bfloat16)
+        self.y = self.engine.empty_symmetric((tokens, hidden), torch.bfloat16)
+        self.residual = self.engine.empty_symmetric((tokens, hidden), torch.bfloat16)
+        self.flags = self.engine.empty_symmetric((2 * self.world,), torch.int32)
+        self.flags.zero_()
+        self.cta_counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self.epoch = 0
+        _fence(group)
+
+    def __call__(self, gamma: torch.Tensor, x: torch.Tensor = None, residual: torch.Tensor = None, ctas: int = 0):
+        if x is not None and x.data_ptr() != self.x.data_ptr():
+            self.x.copy_(x)
+        if residual is not None and residual.data_ptr() != self.residual.data_ptr():
+            self.residual.copy_(residual)
+        self.epoch += 1
+        _native().ar_residual_rmsnorm(self.x.heap_offset, self.y.heap_offset, self.residual.heap_offset,
+                                      self.flags.heap_offset, gamma, self.cta_counter, self.tokens, self.hidden,
+                                      self.eps, self.epoch, self.use_nvls, ctas)
+        return self.y, self.residual

@@ -121,6 +121,33 @@ def main():
                                        msg=lambda t: f"ag_gemm {m}x{n}x{k} call {call} rank {rank}: {t}")
         report["checked"] += 1
 
+    # ---- all-reduce + residual + RMSNorm (one-shot for tiny token counts, two-shot otherwise) ----
+    from pccl_b200.ops import AllReduceResidualRMSNorm
+    hidden = 4096
+    for tokens in (1, 128, 1024):
+        for use_nvls in (True, False):
+            gen = torch.Generator(device="cuda").manual_seed(100 + rank)
+            xp = torch.randn(tokens, hidden, device="cuda", generator=gen).to(torch.bfloat16)
+            gen0 = torch.Generator(device="cuda").manual_seed(5)          # identical on every rank
+            res0 = torch.randn(tokens, hidden, device="cuda", generator=gen0).to(torch.bfloat16)
+            gamma = (1 + 0.1 * torch.randn(hidden, device="cuda", generator=gen0)).to(torch.bfloat16)
+            total = xp.float().clone()
+            dist.all_reduce(total)
+            h_ref = total + res0.float()
+            y_ref = h_ref * torch.rsqrt(h_ref.pow(2).mean(-1, keepdim=True) + 1e-5) * gamma.float()
+            op = AllReduceResidualRMSNorm(tokens, hidden, use_nvls=use_nvls)
+            for call in range(2):
+                op.x.copy_(xp)
+                op.residual.copy_(res0)
+                y, h = op(gamma)
+                torch.cuda.synchronize()
+                gemm.check()
+                torch.testing.assert_close(h.float(), h_ref, atol=0.06, rtol=2e-2,
+                                           msg=lambda t: f"ar_rmsnorm h T={tokens} nvls={use_nvls} rank {rank}: {t}")
+                torch.testing.assert_close(y.float(), y_ref, atol=0.06, rtol=2e-2,
+                                           msg=lambda t: f"ar_rmsnorm y T={tokens} nvls={use_nvls} rank {rank}: {t}")
+            report["checked"] += 1
+
     torch.cuda.synchronize()
     dist.barrier()
     if rank == 0:
