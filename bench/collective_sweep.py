@@ -1,0 +1,216 @@
+"""Collective bandwidth / latency sweep against NCCL.
+
+Multi-GPU (one process per GPU):
+
+    python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 bench/collective_sweep.py \
+        --collectives allreduce,allgather,reduce_scatter --dtypes fp32,bf16 \
+        --min-bytes 1K --max-bytes 1G --algos auto,ring,rhd,tree,oneshot,twoshot,nvls --channels auto
+
+Single GPU (N virtual ranks in one cooperative launch, peer traffic through HBM):
+
+    python bench/collective_sweep.py --virtual-ranks 2 --max-bytes 256M --algos twoshot
+
+Per (collective, dtype, size, algorithm, channels) one JSON line: device time (CUDA events around
+`--iters` back-to-back calls, max over ranks), algorithm and bus bandwidth
+(bus = alg * 2(N-1)/N for all-reduce, alg * (N-1)/N otherwise), the NCCL time for the same call
+(defaults, NVLS allowed, no clone in the timed region), and the ratio.  Messages smaller than
+the 126 MB L2 are timed L2-warm (like NCCL's own tests); the JSON says so.
+The reference's sweep is tests/bench_algo_comparison.py (rank-0 timing, host sync per call).
+"""
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+DTYPES = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}
+
+
+def parse_size(text: str) -> int:
+    mult = {"K": 1 << 10, "M": 1 << 20, "G": 1 << 30}
+    return int(text[:-1]) * mult[text[-1].upper()] if text[-1].upper() in mult else int(text)
+
+
+def sizes(lo: int, hi: int):
+    s = lo
+    while s <= hi:
+        yield s
+        s *= 2
+
+
+def bus_factor(kind: str, n: int) -> float:
+    return 2.0 * (n - 1) / n if kind == "allreduce" else (n - 1) / n
+
+
+def timed_loop(fn, iters, sync, barrier=None):
+    for _ in range(3):
+        fn()
+    sync()
+    if barrier:
+        barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(iters):
+        fn()
+    stop.record()
+    sync()
+    return start.elapsed_time(stop) / iters
+
+
+def run_multi(args):
+    import torch.distributed as dist
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    os.environ.setdefault("PCCL_BUFFER_SIZE", str(max(2 << 30, 2 * args.max_bytes)))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+    import pccl_b200.parallel as pp
+    engine = pp.init()
+
+    def reduce_max(ms):
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    for kind in args.collectives:
+        for dname in args.dtypes:
+            dtype = DTYPES[dname]
+            esize = torch.empty((), dtype=dtype).element_size()
+            for nbytes in sizes(args.min_bytes, args.max_bytes):
+                numel = max(world * 8, nbytes // esize // (world * 8) * (world * 8))
+                full = pp.working_tensor(numel, dtype)
+                shard = numel // world
+                x_shard = torch.randn(shard, device="cuda").to(dtype)
+                out_shard = torch.empty(shard, device="cuda", dtype=dtype)
+                nccl_buf = torch.randn(numel, device="cuda").to(dtype)
+                nccl_out = torch.empty_like(nccl_buf)
+                iters = args.iters if nbytes <= (64 << 20) else max(3, args.iters // 4)
+
+                def nccl_call():
+                    if kind == "allreduce":
+                        dist.all_reduce(nccl_buf)
+                    elif kind == "allgather":
+                        dist.all_gather_into_tensor(nccl_out, x_shard)
+                    elif kind == "reduce_scatter":
+                        dist.reduce_scatter_tensor(out_shard, nccl_buf)
+                    else:
+                        dist.all_to_all_single(nccl_out, nccl_buf)
+
+                nccl_ms = reduce_max(timed_loop(nccl_call, iters, torch.cuda.synchronize, dist.barrier))
+                for algo in args.algos:
+                    allowed = {"allreduce": ("auto", "ring", "rhd", "tree", "oneshot", "twoshot", "nvls"),
+                               "allgather": ("auto", "ring", "rhd", "twoshot", "nvls"),
+                               "reduce_scatter": ("auto", "ring", "rhd", "twoshot", "nvls"),
+                               "alltoall": ("auto", "ring", "twoshot")}[kind]
+                    if algo not in allowed:
+                        continue
+                    if algo == "oneshot" and nbytes > (4 << 20):
+                        continue
+                    if algo in ("rhd", "tree") and world & (world - 1):
+                        continue
+                    for ch in args.channels:
+                        forced_algo = None if algo == "auto" else algo
+                        forced_ch = None if ch == "auto" else int(ch)
+                        try:
+                            if kind == "allreduce":
+                                name = pp.ensure_plan(kind, numel, dtype, forced_algo, forced_ch)
+                                call = lambda: pp.all_reduce(full, algorithm=forced_algo, channels=forced_ch, async_op=True)
+                            elif kind == "allgather":
+                                name = pp.ensure_plan(kind, numel, dtype, forced_algo, forced_ch)
+                                mine = full[rank * shard:(rank + 1) * shard]
+                                call = lambda: pp.all_gather(full, mine, algorithm=forced_algo, channels=forced_ch)
+                            elif kind == "reduce_scatter":
+                                name = pp.ensure_plan(kind, numel, dtype, forced_algo, forced_ch)
+                                mine = full[rank * shard:(rank + 1) * shard]
+                                call = lambda: pp.reduce_scatter(mine, full, algorithm=forced_algo, channels=forced_ch)
+                            else:
+                                name = pp.ensure_plan(kind, numel, dtype, forced_algo or "twoshot", forced_ch)
+                                call = lambda: pp.all_to_all(nccl_out, full, algorithm=forced_algo or "twoshot", channels=forced_ch)
+                        except Exception as err:  # noqa: BLE001
+                            if rank == 0:
+                                print(json.dumps({"collective": kind, "algo": algo, "bytes": nbytes, "skipped": str(err)[:120]}))
+                            continue
+                        ms = reduce_max(timed_loop(call, iters, lambda: pp.synchronize(name), dist.barrier))
+                        if rank == 0:
+                            _, real_algo, real_ch = pp.registered_plans()[name]
+                            alg = numel * esize / (ms * 1e-3) / 1e9
+                            print(json.dumps({
+                                "collective": kind, "dtype": dname, "bytes": numel * esize, "world": world,
+                                "algo": real_algo, "requested": algo, "channels": real_ch,
+                                "nvls": bool(engine.nvls_active()), "us": round(ms * 1e3, 2),
+                                "algbw_gbs": round(alg, 2), "busbw_gbs": round(alg * bus_factor(kind, world), 2),
+                                "nccl_us": round(nccl_ms * 1e3, 2), "vs_nccl": round(nccl_ms / ms, 3),
+                                "l2": "cold (message > L2)" if numel * esize > (126 << 20) else "warm",
+                                "in_place": kind != "alltoall"}), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def run_virtual(args):
+    from pccl_b200 import Compiler, engine_c
+    from pccl_b200.dsl.algorithms import ALGORITHMS
+    torch.cuda.set_device(0)
+    world = args.virtual_ranks
+    cluster = engine_c.LocalCluster(world, 0, 2 * args.max_bytes + (16 << 20))
+    names = {"fp32": "float32", "bf16": "bfloat16", "fp16": "float16"}
+    for kind in args.collectives:
+        for dname in args.dtypes:
+            dtype = DTYPES[dname]
+            esize = torch.empty((), dtype=dtype).element_size()
+            for nbytes in sizes(args.min_bytes, args.max_bytes):
+                numel = max(world * 8, nbytes // esize // (world * 8) * (world * 8))
+                for algo in args.algos:
+                    if algo == "auto":
+                        algo = "twoshot"
+                    for ch in args.channels:
+                        channels = 1 if ch == "auto" else int(ch)
+                        try:
+                            plans = [Compiler().compile_to_json(getattr(ALGORITHMS[algo](), "build_" + kind)(
+                                r, world, numel, names[dname], "sm", channels)) for r in range(world)]
+                            name = f"{kind}_{algo}_{dname}_{numel}_{channels}"
+                            cluster.regOp(name, plans)
+                        except Exception as err:  # noqa: BLE001
+                            print(json.dumps({"collective": kind, "algo": algo, "bytes": nbytes, "skipped": str(err)[:120]}))
+                            continue
+                        in_n = numel // world if kind == "allgather" else numel
+                        out_n = numel // world if kind == "reduce_scatter" else numel
+                        xs = [torch.randn(in_n, device="cuda").to(dtype) for _ in range(world)]
+                        outs = [torch.empty(out_n, device="cuda", dtype=dtype) for _ in range(world)]
+                        iters = args.iters if nbytes <= (64 << 20) else max(3, args.iters // 4)
+                        ms = timed_loop(lambda: cluster.exeOp(name, xs, outs), iters, torch.cuda.synchronize)
+                        alg = numel * esize / (ms * 1e-3) / 1e9
+                        print(json.dumps({"collective": kind, "dtype": dname, "bytes": numel * esize,
+                                          "virtual_ranks": world, "algo": algo, "channels": channels,
+                                          "ctas_per_rank": int(cluster.opInfo(name, 0)["ctas"]),
+                                          "us": round(ms * 1e3, 2), "algbw_gbs": round(alg, 2),
+                                          "busbw_gbs": round(alg * bus_factor(kind, world), 2),
+                                          "note": "one GPU, staged in/out copies included"}), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--collectives", default="allreduce")
+    ap.add_argument("--dtypes", default="fp32")
+    ap.add_argument("--min-bytes", default="1K")
+    ap.add_argument("--max-bytes", default="512M")
+    ap.add_argument("--algos", default="auto")
+    ap.add_argument("--channels", default="auto")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--virtual-ranks", type=int, default=0)
+    args = ap.parse_args()
+    args.collectives = args.collectives.split(",")
+    args.dtypes = args.dtypes.split(",")
+    args.algos = args.algos.split(",")
+    args.channels = args.channels.split(",")
+    args.min_bytes, args.max_bytes = parse_size(args.min_bytes), parse_size(args.max_bytes)
+    if args.virtual_ranks:
+        run_virtual(args)
+    else:
+        run_multi(args)
+
+
+if __name__ == "__main__":
+    main()
