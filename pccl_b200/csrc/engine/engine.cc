@@ -174,6 +174,20 @@ void RankContext::upload(RegisteredOp& op) {
   if (op.d_program == nullptr) PCCL_CUDA(cudaMalloc(reinterpret_cast<void**>(&op.d_program), sizeof(RankProgram)));
   PCCL_CUDA(cudaMemcpy(op.d_program, &P, sizeof P, cudaMemcpyHostToDevice));
 
+  // Copy-engine executor: plans that ask for it (ce.copy operations) or PCCL_EXECUTOR=ce.
+  op.ce.reset();
+  const bool want_ce = op.plan.has_ce_ops || Environs::get("PCCL_EXECUTOR") == "ce";
+  if (want_ce) {
+    bool peers_ready = true;
+    for (int r = 0; r < world_; ++r) peers_ready &= heap_.has_peer(r);
+    if (!CeSchedule::supports(lp)) {
+      PCCL_LOG_WARN("operation '" << op.name << "' has cross-chain dependencies; staying on the SM executor");
+    } else if (peers_ready) {
+      op.ce = std::make_unique<CeSchedule>();
+      op.ce->build(lp, P, static_cast<uint64_t>(Environs::get_int("PCCL_CE_MIN_BYTES", 64 << 10)));
+    }
+  }
+  op.stats.copy_engine = op.ce != nullptr;
   op.stats.algorithm = op.plan.algorithm;
   op.stats.collective = op.plan.collective_type;
   op.stats.chains = P.num_chains;
@@ -266,6 +280,7 @@ void RankContext::check_status(const std::string& op_name) {
 void RankContext::reset_op_counters(RegisteredOp& op) {
   const size_t counters = std::max<size_t>(1, op.lowered.chains.size());
   PCCL_CUDA(cudaMemset(op.chain_sync, 0, 2 * counters * sizeof(uint32_t)));
+  if (op.ce) op.ce->reset_counters();
   op.launch_index = 0;
 }
 
@@ -367,10 +382,14 @@ void Engine::exeOp(const std::string& name, const void* in, size_t in_bytes, voi
   }
   {
     NvtxRange range("execute");
-    LaunchParams lp{op.d_program, op.launch_index};
-    LaunchConfig cfg{std::max<uint32_t>(1, op.lowered.total_ctas), op.threads, 1, false};
-    const int err = launch_plan_interp(lp, cfg, stream);
-    PCCL_CHECK(err == 0, "kernel launch failed: " << cudaGetErrorString(static_cast<cudaError_t>(err)));
+    if (op.ce) {
+      op.ce->run(op.host_program.data, rank_, op.launch_index, stream);
+    } else {
+      LaunchParams lp{op.d_program, op.launch_index};
+      LaunchConfig cfg{std::max<uint32_t>(1, op.lowered.total_ctas), op.threads, 1, false};
+      const int err = launch_plan_interp(lp, cfg, stream);
+      PCCL_CHECK(err == 0, "kernel launch failed: " << cudaGetErrorString(static_cast<cudaError_t>(err)));
+    }
     ++op.launch_index;
   }
   {
@@ -480,6 +499,7 @@ std::string Engine::statsJson() {
     o.set("ctas", static_cast<int64_t>(s.ctas));
     o.set("steps", static_cast<int64_t>(s.steps));
     o.set("multicast", s.multicast);
+    o.set("copy_engine", s.copy_engine);
     all.set(kv.first, o);
   }
   return all.dump();

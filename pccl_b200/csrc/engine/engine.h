@@ -19,6 +19,7 @@
 
 #include "../common/fd_socket.h"
 #include "../common/json.h"
+#include "../executors/ce/ce_executor.h"
 #include "heap.h"
 #include "plan.h"
 
@@ -43,6 +44,7 @@ struct RegisteredOp {
   uint32_t* chain_progress = nullptr;
   uint32_t launch_index = 0;
   uint32_t threads = 512;
+  std::unique_ptr<CeSchedule> ce;       // set when the copy-engine executor runs this operation
   OpStats stats;
 };
 

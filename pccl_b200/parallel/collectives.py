@@ -73,7 +73,7 @@ def _plan_name(kind: str, algorithm: str, dtype: str, numel: int, channels: int)
 
 
 def ensure_plan(kind: str, numel: int, dtype: torch.dtype, algorithm: Optional[str] = None,
-                channels: Optional[int] = None, reduce_op: str = "sum") -> str:
+                channels: Optional[int] = None, reduce_op: str = "sum", executor: Optional[str] = None) -> str:
     """Compile + register (once) the plan for this collective; returns its name."""
     world, rank = _state["world"], _state["rank"]
     dtype_name = _DTYPE_NAME[dtype]
@@ -95,12 +95,13 @@ def ensure_plan(kind: str, numel: int, dtype: torch.dtype, algorithm: Optional[s
     # Every channel's slice must split evenly over the ranks, in 16-byte units where possible.
     while channels > 1 and numel % (channels * world):
         channels //= 2
-    name = _plan_name(kind, algorithm, dtype_name, numel, channels) + ("" if reduce_op == "sum" else "_" + reduce_op)
+    name = _plan_name(kind, algorithm, dtype_name, numel, channels) + ("" if reduce_op == "sum" else "_" + reduce_op) \
+        + ("" if executor in (None, "sm") else "_" + executor)
     if name in _state["registered"]:
         return name
     template = ALGORITHMS[algorithm]()
-    executor = "multimem" if algorithm == "nvls" else "sm"
-    graph = getattr(template, "build_" + kind)(rank, world, numel, dtype_name, executor, channels)
+    plan_executor = executor or ("multimem" if algorithm == "nvls" else "sm")
+    graph = getattr(template, "build_" + kind)(rank, world, numel, dtype_name, plan_executor, channels)
     if reduce_op != "sum":
         for node in graph.nodes.values():
             if hasattr(node, "reduce_op"):
@@ -141,15 +142,20 @@ def reduce_scatter(output: torch.Tensor, input: torch.Tensor, op: str = "sum",
 
 
 def all_gather(output: torch.Tensor, input: torch.Tensor, algorithm: Optional[str] = None,
-               channels: Optional[int] = None) -> torch.Tensor:
-    name = ensure_plan("allgather", output.numel(), output.dtype, algorithm, channels)
+               channels: Optional[int] = None, executor: Optional[str] = None) -> torch.Tensor:
+    """``executor="ce"`` moves the shards with the copy engines (``algorithm`` twoshot)."""
+    if executor == "ce":
+        algorithm = "twoshot"
+    name = ensure_plan("allgather", output.numel(), output.dtype, algorithm, channels, executor=executor)
     _engine.execute_operation(name, input, output)
     return output
 
 
 def all_to_all(output: torch.Tensor, input: torch.Tensor, algorithm: Optional[str] = None,
-               channels: Optional[int] = None) -> torch.Tensor:
-    name = ensure_plan("alltoall", input.numel(), input.dtype, algorithm or "twoshot", channels)
+               channels: Optional[int] = None, executor: Optional[str] = None) -> torch.Tensor:
+    if executor == "ce":
+        algorithm = "twoshot"
+    name = ensure_plan("alltoall", input.numel(), input.dtype, algorithm or "twoshot", channels, executor=executor)
     _engine.execute_operation(name, input, output)
     return output
 

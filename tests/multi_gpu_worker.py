@@ -79,6 +79,26 @@ def main():
                 assert torch.equal(got, want), f"alltoall {algo} {dtype} n={numel}"
                 report["checked"] += 1
 
+    # copy-engine executor: same results, data moved by cudaMemcpyAsync on per-channel streams
+    numel = world * (1 << 18)
+    x = torch.randn(numel, device="cuda", generator=torch.Generator(device="cuda").manual_seed(50 + rank))
+    shard = numel // world
+    expect = torch.empty(numel, device="cuda")
+    dist.all_gather_into_tensor(expect, x[:shard].contiguous())
+    full = torch.zeros(numel, device="cuda")
+    for channels in (1, 4):
+        full.zero_()
+        pp.all_gather(full, x[:shard].contiguous(), channels=channels, executor="ce")
+        assert torch.equal(full, expect), f"ce allgather c{channels}"
+    want = torch.empty(numel, device="cuda")
+    dist.all_to_all_single(want, x)
+    got = torch.empty(numel, device="cuda")
+    pp.all_to_all(got, x, channels=2, executor="ce")
+    assert torch.equal(got, want), "ce alltoall"
+    ce_ops = [n for n, st in engine.stats().items() if st.get("copy_engine")]
+    assert len(ce_ops) >= 3, f"copy-engine executor not used: {ce_ops}"
+    report["copy_engine_ops"] = len(ce_ops)
+
     # max / avg through the API
     x = torch.randn(world * 4096, device="cuda", generator=torch.Generator(device="cuda").manual_seed(rank))
     ref = x.clone(); dist.all_reduce(ref, op=dist.ReduceOp.MAX)
