@@ -98,6 +98,91 @@ void bind_fused_ops(py::module_& m) {
         py::arg("x_off"), py::arg("y_off"), py::arg("res_off"), py::arg("flags_off"), py::arg("gamma"),
         py::arg("cta_counter"), py::arg("tokens"), py::arg("hidden"), py::arg("eps"), py::arg("epoch"),
         py::arg("use_nvls") = true, py::arg("ctas") = 0);
+  // MoE router on its own: top-2 expert indices, renormalised gates, the row each choice claims
+  // in its expert's batch, and the per-expert token counts.  scratch: int32[experts + 1].
+  f.def("moe_route",
+        [](const torch::Tensor& x, const torch::Tensor& wg, torch::Tensor& scratch, torch::Tensor& topk_idx,
+           torch::Tensor& topk_gate, torch::Tensor& topk_slot, torch::Tensor& counts) {
+          const gemm::MatrixDesc dx = as_matrix(x, "x"), dg = as_matrix(wg, "wg");
+          TORCH_CHECK(x.is_contiguous() && wg.is_contiguous() && dx.cols == dg.cols, "x / wg must be contiguous [*, hidden]");
+          TORCH_CHECK(topk_gate.is_cuda() && topk_gate.scalar_type() == torch::kFloat32 && topk_gate.is_contiguous() &&
+                          topk_gate.numel() >= 2 * dx.rows, "topk_gate must be float32 [tokens, 2]");
+          gemm::PeerBases self{};
+          self.rank = 0;
+          self.world = 1;
+          gemm::MoeBuffers none{};
+          gemm::moe_route_dispatch(self, none, x.data_ptr(), wg.data_ptr(), dx.rows, dx.cols, dg.rows,
+                                   as_u32(scratch, dg.rows + 1, "scratch"),
+                                   reinterpret_cast<int32_t*>(as_u32(topk_idx, 2 * dx.rows, "topk_idx")),
+                                   topk_gate.data_ptr<float>(),
+                                   reinterpret_cast<int32_t*>(as_u32(topk_slot, 2 * dx.rows, "topk_slot")),
+                                   as_u32(counts, dg.rows, "counts"), false, 1,
+                                   c10::cuda::getCurrentCUDAStream().stream());
+        },
+        py::arg("x"), py::arg("wg"), py::arg("scratch"), py::arg("topk_idx"), py::arg("topk_gate"),
+        py::arg("topk_slot"), py::arg("counts"));
+  // Expert-parallel MoE feed-forward: route + dispatch, expert GEMM 1 (SwiGLU), expert GEMM 2 +
+  // return + combine.  offsets = [recv, meta, counts, ready, done, comb] in the symmetric heap
+  // (or in `local_heap`, a CUDA byte tensor standing in for it on a single GPU without an
+  // engine).  phases: bit 0 dispatch, bit 1 up, bit 2 down (all three by default).
+  f.def("moe_forward",
+        [](const torch::Tensor& x, const torch::Tensor& wg, const torch::Tensor& w13, const torch::Tensor& w2,
+           torch::Tensor& h, torch::Tensor& out, torch::Tensor& scratch, torch::Tensor& cta_counter,
+           const std::vector<int64_t>& offsets, int64_t cap, int64_t epoch, c10::optional<torch::Tensor> local_heap,
+           int ctas, int phases, c10::optional<torch::Tensor> topk_idx, c10::optional<torch::Tensor> topk_gate) {
+          const gemm::MatrixDesc dx = as_matrix(x, "x"), dg = as_matrix(wg, "wg");
+          const gemm::MatrixDesc d13 = as_matrix(w13, "w13"), d2 = as_matrix(w2, "w2");
+          TORCH_CHECK(x.is_contiguous() && wg.is_contiguous() && w13.is_contiguous() && w2.is_contiguous() &&
+                          h.is_contiguous() && out.is_contiguous(), "MoE operands must be contiguous");
+          TORCH_CHECK(offsets.size() == 6, "offsets = [recv, meta, counts, ready, done, comb]");
+          gemm::PeerBases peers{};
+          if (local_heap.has_value()) {
+            TORCH_CHECK(local_heap->is_cuda() && local_heap->is_contiguous(), "local_heap must be a CUDA buffer");
+            peers.rank = 0;
+            peers.world = 1;
+            peers.base[0] = static_cast<uint8_t*>(local_heap->data_ptr());
+          } else {
+            peers = peer_bases();
+          }
+          const int tokens = dx.rows, hidden = dx.cols, experts = dg.rows;
+          TORCH_CHECK(experts % peers.world == 0, "experts must divide over the ranks");
+          const int local_experts = experts / peers.world;
+          const int ffn = d2.cols;
+          TORCH_CHECK(d13.rows == local_experts * 2 * ffn && d13.cols == hidden, "w13 must be [local_experts * 2 * ffn, hidden]");
+          TORCH_CHECK(d2.rows == local_experts * hidden, "w2 must be [local_experts * hidden, ffn]");
+          TORCH_CHECK(cap >= tokens, "region capacity must cover the tokens of one rank");
+          TORCH_CHECK(h.scalar_type() == torch::kBFloat16 &&
+                          h.numel() >= static_cast<int64_t>(local_experts) * peers.world * cap * ffn, "h is too small");
+          TORCH_CHECK(out.scalar_type() == torch::kBFloat16 && out.numel() == static_cast<int64_t>(tokens) * hidden,
+                      "out must be bf16 [tokens, hidden]");
+          gemm::MoeBuffers buf{};
+          buf.recv_off = offsets[0]; buf.meta_off = offsets[1]; buf.counts_off = offsets[2];
+          buf.ready_off = offsets[3]; buf.done_off = offsets[4]; buf.comb_off = offsets[5];
+          buf.cap = static_cast<int>(cap);
+          cudaStream_t stream = c10::cuda::getCurrentCUDAStream().stream();
+          int32_t* idx = topk_idx.has_value() ? reinterpret_cast<int32_t*>(as_u32(*topk_idx, 2 * tokens, "topk_idx")) : nullptr;
+          float* gate = nullptr;
+          if (topk_gate.has_value()) {
+            TORCH_CHECK(topk_gate->is_cuda() && topk_gate->scalar_type() == torch::kFloat32 &&
+                            topk_gate->is_contiguous() && topk_gate->numel() >= 2 * tokens, "topk_gate must be float32 [tokens, 2]");
+            gate = topk_gate->data_ptr<float>();
+          }
+          if (phases & 1)
+            gemm::moe_route_dispatch(peers, buf, x.data_ptr(), wg.data_ptr(), tokens, hidden, experts,
+                                     as_u32(scratch, experts + 1, "scratch"), idx, gate, nullptr, nullptr, true,
+                                     static_cast<uint32_t>(epoch), stream);
+          if (phases & 2)
+            gemm::moe_expert_up(peers, buf, hidden, ffn, local_experts, w13.data_ptr(), h.data_ptr(),
+                                static_cast<uint32_t>(epoch), stream, ctas);
+          if (phases & 4)
+            gemm::moe_expert_down(peers, buf, tokens, hidden, ffn, local_experts, h.data_ptr(), w2.data_ptr(),
+                                  out.data_ptr(), as_u32(cta_counter, 1, "cta_counter"),
+                                  static_cast<uint32_t>(epoch), stream, ctas);
+        },
+        py::arg("x"), py::arg("wg"), py::arg("w13"), py::arg("w2"), py::arg("h"), py::arg("out"), py::arg("scratch"),
+        py::arg("cta_counter"), py::arg("offsets"), py::arg("cap"), py::arg("epoch"),
+        py::arg("local_heap") = py::none(), py::arg("ctas") = 0, py::arg("phases") = 7,
+        py::arg("topk_idx") = py::none(), py::arg("topk_gate") = py::none());
   // Device-side error word of the GEMM family (0 = ok); synchronises.
   f.def("read_error", &gemm::read_error);
   f.def("clear_error", &gemm::clear_error);

@@ -54,5 +54,42 @@ void ar_residual_rmsnorm(const PeerBases& peers, uint8_t* mc_base, uint64_t x_of
                          uint64_t flags_off, const void* gamma, uint32_t* cta_counter, int tokens, int hidden,
                          float eps, uint32_t epoch, cudaStream_t stream, int ctas = 0, uint64_t timeout_ms = 2000);
 
+// ---- expert-parallel MoE feed-forward (top-2 routing) ------------------------------------------------
+// Symmetric-heap offsets (identical on every rank) of the buffers the three kernels share.
+// regions = (experts / world) * world, region = local_expert * world + source rank.
+struct MoeBuffers {
+  uint64_t recv_off;      // bf16 [regions][cap][hidden]: dispatched token rows
+  uint64_t meta_off;      // uint2 [regions][cap]: {token * 2 + k, gate}
+  uint64_t counts_off;    // u32 [regions]: rows filled (rewritten by every call)
+  uint64_t ready_off;     // u32 [world]: dispatch flags, zeroed once
+  uint64_t done_off;      // u32 [world]: expert-finished flags, zeroed once
+  uint64_t comb_off;      // bf16 [tokens][2][hidden]: expert outputs back at the tokens' home rank
+  int cap;                // rows per region, a multiple of 128 (>= tokens per rank: nothing is dropped)
+};
+
+// Router (+ dispatch).  x[tokens, hidden], wg[experts, hidden] local bf16.  scratch: local
+// u32[experts + 1], cleared by this call on `stream`.  Optional outputs (null to skip):
+// topk_idx / topk_gate / topk_slot [tokens, 2], expert_counts [experts].  With dispatch the
+// rows, metadata and counts land in the expert ranks' buffers and the ready flag is posted.
+// experts * hidden * 2 bytes of router weight must fit in shared memory (200 KB).
+void moe_route_dispatch(const PeerBases& peers, const MoeBuffers& buf, const void* x, const void* wg, int tokens,
+                        int hidden, int experts, uint32_t* scratch, int32_t* topk_idx, float* topk_gate,
+                        int32_t* topk_slot, uint32_t* expert_counts, bool dispatch, uint32_t epoch,
+                        cudaStream_t stream);
+
+// Expert GEMM 1 with the SwiGLU epilogue: h[regions * cap, ffn] = silu(X W1^T) * (X W3^T) over the
+// filled rows.  w13: local bf16 [local_experts * 2 * ffn, hidden], gate and up rows interleaved in
+// groups of 16 per expert.  Waits (bounded) for every source rank's dispatch flag of this epoch.
+void moe_expert_up(const PeerBases& peers, const MoeBuffers& buf, int hidden, int ffn, int local_experts,
+                   const void* w13, void* h, uint32_t epoch, cudaStream_t stream, int ctas = 0,
+                   uint64_t timeout_ms = 2000);
+
+// Expert GEMM 2 + gate-weighted return + combine: out[tokens, hidden] = sum of the two expert
+// outputs of each local token.  w2: local bf16 [local_experts * hidden, ffn].  cta_counter: local
+// zero-initialised u32; `ctas` must not change between calls of one layer.
+void moe_expert_down(const PeerBases& peers, const MoeBuffers& buf, int tokens, int hidden, int ffn,
+                     int local_experts, const void* h, const void* w2, void* out, uint32_t* cta_counter,
+                     uint32_t epoch, cudaStream_t stream, int ctas = 0, uint64_t timeout_ms = 2000);
+
 }  // namespace gemm
 }  // namespace pccl

@@ -5,6 +5,7 @@
 
 #include "../engine/cuda_driver.h"
 #include "gemm_host.h"
+#include "moe_policies.cuh"
 #include "tp_policies.cuh"
 #include "umma_gemm.cuh"
 
@@ -72,12 +73,14 @@ int sm_count() {
 
 template <class Policy>
 void launch(const MatrixDesc& a, const MatrixDesc& b, const typename Policy::Params& params, int ctas,
-            uint64_t timeout_ms, cudaStream_t stream, int aux_ctas = 0) {
+            uint64_t timeout_ms, cudaStream_t stream, int aux_ctas = 0, int groups = 1) {
+  // groups > 1: B stacks `groups` weight matrices of N rows each and the tile list is built on
+  // the device, so the grid is not trimmed to a tile count known here.
   PCCL_CHECK(a.cols == b.cols, "GEMM: A and B disagree on K (" << a.cols << " vs " << b.cols << ")");
   PCCL_CHECK(a.cols % 8 == 0, "GEMM: K must be a multiple of 8");
-  PCCL_CHECK(b.rows % 8 == 0, "GEMM: N must be a multiple of 8");
+  PCCL_CHECK(b.rows % groups == 0 && b.rows / groups % 8 == 0, "GEMM: N must be a multiple of 8");
   Problem g;
-  g.M = a.rows; g.N = b.rows; g.K = a.cols;
+  g.M = a.rows; g.N = b.rows / groups; g.K = a.cols;
   g.tiles_m = (g.M + kBM - 1) / kBM;
   g.tiles_n = (g.N + kBN - 1) / kBN;
   g.error = error_word();
@@ -91,7 +94,7 @@ void launch(const MatrixDesc& a, const MatrixDesc& b, const typename Policy::Par
   // `aux_ctas` of them do not run GEMM tiles.
   int grid = ctas > 0 ? ctas : sm_count();
   if (grid > sm_count()) grid = sm_count();
-  if (grid - aux_ctas > tiles) grid = tiles + aux_ctas;
+  if (groups == 1 && grid - aux_ctas > tiles) grid = tiles + aux_ctas;
   if (grid - aux_ctas < 1) grid = aux_ctas + 1;
   kernel<<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, g, params);
   PCCL_CUDA(cudaGetLastError());
@@ -177,6 +180,57 @@ void all_gather_gemm(const PeerBases& peers, uint64_t gathered_off, int M, int K
   const int sms = sm_count();
   int grid = ctas > 0 ? ctas : sms;
   launch<AllGatherPolicy>(a, w, p, grid, timeout_ms, stream, p.copy_ctas);
+}
+
+namespace {
+MoeShape moe_shape(const PeerBases& peers, const MoeBuffers& buf, int local_experts, bool wait_ready, uint32_t epoch) {
+  PCCL_CHECK(buf.cap > 0 && buf.cap % kBM == 0, "MoE: region capacity must be a multiple of " << kBM);
+  PCCL_CHECK(local_experts * peers.world <= kMoeMaxRegions,
+             "MoE: local experts x world exceeds " << kMoeMaxRegions << " regions");
+  PCCL_CHECK(epoch >= 1, "MoE: epoch counts calls from 1");
+  MoeShape s{};
+  uint8_t* self = peers.base[peers.rank];
+  s.counts = reinterpret_cast<const uint32_t*>(self + buf.counts_off);
+  s.ready = reinterpret_cast<const uint32_t*>(self + buf.ready_off);
+  s.world = peers.world;
+  s.local_experts = local_experts;
+  s.cap_blocks = buf.cap / kBM;
+  s.wait_ready = wait_ready ? 1 : 0;
+  s.epoch = epoch;
+  return s;
+}
+}  // namespace
+
+void moe_expert_up(const PeerBases& peers, const MoeBuffers& buf, int hidden, int ffn, int local_experts,
+                   const void* w13, void* h, uint32_t epoch, cudaStream_t stream, int ctas, uint64_t timeout_ms) {
+  PCCL_CHECK(ffn % 16 == 0 && hidden % 8 == 0, "MoE: ffn must be a multiple of 16, hidden of 8");
+  MoeUpPolicy::Params p{};
+  p.shape = moe_shape(peers, buf, local_experts, true, epoch);
+  p.h = static_cast<__nv_bfloat16*>(h);
+  p.ldh = ffn;
+  const int rows = local_experts * peers.world * buf.cap;
+  MatrixDesc a{peers.base[peers.rank] + buf.recv_off, rows, hidden, hidden};
+  MatrixDesc b{w13, local_experts * 2 * ffn, hidden, hidden};
+  launch<MoeUpPolicy>(a, b, p, ctas, timeout_ms, stream, 0, local_experts);
+}
+
+void moe_expert_down(const PeerBases& peers, const MoeBuffers& buf, int tokens, int hidden, int ffn,
+                     int local_experts, const void* h, const void* w2, void* out, uint32_t* cta_counter,
+                     uint32_t epoch, cudaStream_t stream, int ctas, uint64_t timeout_ms) {
+  PCCL_CHECK(hidden % 8 == 0 && ffn % 8 == 0, "MoE: hidden and ffn must be multiples of 8");
+  MoeDownPolicy::Params p{};
+  p.shape = moe_shape(peers, buf, local_experts, false, epoch);
+  p.peers = to_view(peers);
+  p.meta_off = buf.meta_off;
+  p.comb_off = buf.comb_off;
+  p.done_off = buf.done_off;
+  p.cta_counter = cta_counter;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.tokens = tokens;
+  const int rows = local_experts * peers.world * buf.cap;
+  MatrixDesc a{h, rows, ffn, ffn};
+  MatrixDesc b{w2, local_experts * hidden, ffn, ffn};
+  launch<MoeDownPolicy>(a, b, p, ctas, timeout_ms, stream, 0, local_experts);
 }
 
 }  // namespace gemm

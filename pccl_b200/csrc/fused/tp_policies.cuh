@@ -41,7 +41,7 @@ __device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t want
 }
 
 // ------------------------------------------------------------------------------------------------
-struct ReduceScatterPolicy {
+struct ReduceScatterPolicy : PolicyDefaults {
   struct Params {
     PeerView peers;
     uint64_t recv_off;          // heap offset of recv[2][world][rows_per_rank][N] bf16
@@ -53,6 +53,9 @@ struct ReduceScatterPolicy {
     uint32_t epoch;             // 1, 2, 3, ... per call
   };
 
+  __device__ static int prepare(const Params&, const Problem& g, uint64_t, const volatile uint32_t*) {
+    return g.tiles_m;
+  }
   // Row blocks are visited round-robin over the owners (rank+1, rank+2, ..., rank), so NVLink
   // traffic is spread over the whole GEMM and every owner receives its blocks in order; the
   // n-tiles of one row block are consecutive so that the block's flag is posted early.
@@ -158,7 +161,7 @@ struct ReduceScatterPolicy {
 };
 
 // ------------------------------------------------------------------------------------------------
-struct AllGatherPolicy {
+struct AllGatherPolicy : PolicyDefaults {
   struct Params {
     PeerView peers;
     uint64_t gathered_off;      // heap offset of the gathered A [world * rows_per_rank][K] bf16 (per rank)
@@ -172,6 +175,9 @@ struct AllGatherPolicy {
     uint32_t epoch;
   };
 
+  __device__ static int prepare(const Params&, const Problem& g, uint64_t, const volatile uint32_t*) {
+    return g.tiles_m;
+  }
   // Shards in the order own, rank+1, rank+2, ...; M-fastest inside a shard.
   __device__ static void tile_coords(const Params& p, const Problem& g, int tile, int* mb, int* nb) {
     const int per_shard = p.blocks_per_rank * g.tiles_n;

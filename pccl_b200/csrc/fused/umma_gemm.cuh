@@ -14,8 +14,11 @@
 //               them — to local memory, or straight into a peer GPU's memory for the fused
 //               GEMM -> reduce-scatter.
 //
-// A Policy supplies the tile order, an optional "rows ready" wait before a tile's A rows
-// are loaded (all-gather -> GEMM), the row-segment store, and a per-tile completion hook.
+// A Policy supplies the tile list (optionally sized on the device: ragged expert batches), the
+// tile order, an optional "rows ready" wait before a tile's A rows are loaded (all-gather ->
+// GEMM), the row of the stacked weight an n-tile starts at (grouped GEMM), the destination /
+// scale / validity of each output row, an element-wise transform of the accumulator (SwiGLU),
+// and a per-tile completion hook.
 // Every wait is bounded; on a timeout the error word is set, all roles leave their loops,
 // the CTA waits for its outstanding TMA transactions, frees its TMEM and returns.
 // The reference contains no GEMM or tensor-core code; this kernel has no counterpart there.
@@ -59,6 +62,32 @@ __device__ __forceinline__ void raise_error(const Problem& g, uint32_t code, uin
 
 __device__ __forceinline__ uint4 pack8_bf16(const float* f);
 
+// What a policy may leave at its default by deriving from this struct.
+struct PolicyDefaults {
+  // Outputs per 32 accumulator columns: 32 (plain) or 16 (pairwise-combining epilogue, SwiGLU).
+  static constexpr int kOutPer32 = 32;
+  // true: the destination, validity and scale of a row come from Policy::row_info (rows of one
+  // tile may go to unrelated addresses); false: tile_base + row * row_pitch.
+  static constexpr bool kRowScatter = false;
+  // Row of B (and column of the accumulator grid) where n-tile nb starts.
+  template <class P>
+  __device__ static int b_row(const P&, const Problem&, int, int nb);
+  // 32 accumulator columns -> kOutPer32 values, scaled by the row's factor.
+  __device__ static void transform(const float* acc, float scale, float* out) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) out[i] = acc[i] * scale;
+  }
+};
+
+template <class P>
+__device__ int PolicyDefaults::b_row(const P&, const Problem&, int, int nb) { return nb * kBN; }
+
+struct RowInfo {
+  uint8_t* dst;      // address of output column 0 of this row
+  float scale;
+  uint32_t valid;
+};
+
 template <class Policy>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
@@ -99,7 +128,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = pipe.tmem_base;
 
-  const int num_tiles = g.tiles_m * g.tiles_n;
+  // Policies with a data-dependent row count (ragged expert batches) size their tile list here;
+  // a negative answer (a wait ran out) leaves no tiles and falls through to the TMEM release.
+  const int tiles_m = Policy::prepare(p, g, deadline, abort_flag);
+  const int num_tiles = tiles_m < 0 ? 0 : tiles_m * g.tiles_n;
   const int k_blocks = (g.K + kBK - 1) / kBK;
 
   if (warp == 0) {
@@ -120,7 +152,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           uint8_t* b_dst = a_dst + kBytesA;
           ptx::mbar_expect_tx(&pipe.full[stage], kStageBytes);
           ptx::tma_load_2d(a_dst, &tma_a, &pipe.full[stage], kb * kBK, mb * kBM);
-          ptx::tma_load_2d(b_dst, &tma_b, &pipe.full[stage], kb * kBK, nb * kBN);
+          ptx::tma_load_2d(b_dst, &tma_b, &pipe.full[stage], kb * kBK, Policy::b_row(p, g, mb, nb));
           ++issued;
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
@@ -205,12 +237,23 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) { if (lane == 0) raise_error(g, kErrEpilogueWait, 2); break; }
       ptx::tc_fence_after_sync();
-      const int row_base = mb * kBM + quarter * 32;
-      uint8_t* const tile_dst = Policy::tile_base(p, g, mb);       // row mb*128, column 0 of the destination
-      const int64_t pitch = Policy::row_pitch(p, g);              // bytes between destination rows
+      constexpr int kOut = Policy::kOutPer32;                  // outputs per 32 accumulator columns
+      constexpr int kRowBytes = kEpiCols / 32 * kOut * 2;       // staged bytes per row and pass
+      constexpr int kChunks = kRowBytes / 16;                   // 16-byte chunks per staged row
+      constexpr int kRowsPerSt = 32 / kChunks;                  // rows written per store instruction
+      // The lane that owns TMEM lane (= tile row) quarter*32 + lane looks up that row's destination.
+      RowInfo info;
+      if constexpr (Policy::kRowScatter) {
+        info = Policy::row_info(p, g, mb, quarter * 32 + lane);
+      } else {
+        info.dst = Policy::tile_base(p, g, mb) + static_cast<int64_t>(quarter * 32 + lane) * Policy::row_pitch(p, g);
+        info.scale = 1.f;
+        info.valid = mb * kBM + quarter * 32 + lane < g.M ? 1u : 0u;
+      }
+      const int out_cols = g.N * kOut / 32;
       const uint32_t taddr = tmem_base + acc * kBN + (static_cast<uint32_t>(quarter * 32) << 16);
-      // Staging buffer of this warp: 32 rows x 16 chunks of 16 bytes, chunk index XOR-swizzled by
-      // the row so that both the row-wise writes and the chunk-wise reads spread over banks.
+      // Staging buffer of this warp: 32 rows of kChunks 16-byte chunks, chunk index XOR-swizzled
+      // by the row so that both the row-wise writes and the chunk-wise reads spread over banks.
       uint8_t* stage_buf = smem + kStages * kStageBytes + (warp - 2) * kEpiWarpBytes;
 #pragma unroll 1
       for (int c0 = 0; c0 < kBN; c0 += kEpiCols) {
@@ -219,22 +262,26 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           uint32_t v[32];
           ptx::tmem_ld_32x32b_x32(taddr + c0 + q * 32, v);
           ptx::tmem_ld_wait();
+          float o[kOut];
+          Policy::transform(reinterpret_cast<const float*>(v), info.scale, o);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int chunk = (q * 4 + i) ^ (lane & 15);
-            *reinterpret_cast<uint4*>(stage_buf + lane * (kEpiCols * 2) + chunk * 16) =
-                pack8_bf16(reinterpret_cast<const float*>(v) + 8 * i);
+          for (int i = 0; i < kOut / 8; ++i) {
+            const int chunk = (q * (kOut / 8) + i) ^ (lane & (kChunks - 1));
+            *reinterpret_cast<uint4*>(stage_buf + lane * kRowBytes + chunk * 16) = pack8_bf16(o + 8 * i);
           }
         }
         __syncwarp();
-        // Half a warp writes one row's 256 contiguous bytes; two rows per instruction.
+        // kChunks lanes write one row's contiguous bytes; kRowsPerSt rows per instruction.
+        const int col_first = (nb * kBN + c0) / 32 * kOut;
 #pragma unroll 4
-        for (int it = 0; it < 16; ++it) {
-          const int r = it * 2 + (lane >> 4), j = lane & 15;
-          const int row = row_base + r, col = nb * kBN + c0 + j * 8;
-          uint8_t* dst = tile_dst + static_cast<int64_t>(quarter * 32 + r) * pitch + static_cast<int64_t>(col) * 2;
-          const uint4 val = *reinterpret_cast<const uint4*>(stage_buf + r * (kEpiCols * 2) + ((j ^ (r & 15)) * 16));
-          if (row < g.M && col < g.N) ptx::st_v4(dst, val);
+        for (int it = 0; it < 32 / kRowsPerSt; ++it) {
+          const int r = it * kRowsPerSt + lane / kChunks, j = lane % kChunks;
+          const uint64_t dst_bits = __shfl_sync(0xffffffffu, reinterpret_cast<uint64_t>(info.dst), r);
+          const uint32_t row_ok = __shfl_sync(0xffffffffu, info.valid, r);
+          const int col = col_first + j * 8;
+          const uint4 val = *reinterpret_cast<const uint4*>(stage_buf + r * kRowBytes + ((j ^ (r & (kChunks - 1))) * 16));
+          if (row_ok && col < out_cols)
+            ptx::st_v4(reinterpret_cast<uint8_t*>(dst_bits) + static_cast<int64_t>(col) * 2, val);
         }
         __syncwarp();
       }
@@ -272,11 +319,14 @@ __device__ __forceinline__ uint4 pack8_bf16(const float* f) {
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-struct StorePolicy {
+struct StorePolicy : PolicyDefaults {
   struct Params {
     __nv_bfloat16* c;
     int64_t ldc;
   };
+  __device__ static int prepare(const Params&, const Problem& g, uint64_t, const volatile uint32_t*) {
+    return g.tiles_m;
+  }
   // M-fastest order: consecutive CTAs share the B tile (weights) through L2.
   __device__ static void tile_coords(const Params&, const Problem& g, int tile, int* mb, int* nb) {
     *mb = tile % g.tiles_m;

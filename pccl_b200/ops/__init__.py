@@ -1,6 +1,7 @@
 """Fused compute + collective operators built on hand-written tcgen05 kernels."""
 
-from . import gemm
+from . import gemm, moe
+from .moe import FusedMoE
 from .tensor_parallel import AllGatherGemm, AllReduceResidualRMSNorm, GemmReduceScatter
 
-__all__ = ["gemm", "GemmReduceScatter", "AllGatherGemm", "AllReduceResidualRMSNorm"]
+__all__ = ["gemm", "moe", "FusedMoE", "GemmReduceScatter", "AllGatherGemm", "AllReduceResidualRMSNorm"]

@@ -168,6 +168,32 @@ def main():
                                            msg=lambda t: f"ar_rmsnorm y T={tokens} nvls={use_nvls} rank {rank}: {t}")
             report["checked"] += 1
 
+    # ---- expert-parallel MoE: route + dispatch, grouped expert GEMMs, gate-weighted return + combine ----
+    from pccl_b200.ops import moe
+    for (tokens, hidden_m, ffn, experts) in ((512, 512, 1024, 8), (300, 1024, 2048, 8)):
+        gen0 = torch.Generator(device="cuda").manual_seed(11)             # identical on every rank
+        wg = (torch.randn(experts, hidden_m, device="cuda", generator=gen0) * 0.5).to(torch.bfloat16)
+        w1 = (torch.randn(experts, ffn, hidden_m, device="cuda", generator=gen0) * hidden_m ** -0.5).to(torch.bfloat16)
+        w3 = (torch.randn(experts, ffn, hidden_m, device="cuda", generator=gen0) * hidden_m ** -0.5).to(torch.bfloat16)
+        w2 = (torch.randn(experts, hidden_m, ffn, device="cuda", generator=gen0) * ffn ** -0.5).to(torch.bfloat16)
+        layer = moe.FusedMoE(tokens, hidden_m, ffn, experts)
+        le = experts // world
+        mine = slice(rank * le, (rank + 1) * le)
+        layer.set_weights(wg, w1[mine], w3[mine], w2[mine])
+        gen = torch.Generator(device="cuda").manual_seed(200 + rank)
+        for call in range(3):
+            xt = torch.randn(tokens, hidden_m, device="cuda", generator=gen).to(torch.bfloat16)
+            out = layer(xt)
+            torch.cuda.synchronize()
+            gemm.check()
+            ref, ref_idx, _ = moe.moe_reference(xt, wg, w1, w3, w2)
+            same = (layer.topk_idx.long() == ref_idx).all(dim=-1)
+            assert same.float().mean() > 0.95, f"moe routing differs on rank {rank}"
+            err = (out.float() - ref)[same].abs().max().item()
+            scale = ref[same].abs().max().item()
+            assert err <= 2e-2 * scale + 1e-3, f"moe T={tokens} call {call} rank {rank}: error {err} vs {scale}"
+        report["checked"] += 1
+
     torch.cuda.synchronize()
     dist.barrier()
     if rank == 0:
