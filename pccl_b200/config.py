@@ -33,9 +33,9 @@ OPTIONS: Dict[str, tuple] = {
     "WORLD_SIZE": ("world_size", int, 1, "number of ranks"),
     "PCCL_BUFFER_SIZE": ("buffer_size", _size, 1 << 30, "bytes of the plan working buffer"),
     "PCCL_ARENA_SIZE": ("arena_size", _size, 1 << 30, "bytes of symmetric memory for fused operators"),
-    "PCCL_NUM_BLOCKS": ("num_blocks", int, 96, "upper bound of CTAs per collective launch"),
+    "PCCL_NUM_BLOCKS": ("num_blocks", int, 128, "upper bound of CTAs per collective launch"),
     "PCCL_FORCE_BLOCKS": ("force_blocks", int, 0, "exact CTA count per launch (0 = heuristic)"),
-    "PCCL_MIN_BYTES_PER_BLOCK": ("min_bytes_per_block", _size, 64 << 10, "smallest share worth another CTA"),
+    "PCCL_MIN_BYTES_PER_BLOCK": ("min_bytes_per_block", _size, 16 << 10, "smallest share worth another CTA"),
     "PCCL_WAIT_TIMEOUT_MS": ("wait_timeout_ms", int, 10000, "time budget of device-side waits per launch"),
     "PCCL_NVLS_ENABLE": ("nvls_enable", _flag, True, "use NVLS multicast when every rank supports it"),
     "PCCL_DISABLE_NVLS": ("disable_nvls", _flag, False, "turn NVLS off"),
@@ -55,9 +55,9 @@ class PcclConfig:
     world_size: int = 1
     buffer_size: int = 1 << 30
     arena_size: int = 1 << 30
-    num_blocks: int = 96
+    num_blocks: int = 128
     force_blocks: int = 0
-    min_bytes_per_block: int = 64 << 10
+    min_bytes_per_block: int = 16 << 10
     wait_timeout_ms: int = 10000
     nvls_enable: bool = True
     disable_nvls: bool = False

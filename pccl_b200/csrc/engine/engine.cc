@@ -33,7 +33,7 @@ uint32_t auto_ctas(const Plan& plan, uint32_t cap) {
   uint64_t moved = 0;
   for (const PlanOp& op : plan.ops)
     if (op.count > 0) moved = std::max<uint64_t>(moved, static_cast<uint64_t>(op.count) * dtype_bytes(plan.dtype));
-  const uint64_t per_channel = std::max<uint64_t>(1, moved / (128 << 10));
+  const uint64_t per_channel = std::max<uint64_t>(1, moved / (16 << 10));
   const uint64_t want = per_channel * static_cast<uint64_t>(plan.num_channels);
   return static_cast<uint32_t>(std::min<uint64_t>(std::max<uint64_t>(want, plan.num_channels), cap));
 }
@@ -64,6 +64,8 @@ RankContext::RankContext(int rank, int world, int device, size_t buffer_bytes, s
   PCCL_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&h_status_), sizeof(DeviceStatus), cudaHostAllocMapped));
   std::memset(h_status_, 0, sizeof(DeviceStatus));
   PCCL_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&h_status_dev_), h_status_, 0));
+  PCCL_CHECK(set_mover_tuning(static_cast<uint32_t>(Environs::get_int("PCCL_MOVER_TUNING", 0))) == 0,
+             "cannot set the data-mover tuning word");
 }
 
 RankContext::~RankContext() {
@@ -111,10 +113,10 @@ void RankContext::upload(RegisteredOp& op) {
   lo.rank = rank_;
   lo.world = world_;
   lo.multicast = heap_.multicast_ready();
-  const uint32_t cap = cta_cap_ ? cta_cap_ : static_cast<uint32_t>(Environs::get_int("PCCL_NUM_BLOCKS", 96));
+  const uint32_t cap = cta_cap_ ? cta_cap_ : static_cast<uint32_t>(Environs::get_int("PCCL_NUM_BLOCKS", 128));
   const int64_t forced = Environs::get_int("PCCL_FORCE_BLOCKS", 0);
   lo.total_ctas = forced > 0 ? std::min<uint32_t>(static_cast<uint32_t>(forced), cap) : auto_ctas(op.plan, cap);
-  lo.min_bytes_per_cta = static_cast<uint64_t>(Environs::get_int("PCCL_MIN_BYTES_PER_BLOCK", 64 << 10));
+  lo.min_bytes_per_cta = static_cast<uint64_t>(Environs::get_int("PCCL_MIN_BYTES_PER_BLOCK", 16 << 10));
   // Templates of this library end with their own barrier; everything else gets one appended.
   const std::string& algo = op.plan.algorithm;
   const bool self_fenced = algo == "oneshot" || algo == "twoshot" || algo == "direct" || algo == "nvls";
@@ -386,7 +388,7 @@ void Engine::exeOp(const std::string& name, const void* in, size_t in_bytes, voi
       op.ce->run(op.host_program.data, rank_, op.launch_index, stream);
     } else {
       LaunchParams lp{op.d_program, op.launch_index};
-      LaunchConfig cfg{std::max<uint32_t>(1, op.lowered.total_ctas), op.threads, 1, false};
+      LaunchConfig cfg{std::max<uint32_t>(1, op.lowered.total_ctas), op.threads, 1, false, op.host_program.dtype};
       const int err = launch_plan_interp(lp, cfg, stream);
       PCCL_CHECK(err == 0, "kernel launch failed: " << cudaGetErrorString(static_cast<cudaError_t>(err)));
     }
@@ -524,7 +526,7 @@ LocalCluster::~LocalCluster() {
 void LocalCluster::regOp(const std::string& name, const std::vector<std::string>& json_per_rank) {
   PCCL_CHECK(static_cast<int>(json_per_rank.size()) == world_, "need one plan per rank");
   // All virtual ranks must be co-resident in one cooperative launch.
-  const int resident = plan_interp_max_ctas(512);
+  const int resident = plan_interp_max_ctas(kInterpThreads);
   PCCL_CHECK(resident > 0, "no CUDA device");
   const uint32_t per_rank = std::max<uint32_t>(1, ctas_override_ ? std::min<uint32_t>(ctas_override_, resident / world_)
                                                                  : static_cast<uint32_t>(resident / world_));
@@ -559,7 +561,8 @@ void LocalCluster::exeOp(const std::string& name, const std::vector<const void*>
     launch_index = op.launch_index;
   }
   LaunchParams lp{d_programs_.at(name), launch_index};
-  LaunchConfig cfg{ctas, 512, static_cast<uint32_t>(world_), true};
+  LaunchConfig cfg{ctas, kInterpThreads, static_cast<uint32_t>(world_), true,
+                   ranks_[0]->op(name).host_program.dtype};
   const int err = launch_plan_interp(lp, cfg, stream);
   PCCL_CHECK(err == 0, "cooperative launch failed: " << cudaGetErrorString(static_cast<cudaError_t>(err)));
   for (int r = 0; r < world_; ++r) {

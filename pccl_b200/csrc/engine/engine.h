@@ -43,7 +43,7 @@ struct RegisteredOp {
   uint32_t* chain_sync = nullptr;       // control-area counters
   uint32_t* chain_progress = nullptr;
   uint32_t launch_index = 0;
-  uint32_t threads = 512;
+  uint32_t threads = kInterpThreads;
   std::unique_ptr<CeSchedule> ce;       // set when the copy-engine executor runs this operation
   OpStats stats;
 };

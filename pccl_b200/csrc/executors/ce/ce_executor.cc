@@ -31,6 +31,7 @@ bool CeSchedule::supports(const LoweredProgram& lp) {
 }
 
 void CeSchedule::build(const LoweredProgram& lp, const RankProgram& base, uint64_t min_copy_bytes) {
+  dtype_ = base.dtype;
   clear();
   PCCL_CHECK(supports(lp), "the copy-engine executor cannot run plans whose chains depend on one another");
   // One Chain record per segment, all in one device table.
@@ -157,7 +158,7 @@ void CeSchedule::run(uint8_t* const* data, int self, uint32_t launch_index, cuda
                                   cudaMemcpyDeviceToDevice, cs));
       } else {
         LaunchParams lp{it.d_program, launch_index};
-        LaunchConfig cfg{it.ctas, 512, 1, false};
+        LaunchConfig cfg{it.ctas, kInterpThreads, 1, false, dtype_};
         const int err = launch_plan_interp(lp, cfg, cs);
         PCCL_CHECK(err == 0, "copy-engine executor: segment launch failed: "
                                  << cudaGetErrorString(static_cast<cudaError_t>(err)));

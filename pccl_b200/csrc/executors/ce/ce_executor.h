@@ -54,6 +54,7 @@ class CeSchedule {
   size_t num_segments() const { return segments_; }
 
  private:
+  uint32_t dtype_ = 0;                  // element type of the plan (selects the kernel instance)
   void clear();
   std::vector<std::vector<CeItem>> chains_;
   std::vector<cudaStream_t> streams_;

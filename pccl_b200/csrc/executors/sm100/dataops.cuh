@@ -168,9 +168,13 @@ __device__ __forceinline__ Span make_span(const SrcTable& t, const uint8_t* dst,
   return sp;
 }
 
-__device__ __forceinline__ uint4 load_vec(const uint8_t* p, bool remote) {
-  return remote ? ptx::ld_peer_v4(p) : ptx::ld_local_v4(p);
-}
+// Tuning word set by the host (PCCL_MOVER_TUNING): bit 0 = keep two register tiles in flight per
+// thread.  Off by default: with unconditional loads one tile of 8 vectors per thread already
+// saturates NVLink, and the second tile measured a few percent slower.
+__constant__ uint32_t g_mover_tuning = 0;
+
+// Local and peer data are both read with weak L2 loads (one instruction, no branch).
+__device__ __forceinline__ uint4 load_vec(const uint8_t* p, bool) { return ptx::ld_local_v4(p); }
 
 // ---- copy family (dtype independent) --------------------------------------------------------
 
@@ -188,7 +192,8 @@ __device__ __noinline__ void copy_range(const SrcTable& t, uint8_t* dst, uint64_
   const uint8_t* src = t.ptr[0];
   const bool remote = t.remote_mask & 1u;
   const Span sp = make_span(t, dst, bytes);
-  const uint32_t tid = threadIdx.x, nthr = blockDim.x;
+  const uint32_t tid = threadIdx.x;
+  constexpr uint32_t nthr = kInterpThreads;     // compile-time: per-vector offsets become immediates
   if (!sp.uniform) {          // byte-exact everywhere (multicast ranges are always aligned)
     if (!kToMulticast) bytes_copy(src, dst, 0, bytes, cta * nthr + tid, nctas * nthr);
     return;
@@ -199,21 +204,49 @@ __device__ __noinline__ void copy_range(const SrcTable& t, uint8_t* dst, uint64_
   }
   src += sp.head;
   dst += sp.head;
-  for (uint64_t t0 = static_cast<uint64_t>(cta) * nthr * kU; t0 < sp.nvec;
-       t0 += static_cast<uint64_t>(nctas) * nthr * kU) {
-    uint4 v[kU];
+  const uint64_t tile = static_cast<uint64_t>(nthr) * kU, stride = static_cast<uint64_t>(nctas) * tile;
+  // Loads are unconditional (see ReduceTile::load); lanes past the end re-read the last vector.
+  auto load = [&](uint4* v, uint64_t first) {
+    if (first + kU * nthr <= sp.nvec) {
+      const uint8_t* p = src + (first + tid) * 16;
 #pragma unroll
-    for (int u = 0; u < kU; ++u) {
-      const uint64_t i = t0 + tid + static_cast<uint64_t>(u) * nthr;
-      if (i < sp.nvec) v[u] = load_vec(src + i * 16, remote);
-    }
+      for (int u = 0; u < kU; ++u) v[u] = load_vec(p + u * nthr * 16, remote);
+    } else {
 #pragma unroll
-    for (int u = 0; u < kU; ++u) {
-      const uint64_t i = t0 + tid + static_cast<uint64_t>(u) * nthr;
-      if (i < sp.nvec) {
-        if (kToMulticast) ptx::mm_st_v4(dst + i * 16, v[u]); else ptx::st_v4(dst + i * 16, v[u]);
+      for (int u = 0; u < kU; ++u) {
+        const uint64_t i = first + tid + u * nthr;
+        v[u] = load_vec(src + (i < sp.nvec ? i : sp.nvec - 1) * 16, remote);
       }
     }
+  };
+  auto store = [&](const uint4* v, uint64_t first) {
+    uint8_t* p = dst + (first + tid) * 16;
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      if (first + tid + u * nthr < sp.nvec) {
+        if (kToMulticast) ptx::mm_st_v4(p + u * nthr * 16, v[u]); else ptx::st_v4(p + u * nthr * 16, v[u]);
+      }
+    }
+  };
+  // Two tiles in flight: the loads of the next tile are issued before this one is stored.
+  uint4 a[kU], b[kU];
+  uint64_t t0 = static_cast<uint64_t>(cta) * tile;
+  if (t0 >= sp.nvec) return;
+  if (!(g_mover_tuning & 1u)) {
+    for (; t0 < sp.nvec; t0 += stride) { load(a, t0); store(a, t0); }
+    return;
+  }
+  load(a, t0);
+  while (true) {
+    const uint64_t t1 = t0 + stride;
+    if (t1 < sp.nvec) load(b, t1);
+    store(a, t0);
+    if (t1 >= sp.nvec) break;
+    const uint64_t t2 = t1 + stride;
+    if (t2 < sp.nvec) load(a, t2);
+    store(b, t1);
+    if (t2 >= sp.nvec) break;
+    t0 = t2;
   }
 }
 
@@ -231,14 +264,107 @@ __device__ __forceinline__ void scalar_fold(const SrcTable& t, uint8_t* dst, uin
   }
 }
 
+// One tile of a reduce: kN sources x kU vectors per thread.  Tiles are software-pipelined in
+// registers: the loads of tile i+1 are issued before tile i is folded and stored, so that a
+// thread keeps 2 * kN * kU independent 16-byte loads in flight (peer latency is microseconds).
+template <int DT, int kN, int kU>
+struct ReduceTile {
+  using C = Codec<DT>;
+  uint4 raw[kN][kU];
+
+  __device__ __forceinline__ void load(const SrcTable& t, int nsrc, uint64_t first, uint64_t head, uint64_t nvec,
+                                       uint32_t tid) {
+#pragma unroll
+    for (int s = 0; s < kN; ++s) {
+      {
+        // A slot beyond the source count re-reads source 0 (its value is never folded): every
+        // register of the tile is written unconditionally.
+        const int ss = s < nsrc ? s : 0;
+        const bool remote = (t.remote_mask >> ss) & 1u;
+        // Loads are unconditional (a conditionally assigned register makes the compiler wait for
+        // each load before issuing the next); lanes past the end re-read the last vector.
+        if (first + kU * kInterpThreads <= nvec) {
+          const uint8_t* p = t.ptr[ss] + head + (first + tid) * 16;
+#pragma unroll
+          for (int u = 0; u < kU; ++u) raw[s][u] = load_vec(p + u * kInterpThreads * 16, remote);
+        } else {
+          const uint8_t* p = t.ptr[ss] + head;
+#pragma unroll
+          for (int u = 0; u < kU; ++u) {
+            const uint64_t i = first + tid + u * kInterpThreads;
+            raw[s][u] = load_vec(p + (i < nvec ? i : nvec - 1) * 16, remote);
+          }
+        }
+      }
+    }
+  }
+
+  __device__ __forceinline__ void fold_store(int nsrc, uint8_t* dst, uint64_t first, uint64_t head, uint64_t nvec,
+                                             int op, float scale, uint32_t tid) const {
+    uint8_t* out = dst + head + (first + tid) * 16;
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      if (first + tid + u * kInterpThreads >= nvec) continue;
+      float acc[C::kLanes];
+      C::unpack(raw[0][u], acc);
+#pragma unroll
+      for (int s = 1; s < kN; ++s) {
+        if (s < nsrc) {
+          float f[C::kLanes];
+          C::unpack(raw[s][u], f);
+#pragma unroll
+          for (int l = 0; l < C::kLanes; ++l) acc[l] = fold1(acc[l], f[l], op);
+        }
+      }
+      if (scale != 1.0f) {
+#pragma unroll
+        for (int l = 0; l < C::kLanes; ++l) acc[l] *= scale;
+      }
+      ptx::st_v4(out + u * kInterpThreads * 16, C::pack(acc));
+    }
+  }
+};
+
+template <int DT, int kN, int kU>
+__device__ __forceinline__ void reduce_tiles(const SrcTable& t, uint8_t* dst, const Span& sp, int op, float scale,
+                                             uint32_t cta, uint32_t nctas) {
+  const uint32_t tid = threadIdx.x;
+  constexpr uint32_t nthr = kInterpThreads;     // compile-time: per-vector offsets become immediates
+  const int nsrc = t.count;
+  const uint64_t tile = static_cast<uint64_t>(nthr) * kU, stride = static_cast<uint64_t>(nctas) * tile;
+  ReduceTile<DT, kN, kU> a, b;
+  uint64_t t0 = static_cast<uint64_t>(cta) * tile;
+  if (t0 >= sp.nvec) return;
+  if (!(g_mover_tuning & 1u)) {
+    for (; t0 < sp.nvec; t0 += stride) {
+      a.load(t, nsrc, t0, sp.head, sp.nvec, tid);
+      a.fold_store(nsrc, dst, t0, sp.head, sp.nvec, op, scale, tid);
+    }
+    return;
+  }
+  a.load(t, nsrc, t0, sp.head, sp.nvec, tid);
+  while (true) {
+    const uint64_t t1 = t0 + stride;
+    if (t1 < sp.nvec) b.load(t, nsrc, t1, sp.head, sp.nvec, tid);
+    a.fold_store(nsrc, dst, t0, sp.head, sp.nvec, op, scale, tid);
+    if (t1 >= sp.nvec) break;
+    const uint64_t t2 = t1 + stride;
+    if (t2 < sp.nvec) a.load(t, nsrc, t2, sp.head, sp.nvec, tid);
+    b.fold_store(nsrc, dst, t1, sp.head, sp.nvec, op, scale, tid);
+    if (t2 >= sp.nvec) break;
+    t0 = t2;
+  }
+}
+
 // dst = scale * fold(op, sources).  One source + scale != 1 is the "avg" epilogue.
 template <int DT>
 __device__ __noinline__ void reduce_range(const SrcTable& t, uint8_t* dst, uint64_t bytes, int op,
                                           float scale, uint32_t cta, uint32_t nctas) {
   using C = Codec<DT>;
-  constexpr int kU = C::kLanes >= 16 ? 2 : 4;
+  constexpr bool kWide = C::kLanes >= 16;           // fp8: 16 accumulators per vector
   const Span sp = make_span(t, dst, bytes);
-  const uint32_t tid = threadIdx.x, nthr = blockDim.x;
+  const uint32_t tid = threadIdx.x;
+  constexpr uint32_t nthr = kInterpThreads;     // compile-time: per-vector offsets become immediates
   if (!sp.uniform) {
     scalar_fold<DT>(t, dst, 0, bytes, op, scale, cta * nthr + tid, nctas * nthr);
     return;
@@ -247,55 +373,11 @@ __device__ __noinline__ void reduce_range(const SrcTable& t, uint8_t* dst, uint6
     scalar_fold<DT>(t, dst, 0, sp.head, op, scale, tid, nthr);
     scalar_fold<DT>(t, dst, sp.tail_begin, bytes, op, scale, tid, nthr);
   }
-  const int nsrc = t.count;
-  for (uint64_t t0 = static_cast<uint64_t>(cta) * nthr * kU; t0 < sp.nvec;
-       t0 += static_cast<uint64_t>(nctas) * nthr * kU) {
-    uint64_t off[kU];
-    bool live[kU];
-#pragma unroll
-    for (int u = 0; u < kU; ++u) {
-      const uint64_t i = t0 + tid + static_cast<uint64_t>(u) * nthr;
-      live[u] = i < sp.nvec;
-      off[u] = sp.head + i * 16;
-    }
-    float acc[kU][C::kLanes];
-    uint4 cur[kU];
-#pragma unroll
-    for (int u = 0; u < kU; ++u)
-      if (live[u]) cur[u] = load_vec(t.ptr[0] + off[u], t.remote_mask & 1u);
-#pragma unroll
-    for (int u = 0; u < kU; ++u) C::unpack(live[u] ? cur[u] : make_uint4(0, 0, 0, 0), acc[u]);
-    if (nsrc > 1) {
-#pragma unroll
-      for (int u = 0; u < kU; ++u)
-        if (live[u]) cur[u] = load_vec(t.ptr[1] + off[u], t.remote_mask >> 1 & 1u);
-      for (int s = 1; s < nsrc; ++s) {
-        uint4 nxt[kU];
-        if (s + 1 < nsrc) {      // prefetch the next source before folding this one
-#pragma unroll
-          for (int u = 0; u < kU; ++u)
-            if (live[u]) nxt[u] = load_vec(t.ptr[s + 1] + off[u], t.remote_mask >> (s + 1) & 1u);
-        }
-#pragma unroll
-        for (int u = 0; u < kU; ++u) {
-          float f[C::kLanes];
-          C::unpack(live[u] ? cur[u] : make_uint4(0, 0, 0, 0), f);
-#pragma unroll
-          for (int l = 0; l < C::kLanes; ++l) acc[u][l] = fold1(acc[u][l], f[l], op);
-          cur[u] = nxt[u];
-        }
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < kU; ++u)
-      if (live[u]) {
-        if (scale != 1.0f) {
-#pragma unroll
-          for (int l = 0; l < C::kLanes; ++l) acc[u][l] *= scale;
-        }
-        ptx::st_v4(dst + off[u], C::pack(acc[u]));
-      }
-  }
+  // 8 loads per tile and thread (4 for fp8), two tiles in flight.
+  if (t.count <= 1) reduce_tiles<DT, 1, 4>(t, dst, sp, op, scale, cta, nctas);
+  else if (t.count == 2) reduce_tiles<DT, 2, kWide ? 2 : 4>(t, dst, sp, op, scale, cta, nctas);
+  else if (t.count <= 4) reduce_tiles<DT, 4, kWide ? 1 : 2>(t, dst, sp, op, scale, cta, nctas);
+  else reduce_tiles<DT, 8, 1>(t, dst, sp, op, scale, cta, nctas);
 }
 
 // ---- multimem reduce family ---------------------------------------------------------------------
@@ -319,22 +401,46 @@ __device__ __noinline__ void mm_reduce_range(const uint8_t* mc_src, uint8_t* dst
                                              uint32_t cta, uint32_t nctas) {
   constexpr int kU = 8;
   const uint64_t nvec = bytes / 16;
-  const uint32_t tid = threadIdx.x, nthr = blockDim.x;
-  for (uint64_t t0 = static_cast<uint64_t>(cta) * nthr * kU; t0 < nvec;
-       t0 += static_cast<uint64_t>(nctas) * nthr * kU) {
-    uint4 v[kU];
+  const uint32_t tid = threadIdx.x;
+  constexpr uint32_t nthr = kInterpThreads;
+  const uint64_t tile = static_cast<uint64_t>(nthr) * kU, stride = static_cast<uint64_t>(nctas) * tile;
+  auto load = [&](uint4* v, uint64_t first) {
+    if (first + kU * nthr <= nvec) {
+      const uint8_t* p = mc_src + (first + tid) * 16;
 #pragma unroll
-    for (int u = 0; u < kU; ++u) {
-      const uint64_t i = t0 + tid + static_cast<uint64_t>(u) * nthr;
-      if (i < nvec) v[u] = mm_load<DT>(mc_src + i * 16, op);
-    }
+      for (int u = 0; u < kU; ++u) v[u] = mm_load<DT>(p + u * nthr * 16, op);
+    } else {
 #pragma unroll
-    for (int u = 0; u < kU; ++u) {
-      const uint64_t i = t0 + tid + static_cast<uint64_t>(u) * nthr;
-      if (i < nvec) {
-        if (kToMulticast) ptx::mm_st_v4(dst + i * 16, v[u]); else ptx::st_v4(dst + i * 16, v[u]);
+      for (int u = 0; u < kU; ++u) {
+        const uint64_t i = first + tid + u * nthr;
+        v[u] = mm_load<DT>(mc_src + (i < nvec ? i : nvec - 1) * 16, op);
       }
     }
+  };
+  auto store = [&](const uint4* v, uint64_t first) {
+    uint8_t* p = dst + (first + tid) * 16;
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      if (first + tid + u * nthr < nvec) {
+        if (kToMulticast) ptx::mm_st_v4(p + u * nthr * 16, v[u]); else ptx::st_v4(p + u * nthr * 16, v[u]);
+      }
+    }
+  };
+  // Two tiles in flight, as in copy_range.
+  uint4 a[kU], b[kU];
+  uint64_t t0 = static_cast<uint64_t>(cta) * tile;
+  if (t0 >= nvec) return;
+  load(a, t0);
+  while (true) {
+    const uint64_t t1 = t0 + stride;
+    if (t1 < nvec) load(b, t1);
+    store(a, t0);
+    if (t1 >= nvec) break;
+    const uint64_t t2 = t1 + stride;
+    if (t2 < nvec) load(a, t2);
+    store(b, t1);
+    if (t2 >= nvec) break;
+    t0 = t2;
   }
 }
 

@@ -169,6 +169,7 @@ __device__ __forceinline__ void run_multimem(const Step& s, const SrcTable& t, u
   else mm_reduce_range<DT, true>(t.ptr[0], dst, s.bytes, s.red_op, cta, nctas);
 }
 
+template <int DT>
 __device__ __forceinline__ void run_step_data(const RankProgram& P, const Step& s, const SrcTable& t,
                                               uint8_t* dst, uint32_t cta, uint32_t nctas) {
   if (t.count == 0 || dst == nullptr) return;
@@ -183,25 +184,21 @@ __device__ __forceinline__ void run_step_data(const RankProgram& P, const Step& 
     case kStepMmReduce:
     case kStepMmAllreduce:
       if (!P.mc_data) return;            // the host never lowers multimem steps without NVLS
-      if (P.dtype == kF32) run_multimem<kF32>(s, t, dst, cta, nctas);
-      else if (P.dtype == kBF16) run_multimem<kBF16>(s, t, dst, cta, nctas);
-      else if (P.dtype == kF16) run_multimem<kF16>(s, t, dst, cta, nctas);
+      // multimem arithmetic exists for f32 / f16 / bf16 only; the host lowers fp8 to SM steps.
+      if constexpr (DT == kF32 || DT == kBF16 || DT == kF16) run_multimem<DT>(s, t, dst, cta, nctas);
       return;
     default:
       break;
   }
-  switch (P.dtype) {
-    case kF32: run_typed<kF32>(s, t, dst, cta, nctas); break;
-    case kF16: run_typed<kF16>(s, t, dst, cta, nctas); break;
-    case kBF16: run_typed<kBF16>(s, t, dst, cta, nctas); break;
-    case kE4M3: run_typed<kE4M3>(s, t, dst, cta, nctas); break;
-    default: run_typed<kE5M2>(s, t, dst, cta, nctas); break;
-  }
+  run_typed<DT>(s, t, dst, cta, nctas);
 }
 
 }  // namespace
 
-__global__ void __launch_bounds__(512, 1) plan_interp_kernel(const LaunchParams lp) {
+// One instance per element type: the data movers are inlined, so the register allocator sees
+// the whole loop nest (separately compiled movers spilled their load tiles at every call).
+template <int DT>
+__global__ void __launch_bounds__(kInterpThreads, 1) plan_interp_kernel(const LaunchParams lp) {
   const RankProgram& P = lp.programs[blockIdx.y];
   __shared__ uint32_t s_ok;
   __shared__ uint32_t s_chain;
@@ -288,7 +285,7 @@ __global__ void __launch_bounds__(512, 1) plan_interp_kernel(const LaunchParams 
     if (s.kind != kStepNoop && s.bytes) {
       if (threadIdx.x == 0) s_dst = describe_step(P, s, &s_src);
       __syncthreads();
-      run_step_data(P, s, s_src, s_dst, cta, chain.num_ctas);
+      run_step_data<DT>(P, s, s_src, s_dst, cta, chain.num_ctas);
     }
 
     // 4. completion barrier
@@ -319,7 +316,7 @@ __global__ void __launch_bounds__(512, 1) plan_interp_kernel(const LaunchParams 
   }
 }
 
-__global__ void __launch_bounds__(512, 1) scale_kernel(uint8_t* ptr, uint64_t bytes, uint32_t dtype, float scale) {
+__global__ void __launch_bounds__(kInterpThreads, 1) scale_kernel(uint8_t* ptr, uint64_t bytes, uint32_t dtype, float scale) {
   __shared__ SrcTable t;
   if (threadIdx.x == 0) { t.ptr[0] = ptr; t.count = 1; t.remote_mask = 0; }
   __syncthreads();
@@ -335,16 +332,32 @@ __global__ void __launch_bounds__(512, 1) scale_kernel(uint8_t* ptr, uint64_t by
 int launch_scale(void* ptr, uint64_t bytes, uint32_t dtype, float scale, void* stream) {
   if (bytes == 0) return 0;
   const uint32_t ctas = static_cast<uint32_t>(bytes / (256 << 10)) + 1;
-  scale_kernel<<<ctas > 128 ? 128 : ctas, 512, 0, static_cast<cudaStream_t>(stream)>>>(
+  scale_kernel<<<ctas > 128 ? 128 : ctas, kInterpThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<uint8_t*>(ptr), bytes, dtype, scale);
   return static_cast<int>(cudaGetLastError());
+}
+
+namespace {
+const void* interp_entry(uint32_t dtype) {
+  switch (dtype) {
+    case kF32: return reinterpret_cast<const void*>(plan_interp_kernel<kF32>);
+    case kF16: return reinterpret_cast<const void*>(plan_interp_kernel<kF16>);
+    case kBF16: return reinterpret_cast<const void*>(plan_interp_kernel<kBF16>);
+    case kE4M3: return reinterpret_cast<const void*>(plan_interp_kernel<kE4M3>);
+    default: return reinterpret_cast<const void*>(plan_interp_kernel<kE5M2>);
+  }
+}
+}  // namespace
+
+int set_mover_tuning(uint32_t word) {
+  return static_cast<int>(cudaMemcpyToSymbol(g_mover_tuning, &word, sizeof word));
 }
 
 int plan_interp_max_ctas(int threads) {
   int dev = 0, sms = 0, per_sm = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return 0;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, plan_interp_kernel, threads, 0) != cudaSuccess)
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, plan_interp_kernel<kF32>, threads, 0) != cudaSuccess)
     return 0;
   return sms * per_sm;
 }
@@ -352,15 +365,12 @@ int plan_interp_max_ctas(int threads) {
 int launch_plan_interp(const LaunchParams& params, const LaunchConfig& cfg, void* stream) {
   dim3 grid(cfg.ctas, cfg.virtual_ranks, 1), block(cfg.threads, 1, 1);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (cfg.cooperative) {
-    // Virtual ranks wait on one another inside a single launch: co-residency must be guaranteed.
-    LaunchParams copy = params;
-    void* args[] = {&copy};
-    return static_cast<int>(cudaLaunchCooperativeKernel(
-        reinterpret_cast<void*>(plan_interp_kernel), grid, block, args, 0, st));
-  }
-  plan_interp_kernel<<<grid, block, 0, st>>>(params);
-  return static_cast<int>(cudaGetLastError());
+  LaunchParams copy = params;
+  void* args[] = {&copy};
+  // Virtual ranks wait on one another inside a single launch: co-residency must be guaranteed.
+  if (cfg.cooperative)
+    return static_cast<int>(cudaLaunchCooperativeKernel(interp_entry(cfg.dtype), grid, block, args, 0, st));
+  return static_cast<int>(cudaLaunchKernel(interp_entry(cfg.dtype), grid, block, args, 0, st));
 }
 
 }  // namespace pccl

@@ -108,10 +108,16 @@ struct LaunchParams {
   uint32_t launch_index;           // number of earlier launches of this op since the last reset
 };
 
+// Threads per interpreter CTA.  256 rather than 512: the data movers keep two register tiles of
+// 16-byte loads in flight per thread, which needs the 255-register budget.
+constexpr uint32_t kInterpThreads = 256;
+
 // Host-callable launchers (defined in interp_kernel.cu).
-struct LaunchConfig { uint32_t ctas, threads, virtual_ranks; bool cooperative; };
+struct LaunchConfig { uint32_t ctas, threads, virtual_ranks; bool cooperative; uint32_t dtype; };
 int launch_plan_interp(const LaunchParams& params, const LaunchConfig& cfg, void* stream);
 int plan_interp_max_ctas(int threads);
+// Data-mover tuning: bit 0 = two register tiles in flight per thread, bit 1 = strong peer loads.
+int set_mover_tuning(uint32_t word);
 // ptr[0..bytes) *= scale, interpreted as `dtype` (the epilogue of an "avg" reduction).
 int launch_scale(void* ptr, uint64_t bytes, uint32_t dtype, float scale, void* stream);
 

@@ -73,6 +73,25 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// acc += sum over ranks of x_r[offset .. offset + 16).  All kW loads are issued unconditionally
+// before the first add (slots past the world re-read the own row and are not added): a
+// conditionally assigned register makes the compiler wait for each load in turn.
+template <int kW>
+__device__ __forceinline__ void pull_sum(const NormParams& p, uint64_t offset, float* acc) {
+  const int me = p.peers.rank, world = p.peers.world;
+  uint4 raw[kW];
+#pragma unroll
+  for (int r = 0; r < kW; ++r) raw[r] = ptx::ld_peer_v4(p.peers.base[r < world ? r : me] + p.x_off + offset);
+#pragma unroll
+  for (int r = 0; r < kW; ++r) {
+    if (r >= world) break;
+    float f[8];
+    unpack8(raw[r], f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] += f[i];
+  }
+}
+
 __global__ void __launch_bounds__(kThreadsNorm) ar_residual_rmsnorm_kernel(const NormParams p) {
   extern __shared__ float h_row[];            // hidden fp32 values of the current token
   __shared__ float warp_sums[kThreadsNorm / 32];
@@ -114,20 +133,12 @@ __global__ void __launch_bounds__(kThreadsNorm) ar_residual_rmsnorm_kernel(const
         unpack8(ptx::mm_ld_reduce_add_bf16(p.mc_base + p.x_off + row + v * 16), f);
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] += f[i];
+      } else if (world <= 2) {
+        pull_sum<2>(p, row + v * 16, acc);
+      } else if (world <= 4) {
+        pull_sum<4>(p, row + v * 16, acc);
       } else {
-        uint4 raw[8];
-#pragma unroll
-        for (int r = 0; r < 8; ++r)
-          if (r < world) raw[r] = r == me ? ptx::ld_local_v4(self + p.x_off + row + v * 16)
-                                          : ptx::ld_peer_v4(p.peers.base[r] + p.x_off + row + v * 16);
-#pragma unroll
-        for (int r = 0; r < 8; ++r)
-          if (r < world) {
-            float f[8];
-            unpack8(raw[r], f);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[i] += f[i];
-          }
+        pull_sum<8>(p, row + v * 16, acc);
       }
 #pragma unroll
       for (int i = 0; i < 8; ++i) { h_row[v * 8 + i] = acc[i]; ss += acc[i] * acc[i]; }

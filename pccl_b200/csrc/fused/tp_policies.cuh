@@ -98,6 +98,45 @@ struct ReduceScatterPolicy : PolicyDefaults {
   __device__ static int aux_ctas(const Params&) { return 0; }
   __device__ static void aux_main(const Params&, const Problem&, int, int, uint64_t, const volatile uint32_t*) {}
 
+  // out = sum over the sources' slots, rank order, fp32.  kRV vectors per thread and iteration and
+  // kW slots each are loaded before the first add.  Every load is unconditional (lanes past the
+  // end re-read the last vector, slots past the world re-read the own one): a conditionally
+  // assigned register makes the compiler wait for each load before it issues the next.
+  template <int kW>
+  __device__ static void sum_slots(const Params& p, const Problem& g, int me, int world, int row0, int col0,
+                                   int vec_per_row, int total) {
+    constexpr int kRV = kW >= 8 ? 2 : 4;
+    for (int i = threadIdx.x; i < total; i += blockDim.x * kRV) {
+      uint4 raw[kRV][kW];
+      int r[kRV], c[kRV];
+#pragma unroll
+      for (int u = 0; u < kRV; ++u) {
+        const int idx = min(i + u * static_cast<int>(blockDim.x), total - 1);
+        r[u] = row0 + idx / vec_per_row;
+        c[u] = col0 + (idx % vec_per_row) * 8;
+#pragma unroll
+        for (int s = 0; s < kW; ++s)
+          raw[u][s] = ptx::ld_local_v4(slot(p, g, me, s < world ? s : me, r[u]) + static_cast<uint64_t>(c[u]) * 2);
+      }
+#pragma unroll
+      for (int u = 0; u < kRV; ++u) {
+        if (i + u * static_cast<int>(blockDim.x) >= total) continue;
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+        for (int s = 0; s < kW; ++s) {
+          if (s >= world) break;
+          const uint32_t w[4] = {raw[u][s].x, raw[u][s].y, raw[u][s].z, raw[u][s].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc[2 * j] += __uint_as_float(w[j] << 16);
+            acc[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u);
+          }
+        }
+        *reinterpret_cast<uint4*>(p.out + static_cast<int64_t>(r[u]) * p.ldo + c[u]) = pack8_bf16(acc);
+      }
+    }
+  }
+
   // Reducer phase: item = (local row block, n tile); sum the world slots in rank order.
   __device__ static void finish(const Params& p, const Problem& g, int cta, int num_ctas, uint64_t deadline,
                                 const volatile uint32_t* abort_flag) {
@@ -120,42 +159,10 @@ struct ReduceScatterPolicy : PolicyDefaults {
       const int row0 = block * kBM, col0 = nb * kBN;
       const int rows = min(kBM, p.rows_per_rank - row0), cols = min(kBN, g.N - col0);
       const int vec_per_row = cols / 8;                    // 8 bf16 per 16 bytes (N % 8 == 0)
-      // Four vectors per thread and iteration, all slots loaded before the first add, so that
-      // up to 4 * world independent 16-byte loads are in flight per thread.
-      constexpr int kRV = 4;
       const int total = rows * vec_per_row;
-      for (int i = threadIdx.x; i < total; i += blockDim.x * kRV) {
-        uint4 raw[kRV][kMaxRanks];
-        int r[kRV], c[kRV];
-        bool live[kRV];
-#pragma unroll
-        for (int u = 0; u < kRV; ++u) {
-          const int idx = i + u * blockDim.x;
-          live[u] = idx < total;
-          r[u] = row0 + idx / vec_per_row;
-          c[u] = col0 + (idx % vec_per_row) * 8;
-#pragma unroll
-          for (int s = 0; s < kMaxRanks; ++s)
-            if (live[u] && s < world)
-              raw[u][s] = ptx::ld_local_v4(slot(p, g, me, s, r[u]) + static_cast<uint64_t>(c[u]) * 2);
-        }
-#pragma unroll
-        for (int u = 0; u < kRV; ++u) {
-          if (!live[u]) continue;
-          float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll
-          for (int s = 0; s < kMaxRanks; ++s) {
-            if (s >= world) break;
-            const uint32_t w[4] = {raw[u][s].x, raw[u][s].y, raw[u][s].z, raw[u][s].w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              acc[2 * j] += __uint_as_float(w[j] << 16);
-              acc[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u);
-            }
-          }
-          *reinterpret_cast<uint4*>(p.out + static_cast<int64_t>(r[u]) * p.ldo + c[u]) = pack8_bf16(acc);
-        }
-      }
+      if (world <= 2) sum_slots<2>(p, g, me, world, row0, col0, vec_per_row, total);
+      else if (world <= 4) sum_slots<4>(p, g, me, world, row0, col0, vec_per_row, total);
+      else sum_slots<8>(p, g, me, world, row0, col0, vec_per_row, total);
     }
   }
 };
@@ -242,9 +249,11 @@ struct AllGatherPolicy : PolicyDefaults {
       constexpr int kU = 16;                               // 16-byte loads in flight per thread
       for (uint64_t v = threadIdx.x; v < vecs; v += static_cast<uint64_t>(blockDim.x) * kU) {
         uint4 t[kU];
+        // Unconditional loads (lanes past the end re-read the last vector) so that all kU are in
+        // flight at once; only the stores are predicated.
 #pragma unroll
         for (int u = 0; u < kU; ++u)
-          if (v + u * blockDim.x < vecs) t[u] = ptx::ld_peer_v4(from + (v + u * blockDim.x) * 16);
+          t[u] = ptx::ld_peer_v4(from + min(v + u * blockDim.x, vecs - 1) * 16);
 #pragma unroll
         for (int u = 0; u < kU; ++u)
           if (v + u * blockDim.x < vecs) ptx::st_v4(to + (v + u * blockDim.x) * 16, t[u]);

@@ -53,12 +53,13 @@ __device__ __forceinline__ void red_relaxed_gpu_add(uint32_t* p, uint32_t v) {
 __device__ __forceinline__ void fence_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 __device__ __forceinline__ void fence_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
 
-// 16-byte data loads.  Peer memory is read with relaxed.sys so that a value
-// rewritten by the peer between two steps is never served from a stale L1 line;
-// local memory written earlier in the same launch by other SMs is read at L2 (.cg).
+// 16-byte data loads.  Both kinds are weak loads served at L2 (.cg bypasses L1, so a line
+// rewritten between two steps is never read stale from L1); ordering against the producer
+// comes from the acquire on the signal that precedes them.  Weak loads pipeline freely: a
+// thread keeps many in flight, which strong (relaxed.sys) loads did not do in measurement.
 __device__ __forceinline__ uint4 ld_peer_v4(const void* p) {
   uint4 v;
-  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
   return v;
 }

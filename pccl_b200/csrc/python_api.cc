@@ -13,6 +13,7 @@
 #include "common/util.h"
 #include "engine/engine.h"
 #include "fused/fused_ops.h"
+namespace pccl { void bind_rdma(pybind11::module_& m); }
 
 namespace py = pybind11;
 using namespace pccl;
@@ -184,4 +185,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_static("registerOpt", &Environs::register_option);
 
   bind_fused_ops(m);
+  bind_rdma(m);
 }

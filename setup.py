@@ -18,6 +18,11 @@ sources = sorted(glob.glob(os.path.join(CSRC, "**", "*.cc"), recursive=True)
 
 os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")
 
+# The verbs transport of the RDMA executor is opt-in (PCCL_RDMA=1) and needs the verbs headers.
+RDMA = os.environ.get("PCCL_RDMA", "0") == "1" and os.path.exists("/usr/include/infiniband/verbs.h")
+rdma_macros = [("PCCL_RDMA_ENABLED", None)] if RDMA else []
+rdma_libs = ["ibverbs"] if RDMA else []
+
 setup(
     name="pccl_b200",
     version="0.3.0",
@@ -27,6 +32,8 @@ setup(
             name="pccl_b200.engine_c",
             sources=sources,
             include_dirs=[os.path.join(ROOT, CSRC)],
+            define_macros=rdma_macros,
+            libraries=rdma_libs,
             # Link the shared libstdc++ explicitly: on images whose compiler directory holds only
             # libstdc++.a the driver would otherwise embed a second, uninitialised copy of the
             # iostream/locale state into the extension.
