@@ -49,7 +49,7 @@ def main():
     ap.add_argument("--tokens-per-rank", type=int, default=1024)
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--k-local", type=int, default=1792)
-    ap.add_argument("--copy-ctas", type=int, default=20)
+    ap.add_argument("--copy-ctas", type=int, default=0)
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
@@ -115,6 +115,36 @@ def main():
                     "fused_ms": round(t_fused, 4), "unfused_nccl_cublas_ms": round(t_unfused, 4),
                     "cublas_gemm_only_ms": round(t_gemm, 4), "speedup_vs_unfused": round(t_unfused / t_fused, 3),
                     "roofline_ms": round(roof_ms, 4), "fraction_of_roofline": round(roof_ms / t_fused, 3)})
+    # all-reduce + residual + RMSNorm (decode, small prefill, large prefill token counts)
+    from pccl_b200.ops import AllReduceResidualRMSNorm
+    hbm_gbs = json.load(open(peaks_path))["hbm_gbs"] if os.path.exists(peaks_path) else 6650.0
+    for tokens in (1, 128, 8192):
+        gamma = torch.ones(h, device="cuda", dtype=torch.bfloat16)
+        part = torch.randn(tokens, h, device="cuda").to(torch.bfloat16)
+        res = torch.randn(tokens, h, device="cuda").to(torch.bfloat16)
+        for use_nvls in ("force", False):
+            op = AllReduceResidualRMSNorm(tokens, h, use_nvls=use_nvls)
+            op.x.copy_(part)
+            op.residual.copy_(res)
+            t_fused = timed(lambda: op(gamma), args.iters, flush)
+            gemm.check()
+            buf, resid = part.clone(), res.clone()
+
+            def unfused_norm():
+                dist.all_reduce(buf)
+                resid.add_(buf)
+                return torch.nn.functional.rms_norm(resid, (h,), gamma, 1e-5)
+
+            t_unfused = timed(unfused_norm, args.iters, flush)
+            # bytes that must cross NVLink per GPU (two-shot: send and receive (W-1)/W of x, then of y and h)
+            link_bytes = (world - 1) / world * tokens * h * 2 * 3
+            local_bytes = tokens * h * 2 * 4 / world
+            roof_ms = max(link_bytes / (link_gbs * 1e9), local_bytes / (hbm_gbs * 1e9)) * 1e3
+            results.append({"op": "ar_residual_rmsnorm", "tokens": tokens, "hidden": h, "world": world,
+                            "path": "nvls" if use_nvls else "peer", "fused_ms": round(t_fused, 4),
+                            "unfused_nccl_torch_ms": round(t_unfused, 4),
+                            "speedup_vs_unfused": round(t_unfused / t_fused, 3),
+                            "roofline_ms": round(roof_ms, 5), "fraction_of_roofline": round(roof_ms / t_fused, 3)})
     if rank == 0:
         for r in results:
             print(json.dumps(r), flush=True)

@@ -79,7 +79,7 @@ void bind_fused_ops(py::module_& m) {
                                 ctas);
         },
         py::arg("gathered_off"), py::arg("m"), py::arg("k"), py::arg("w"), py::arg("out"), py::arg("flags_off"),
-        py::arg("ready"), py::arg("epoch"), py::arg("copy_ctas") = 20, py::arg("ctas") = 0);
+        py::arg("ready"), py::arg("epoch"), py::arg("copy_ctas") = 0, py::arg("ctas") = 0);
   // Fused all-reduce + residual + RMSNorm over symmetric buffers.
   f.def("ar_residual_rmsnorm",
         [](int64_t x_off, int64_t y_off, int64_t res_off, int64_t flags_off, const torch::Tensor& gamma,

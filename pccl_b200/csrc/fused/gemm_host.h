@@ -45,7 +45,7 @@ void gemm_reduce_scatter(const PeerBases& peers, const MatrixDesc& x, const Matr
 // u32[2 * world]; ready: local zero-initialised u32[M / 128].
 void all_gather_gemm(const PeerBases& peers, uint64_t gathered_off, int M, int K, const MatrixDesc& w,
                      uint64_t flags_off, uint32_t* ready, void* out, int64_t ldc, uint32_t epoch,
-                     cudaStream_t stream, int copy_ctas = 20, int ctas = 0, uint64_t timeout_ms = 2000);
+                     cudaStream_t stream, int copy_ctas = 0, int ctas = 0, uint64_t timeout_ms = 2000);
 
 // Fused all-reduce + residual add + RMSNorm.  x, y and the residual h are [tokens][hidden] bf16
 // at the given symmetric-heap offsets on every rank; flags_off: symmetric u32[2 * world] (zeroed

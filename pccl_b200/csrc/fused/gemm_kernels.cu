@@ -1,6 +1,7 @@
 // Launchers of the tcgen05 GEMM kernels: tensor-map construction and launch.
 #include <cuda.h>
 
+#include <algorithm>
 #include <mutex>
 
 #include "../engine/cuda_driver.h"
@@ -172,12 +173,30 @@ void all_gather_gemm(const PeerBases& peers, uint64_t gathered_off, int M, int K
   p.ldc = ldc;
   p.rows_per_rank = M / peers.world;
   p.blocks_per_rank = p.rows_per_rank / kBM;
-  p.copy_ctas = peers.world > 1 ? copy_ctas : 0;
+  // Copier CTAs: by default the SMs that the GEMM tiles leave idle (at least 16, at most 48).  When
+  // there are fewer remote row blocks than copiers, a block is split into `copy_parts` pieces and
+  // the copier count is trimmed to a whole number of blocks' worth, so that one round of copying
+  // covers everything and no copier runs a second, lonely round.
+  const int sms = sm_count();
   const int remote_blocks = (peers.world - 1) * p.blocks_per_rank;
-  p.copy_parts = p.copy_ctas > remote_blocks ? (p.copy_ctas + remote_blocks - 1) / remote_blocks : 1;
+  if (peers.world == 1) {
+    p.copy_ctas = 0;
+    p.copy_parts = 1;
+  } else {
+    const int tiles = ((M + kBM - 1) / kBM) * ((w.rows + kBN - 1) / kBN);
+    // More tiles than SMs: the GEMM runs several waves and the copy must keep ahead of it; a
+    // copier pulls roughly 16 GB/s, so give it 32 SMs.
+    int want = copy_ctas > 0 ? copy_ctas : (tiles >= sms ? 32 : std::min(48, std::max(16, sms - tiles)));
+    if (want >= remote_blocks) {
+      p.copy_parts = want / remote_blocks;
+      want = p.copy_parts * remote_blocks;
+    } else {
+      p.copy_parts = 1;
+    }
+    p.copy_ctas = want;
+  }
   p.epoch = epoch;
   MatrixDesc a{peers.base[peers.rank] + gathered_off, M, K, K};
-  const int sms = sm_count();
   int grid = ctas > 0 ? ctas : sms;
   launch<AllGatherPolicy>(a, w, p, grid, timeout_ms, stream, p.copy_ctas);
 }

@@ -32,7 +32,7 @@ _is_power_of_2 = is_power_of_two
 
 #: message-size crossovers (bytes) on a switched fabric, by world size: (one-shot up to, two-shot up to)
 SWITCHED_CROSSOVERS: Dict[int, tuple] = {
-    2: (512 * 1024, 16 * 1024 * 1024),
+    2: (4 * 1024 * 1024, 1 << 62),       # two ranks: in-switch reduction moves 1.5x the bytes of two-shot
     4: (256 * 1024, 8 * 1024 * 1024),
     8: (128 * 1024, 4 * 1024 * 1024),
 }

@@ -58,7 +58,7 @@ class GemmReduceScatter:
 
 
 class AllGatherGemm:
-    def __init__(self, m: int, n_local: int, k: int, group=None, copy_ctas: int = 20):
+    def __init__(self, m: int, n_local: int, k: int, group=None, copy_ctas: int = 0):
         self.engine = _engine.get_engine()
         self.world, self.rank = self.engine.world, self.engine.rank
         if m % (self.world * _BLOCK):
@@ -95,13 +95,17 @@ class AllReduceResidualRMSNorm:
 
     ``self.x`` (this rank's partial, written by the caller), ``self.residual`` (read and
     updated in place) and ``self.y`` (result) are ``[tokens, hidden]`` bf16 tensors in
-    symmetric memory owned by the operator.
+    symmetric memory owned by the operator.  ``use_nvls``: True = in-switch reduction when the
+    engine has multicast and there are more than two ranks, "force" = whenever it has multicast,
+    False = peer loads / stores only.
     """
 
     def __init__(self, tokens: int, hidden: int, eps: float = 1e-5, group=None, use_nvls: bool = True):
         self.engine = _engine.get_engine()
         self.world, self.rank = self.engine.world, self.engine.rank
-        self.tokens, self.hidden, self.eps, self.use_nvls = tokens, hidden, eps, use_nvls
+        # With two ranks the in-switch reduction moves 1.5x the bytes of the peer path: keep it for W > 2.
+        self.tokens, self.hidden, self.eps = tokens, hidden, eps
+        self.use_nvls = bool(use_nvls) and (self.world > 2 or use_nvls == "force")
         self.x = self.engine.empty_symmetric((tokens, hidden), torch.bfloat16)
         self.y = self.engine.empty_symmetric((tokens, hidden), torch.bfloat16)
         self.residual = self.engine.empty_symmetric((tokens, hidden), torch.bfloat16)

@@ -145,7 +145,7 @@ def main():
     from pccl_b200.ops import AllReduceResidualRMSNorm
     hidden = 4096
     for tokens in (1, 128, 1024):
-        for use_nvls in (True, False):
+        for use_nvls in ("force", False):
             gen = torch.Generator(device="cuda").manual_seed(100 + rank)
             xp = torch.randn(tokens, hidden, device="cuda", generator=gen).to(torch.bfloat16)
             gen0 = torch.Generator(device="cuda").manual_seed(5)          # identical on every rank
