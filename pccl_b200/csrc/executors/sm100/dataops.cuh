@@ -169,7 +169,7 @@ __device__ __forceinline__ Span make_span(const SrcTable& t, const uint8_t* dst,
 }
 
 // Tuning word set by the host (PCCL_MOVER_TUNING): bit 0 = keep two register tiles in flight per
-// thread.  Off by default: with unconditional loads one tile of 8 vectors per thread already
+// thread in copy / reduce steps; bit 1 = only one tile in multimem steps.  Off by default: with unconditional loads one tile of 8 vectors per thread already
 // saturates NVLink, and the second tile measured a few percent slower.
 __constant__ uint32_t g_mover_tuning = 0;
 
@@ -426,10 +426,15 @@ __device__ __noinline__ void mm_reduce_range(const uint8_t* mc_src, uint8_t* dst
       }
     }
   };
-  // Two tiles in flight, as in copy_range.
+  // Two tiles in flight by default (in-switch reductions have a longer round trip than peer
+  // loads); bit 1 of the tuning word selects one tile.
   uint4 a[kU], b[kU];
   uint64_t t0 = static_cast<uint64_t>(cta) * tile;
   if (t0 >= nvec) return;
+  if (g_mover_tuning & 2u) {
+    for (; t0 < nvec; t0 += stride) { load(a, t0); store(a, t0); }
+    return;
+  }
   load(a, t0);
   while (true) {
     const uint64_t t1 = t0 + stride;

@@ -98,6 +98,22 @@ void bind_fused_ops(py::module_& m) {
         py::arg("x_off"), py::arg("y_off"), py::arg("res_off"), py::arg("flags_off"), py::arg("gamma"),
         py::arg("cta_counter"), py::arg("tokens"), py::arg("hidden"), py::arg("eps"), py::arg("epoch"),
         py::arg("use_nvls") = true, py::arg("ctas") = 0);
+  // Packet-protocol all-reduce (sum) for small messages; out may be the input tensor.
+  f.def("allreduce_ll",
+        [](const torch::Tensor& in, torch::Tensor& out, int64_t buf_off, int64_t capacity_bytes, int64_t epoch) {
+          TORCH_CHECK(in.is_cuda() && out.is_cuda() && in.is_contiguous() && out.is_contiguous() &&
+                          in.scalar_type() == out.scalar_type() && in.numel() == out.numel(),
+                      "allreduce_ll: contiguous CUDA tensors of one dtype and size");
+          int dtype = -1;
+          if (in.scalar_type() == torch::kFloat32) dtype = 0;
+          else if (in.scalar_type() == torch::kFloat16) dtype = 1;
+          else if (in.scalar_type() == torch::kBFloat16) dtype = 2;
+          TORCH_CHECK(dtype >= 0, "allreduce_ll: float32, float16 or bfloat16");
+          gemm::allreduce_ll(peer_bases(), static_cast<uint64_t>(buf_off), static_cast<uint64_t>(capacity_bytes),
+                             in.data_ptr(), out.data_ptr(), static_cast<uint64_t>(in.nbytes()), dtype,
+                             static_cast<uint32_t>(epoch), c10::cuda::getCurrentCUDAStream().stream());
+        },
+        py::arg("input"), py::arg("output"), py::arg("buf_off"), py::arg("capacity_bytes"), py::arg("epoch"));
   // MoE router on its own: top-2 expert indices, renormalised gates, the row each choice claims
   // in its expert's batch, and the per-expert token counts.  scratch: int32[experts + 1].
   f.def("moe_route",

@@ -54,6 +54,12 @@ void ar_residual_rmsnorm(const PeerBases& peers, uint8_t* mc_base, uint64_t x_of
                          uint64_t flags_off, const void* gamma, uint32_t* cta_counter, int tokens, int hidden,
                          float eps, uint32_t epoch, cudaStream_t stream, int ctas = 0, uint64_t timeout_ms = 2000);
 
+// Small-message all-reduce (sum) with flag-carrying packets; in / out are ordinary device tensors
+// (out may alias in).  buf_off: symmetric uint4 [2][world][capacity_bytes / 8], zeroed once before
+// the first call on every rank.  dtype: 0 f32, 1 f16, 2 bf16.  epoch = 1, 2, 3, ... per call.
+void allreduce_ll(const PeerBases& peers, uint64_t buf_off, uint64_t capacity_bytes, const void* in, void* out,
+                  uint64_t bytes, int dtype, uint32_t epoch, cudaStream_t stream, uint64_t timeout_ms = 2000);
+
 // ---- expert-parallel MoE feed-forward (top-2 routing) ------------------------------------------------
 // Symmetric-heap offsets (identical on every rank) of the buffers the three kernels share.
 // regions = (experts / world) * world, region = local_expert * world + source rank.

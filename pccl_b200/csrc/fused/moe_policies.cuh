@@ -133,7 +133,7 @@ struct MoeUpPolicy : PolicyDefaults {
   __device__ static int64_t row_pitch(const Params& p, const Problem&) { return p.ldh * 2; }
   __device__ static void tile_done(const Params&, const Problem&, int, int) {}
   __device__ static int aux_ctas(const Params&) { return 0; }
-  __device__ static void aux_main(const Params&, const Problem&, int, int, uint64_t, const volatile uint32_t*) {}
+  __device__ static void aux_main(const Params&, const Problem&, int, int, uint64_t, const volatile uint32_t*, uint8_t*) {}
   __device__ static void finish(const Params&, const Problem&, int, int, uint64_t, const volatile uint32_t*) {}
 };
 
@@ -184,7 +184,7 @@ struct MoeDownPolicy : PolicyDefaults {
   __device__ static int64_t row_pitch(const Params&, const Problem&) { return 0; }
   __device__ static void tile_done(const Params&, const Problem&, int, int) {}
   __device__ static int aux_ctas(const Params&) { return 0; }
-  __device__ static void aux_main(const Params&, const Problem&, int, int, uint64_t, const volatile uint32_t*) {}
+  __device__ static void aux_main(const Params&, const Problem&, int, int, uint64_t, const volatile uint32_t*, uint8_t*) {}
 
   // "All my expert outputs are delivered" -> every rank (posted by the last CTA to get here);
   // then wait for every expert rank and add the two expert rows of each local token.

@@ -96,7 +96,7 @@ struct ReduceScatterPolicy : PolicyDefaults {
     }
   }
   __device__ static int aux_ctas(const Params&) { return 0; }
-  __device__ static void aux_main(const Params&, const Problem&, int, int, uint64_t, const volatile uint32_t*) {}
+  __device__ static void aux_main(const Params&, const Problem&, int, int, uint64_t, const volatile uint32_t*, uint8_t*) {}
 
   // out = sum over the sources' slots, rank order, fp32.  kRV vectors per thread and iteration and
   // kW slots each are loaded before the first add.  Every load is unconditional (lanes past the
@@ -214,9 +214,19 @@ struct AllGatherPolicy : PolicyDefaults {
   // local gathered matrix, fence, publish ready[mb].  Finally each source is told that its shard
   // has been read, and CTA 0 waits until every peer has read this rank's shard, so the caller
   // may overwrite its input when the kernel is done.
+  static constexpr int kCopyStages = 12, kCopyLag = 8;     // 8 loads of 16 KB in flight, 4 stores pending
+  static constexpr uint32_t kCopyChunk = 16 * 1024;
+
   __device__ static void aux_main(const Params& p, const Problem& g, int cta, int num_ctas, uint64_t deadline,
-                                  const volatile uint32_t* abort_flag) {
+                                  const volatile uint32_t* abort_flag, uint8_t* smem) {
     __shared__ uint32_t ok_flag;
+    __shared__ uint64_t bars[kCopyStages];
+    if (threadIdx.x == 0) {
+      for (int s = 0; s < kCopyStages; ++s) ptx::mbar_init(&bars[s], 1);
+      ptx::mbar_init_fence();
+    }
+    __syncthreads();
+    uint32_t chunk_base = 0;                                // chunks issued by this CTA so far (stage phases)
     const int me = p.peers.rank, world = p.peers.world;
     uint32_t* my_flags = reinterpret_cast<uint32_t*>(p.peers.base[me] + p.flags_off);
     if (cta == 0 && static_cast<int>(threadIdx.x) < world && static_cast<int>(threadIdx.x) != me) {
@@ -246,19 +256,53 @@ struct AllGatherPolicy : PolicyDefaults {
       from += part * per_part * 16;
       to += part * per_part * 16;
       const uint64_t vecs = part * per_part >= block_vecs ? 0 : min(per_part, block_vecs - part * per_part);
-      constexpr int kU = 16;                               // 16-byte loads in flight per thread
-      for (uint64_t v = threadIdx.x; v < vecs; v += static_cast<uint64_t>(blockDim.x) * kU) {
-        uint4 t[kU];
-        // Unconditional loads (lanes past the end re-read the last vector) so that all kU are in
-        // flight at once; only the stores are predicated.
-#pragma unroll
-        for (int u = 0; u < kU; ++u)
-          t[u] = ptx::ld_peer_v4(from + min(v + u * blockDim.x, vecs - 1) * 16);
-#pragma unroll
-        for (int u = 0; u < kU; ++u)
-          if (v + u * blockDim.x < vecs) ptx::st_v4(to + (v + u * blockDim.x) * 16, t[u]);
+      // One thread moves the part with bulk copies: peer memory -> shared memory (completing on an
+      // mbarrier) -> local gathered matrix, kCopyLag loads in flight.  No SM load/store loop, and
+      // never a multicast: each copier fetches only its own part.
+      if (threadIdx.x == 0 && vecs > 0) {
+        const uint64_t bytes = vecs * 16;
+        const uint32_t chunks = static_cast<uint32_t>((bytes + kCopyChunk - 1) / kCopyChunk);
+        bool ok = true;
+        uint32_t loaded = 0;                               // chunks whose load has been issued
+        for (uint32_t i = 0; i < chunks + kCopyLag && ok; ++i) {
+          if (i >= static_cast<uint32_t>(kCopyLag)) {      // consume chunk c: wait for its load, store it
+            const uint32_t c = i - kCopyLag, seq = chunk_base + c;
+            const uint32_t len = static_cast<uint32_t>(min(static_cast<uint64_t>(kCopyChunk), bytes - static_cast<uint64_t>(c) * kCopyChunk));
+            if (!ptx::mbar_wait(&bars[seq % kCopyStages], (seq / kCopyStages) & 1u, deadline, abort_flag)) {
+              ok = false;
+              break;
+            }
+            ptx::bulk_store(to + static_cast<uint64_t>(c) * kCopyChunk, smem + (seq % kCopyStages) * kCopyChunk, len);
+            ptx::bulk_commit();
+          }
+          if (i < chunks) {                                // produce chunk i into its stage
+            const uint32_t seq = chunk_base + i;
+            const uint32_t len = static_cast<uint32_t>(min(static_cast<uint64_t>(kCopyChunk), bytes - static_cast<uint64_t>(i) * kCopyChunk));
+            // The store that last read this stage (kCopyStages chunks ago) must be done reading.
+            ptx::bulk_wait_read<kCopyStages - kCopyLag>();
+            ptx::mbar_expect_tx(&bars[seq % kCopyStages], len);
+            ptx::bulk_load(smem + (seq % kCopyStages) * kCopyChunk, from + static_cast<uint64_t>(i) * kCopyChunk, len,
+                           &bars[seq % kCopyStages]);
+            loaded = i + 1;
+          }
+        }
+        if (!ok) {
+          // Leaving early: wait (bounded) for the loads still writing this CTA's shared memory.
+          raise_error(g, kErrPolicyWait, 8);
+          const uint64_t drain = ptx::globaltimer() + 50000000ull;
+          uint32_t no_abort = 0;
+          for (uint32_t c = loaded > static_cast<uint32_t>(kCopyStages) ? loaded - kCopyStages : 0; c < loaded; ++c) {
+            const uint32_t seq = chunk_base + c;
+            ptx::mbar_wait(&bars[seq % kCopyStages], (seq / kCopyStages) & 1u, drain, &no_abort);
+          }
+        }
+        ptx::bulk_wait_all();
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+        chunk_base += chunks;
+        if (!ok) ok_flag = 0;
       }
       __syncthreads();
+      if (!ok_flag) return;
       if (threadIdx.x == 0) {
         ptx::fence_gpu();
         ptx::red_release_gpu_add(p.ready + mb, 1u);

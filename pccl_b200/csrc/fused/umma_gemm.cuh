@@ -103,7 +103,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   // Auxiliary CTAs (e.g. the copiers of all-gather -> GEMM) take no part in the GEMM pipeline.
   const int aux = Policy::aux_ctas(p);
   if (static_cast<int>(blockIdx.x) < aux) {
-    Policy::aux_main(p, g, blockIdx.x, aux, deadline, abort_flag);
+    Policy::aux_main(p, g, blockIdx.x, aux, deadline, abort_flag, smem);
     return;
   }
   const int cta = blockIdx.x - aux, num_ctas = gridDim.x - aux;
@@ -343,7 +343,7 @@ struct StorePolicy : PolicyDefaults {
   __device__ static int64_t row_pitch(const Params& p, const Problem&) { return p.ldc * 2; }
   __device__ static void tile_done(const Params&, const Problem&, int, int) {}
   __device__ static int aux_ctas(const Params&) { return 0; }
-  __device__ static void aux_main(const Params&, const Problem&, int, int, uint64_t, const volatile uint32_t*) {}
+  __device__ static void aux_main(const Params&, const Problem&, int, int, uint64_t, const volatile uint32_t*, uint8_t*) {}
   __device__ static void finish(const Params&, const Problem&, int, int, uint64_t, const volatile uint32_t*) {}
 };
 

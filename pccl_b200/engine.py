@@ -74,6 +74,9 @@ class Engine:
 
     # -- reference verbs ------------------------------------------------------------------
     def register_operation(self, name: str, filename: str) -> bool:
+        """``filename``: path of a plan file (the reference's contract) or the plan JSON text itself."""
+        if str(filename).lstrip().startswith("{"):
+            return self.register_operation_from_string(name, str(filename))
         return self._engine.regOp(name, str(filename))
 
     def register_operation_from_string(self, name: str, plan_json: str) -> bool:
@@ -150,6 +153,8 @@ class CpuEngine:
         self.group = None
 
     def register_operation(self, name: str, filename: str) -> bool:
+        if str(filename).lstrip().startswith("{"):
+            return self.register_operation_from_string(name, str(filename))
         try:
             with open(filename) as handle:
                 return self.register_operation_from_string(name, handle.read())

@@ -5,3 +5,10 @@ from .collectives import (all_gather, all_reduce, all_to_all, default_channels, 
 
 __all__ = ["init", "all_reduce", "all_gather", "reduce_scatter", "all_to_all", "working_tensor",
            "ensure_plan", "default_channels", "registered_plans", "synchronize"]
+
+
+def __getattr__(name):
+    if name in ("ColumnParallelLinear", "RowParallelLinear", "ExpertParallelMoE", "GradientBuckets"):
+        from . import layers
+        return getattr(layers, name)
+    raise AttributeError(name)

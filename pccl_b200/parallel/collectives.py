@@ -47,7 +47,35 @@ def init(group: Optional[dist.ProcessGroup] = None):
         _engine.initialize_engine(group)
     else:
         _engine.get_engine()
+    _setup_ll(group)
     return _engine.get_engine()
+
+
+#: largest message (bytes) the packet-protocol all-reduce takes; its payload doubles on the wire
+LL_MAX_BYTES = int(os.environ.get("PCCL_LL_MAX_BYTES", 256 << 10))
+
+
+def _setup_ll(group) -> None:
+    """Receive buffer of the small-message all-reduce: [2 parities][world][2 x LL_MAX_BYTES], zeroed."""
+    eng = _engine.get_engine()
+    _state["ll"] = None
+    if _state["world"] < 2 or not torch.cuda.is_available() or not hasattr(eng, "empty_symmetric") \
+            or LL_MAX_BYTES <= 0 or os.environ.get("PCCL_EXECUTOR") == "cpu":
+        return
+    buf = eng.empty_symmetric((2 * _state["world"] * 2 * LL_MAX_BYTES,), torch.uint8)
+    buf.zero_()
+    torch.cuda.synchronize()
+    dist.barrier(group=group)
+    _state["ll"] = {"buf": buf, "epoch": 0, "native": _engine.load_native().fused}
+
+
+def _ll_eligible(tensor: torch.Tensor, op: str, algorithm: Optional[str]) -> bool:
+    ll = _state.get("ll")
+    if ll is None or op != "sum" or algorithm not in (None, "ll"):
+        return False
+    nbytes = tensor.numel() * tensor.element_size()
+    return (tensor.is_cuda and tensor.is_contiguous() and nbytes % 8 == 0 and 0 < nbytes <= LL_MAX_BYTES
+            and tensor.data_ptr() % 8 == 0 and tensor.dtype in (torch.float32, torch.float16, torch.bfloat16))
 
 
 def working_tensor(shape, dtype=torch.float32) -> torch.Tensor:
@@ -127,7 +155,19 @@ def ensure_plan(kind: str, numel: int, dtype: torch.dtype, algorithm: Optional[s
 
 def all_reduce(tensor: torch.Tensor, op: str = "sum", algorithm: Optional[str] = None,
                channels: Optional[int] = None, async_op: bool = False) -> torch.Tensor:
-    """In-place all-reduce of ``tensor`` (sum / max / min / avg)."""
+    """In-place all-reduce of ``tensor`` (sum / max / min / avg).
+
+    Sums of up to ``LL_MAX_BYTES`` go through the packet-protocol kernel (no plan, no staging copy,
+    asynchronous on the current stream) unless an algorithm is forced.
+    """
+    if _ll_eligible(tensor, op, algorithm):
+        ll = _state["ll"]
+        ll["epoch"] += 1
+        ll["native"].allreduce_ll(tensor, tensor, ll["buf"].heap_offset, LL_MAX_BYTES, ll["epoch"])
+        return tensor
+    if algorithm == "ll":
+        raise ValueError("the packet-protocol all-reduce takes contiguous f32/f16/bf16 sums of at most "
+                         f"{LL_MAX_BYTES} bytes")
     name = ensure_plan("allreduce", tensor.numel(), tensor.dtype, algorithm, channels, op)
     run = _engine.execute_operation_async if async_op else _engine.execute_operation
     run(name, tensor, tensor)

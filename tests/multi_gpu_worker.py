@@ -99,6 +99,29 @@ def main():
     assert len(ce_ops) >= 3, f"copy-engine executor not used: {ce_ops}"
     report["copy_engine_ops"] = len(ce_ops)
 
+    # packet-protocol small-message all-reduce: ordinary (non-symmetric) tensors, in place, many calls
+    for dtype in (torch.float32, torch.bfloat16, torch.float16):
+        for numel in (4, 1024, 20000, 65536):
+            for call in range(3):
+                gen = torch.Generator(device="cuda").manual_seed(1000 * call + 17 * rank + numel)
+                x = torch.randn(numel, device="cuda", generator=gen).to(dtype)
+                ref = x.float().clone()
+                dist.all_reduce(ref)
+                y = pp.all_reduce(x.clone(), algorithm="ll")
+                torch.cuda.synchronize()
+                gemm_mod = __import__("pccl_b200.ops.gemm", fromlist=["check"])
+                gemm_mod.check()
+                atol = 1e-5 if dtype == torch.float32 else 0.06
+                torch.testing.assert_close(y.float(), ref, atol=atol, rtol=2e-2,
+                                           msg=lambda t: f"ll allreduce {dtype} n={numel} call {call} rank {rank}: {t}")
+        report["checked"] += 1
+    # every rank must hold bit-identical results (sums are taken in rank order)
+    x = torch.randn(4096, device="cuda", generator=torch.Generator(device="cuda").manual_seed(5 + rank))
+    y = pp.all_reduce(x.clone(), algorithm="ll")
+    gathered = [torch.empty_like(y) for _ in range(world)]
+    dist.all_gather(gathered, y)
+    assert all(torch.equal(gathered[0], g) for g in gathered), "ll allreduce differs between ranks"
+
     # max / avg through the API
     x = torch.randn(world * 4096, device="cuda", generator=torch.Generator(device="cuda").manual_seed(rank))
     ref = x.clone(); dist.all_reduce(ref, op=dist.ReduceOp.MAX)
@@ -193,6 +216,40 @@ def main():
             scale = ref[same].abs().max().item()
             assert err <= 2e-2 * scale + 1e-3, f"moe T={tokens} call {call} rank {rank}: error {err} vs {scale}"
         report["checked"] += 1
+
+    # ---- model blocks and data-parallel gradient buckets ----
+    from pccl_b200.models import TensorParallelMLP
+    from pccl_b200.parallel.layers import GradientBuckets
+    tokens, hid, f_local = world * 128, 512, 256
+    gen0 = torch.Generator(device="cuda").manual_seed(21)                 # identical on every rank
+    wgu_all = [(torch.randn(2 * f_local, hid, device="cuda", generator=gen0) * hid ** -0.5).to(torch.bfloat16)
+               for _ in range(world)]
+    wd_all = [(torch.randn(hid, f_local, device="cuda", generator=gen0) * f_local ** -0.5).to(torch.bfloat16)
+              for _ in range(world)]
+    x_full = torch.randn(tokens, hid, device="cuda", generator=gen0).to(torch.bfloat16)
+    mlp = TensorParallelMLP(tokens, hid, f_local, wgu_all[rank], wd_all[rank])
+    rows = tokens // world
+    y = mlp(x_full[rank * rows:(rank + 1) * rows].contiguous())
+    torch.cuda.synchronize()
+    gemm.check()
+    ref = TensorParallelMLP.reference(x_full, wgu_all, wd_all)[rank * rows:(rank + 1) * rows]
+    err = (y.float() - ref).abs().max().item()
+    assert err <= 3e-2 * ref.abs().max().item() + 1e-2, f"tp mlp rank {rank}: error {err}"
+    report["checked"] += 1
+
+    params = [torch.nn.Parameter(torch.zeros(n, device="cuda", dtype=torch.bfloat16)) for n in (1000, 333, 70000, 8)]
+    expect = []
+    for i, prm in enumerate(params):
+        gen = torch.Generator(device="cuda").manual_seed(300 + 10 * rank + i)
+        prm.grad = torch.randn(prm.shape, device="cuda", generator=gen).to(torch.bfloat16)
+        total = prm.grad.float().clone()
+        dist.all_reduce(total)
+        expect.append(total / world)
+    GradientBuckets(params, bucket_bytes=64 << 10).reduce()
+    torch.cuda.synchronize()
+    for prm, want in zip(params, expect):
+        torch.testing.assert_close(prm.grad.float(), want, atol=0.03, rtol=2e-2)
+    report["checked"] += 1
 
     torch.cuda.synchronize()
     dist.barrier()

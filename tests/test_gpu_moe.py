@@ -58,3 +58,21 @@ def test_fused_moe_single_gpu(tokens, hidden, ffn, experts):
         err = (out.float() - ref)[same_route].abs().max().item()
         scale = ref[same_route].abs().max().item()
         assert err <= 2e-2 * scale + 1e-3, f"call {call}: max error {err} against magnitude {scale}"
+
+
+def test_mixtral_block_single_gpu():
+    from pccl_b200.models import MixtralMoEBlock, rms_norm
+    from pccl_b200.ops import moe
+    tokens, hidden, ffn, experts = 256, 512, 1024, 8
+    wg, w1, w3, w2 = _weights(experts, hidden, ffn, seed=3)
+    gamma = (1 + 0.1 * torch.randn(hidden, device="cuda")).to(torch.bfloat16)
+    block = MixtralMoEBlock(tokens, hidden, ffn, experts, gamma, local=True)
+    block.load(wg, w1, w3, w2)
+    x = torch.randn(tokens, hidden, device="cuda").to(torch.bfloat16)
+    y = block(x)
+    torch.cuda.synchronize()
+    normed = rms_norm(x, gamma)
+    ref, ref_idx, _ = moe.moe_reference(normed, wg, w1, w3, w2)
+    same = (block.moe.op.topk_idx.long() == ref_idx).all(dim=-1)
+    err = ((y.float() - x.float()) - ref)[same].abs().max().item()
+    assert err <= 2e-2 * ref[same].abs().max().item() + 2e-2
