@@ -125,14 +125,15 @@ def run_multi(args):
                             elif kind == "allgather":
                                 name = pp.ensure_plan(kind, numel, dtype, forced_algo, forced_ch)
                                 mine = full[rank * shard:(rank + 1) * shard]
-                                call = lambda: pp.all_gather(full, mine, algorithm=forced_algo, channels=forced_ch)
+                                call = lambda: pp.all_gather(full, mine, algorithm=forced_algo, channels=forced_ch, async_op=True)
                             elif kind == "reduce_scatter":
                                 name = pp.ensure_plan(kind, numel, dtype, forced_algo, forced_ch)
                                 mine = full[rank * shard:(rank + 1) * shard]
-                                call = lambda: pp.reduce_scatter(mine, full, algorithm=forced_algo, channels=forced_ch)
+                                call = lambda: pp.reduce_scatter(mine, full, algorithm=forced_algo, channels=forced_ch, async_op=True)
                             else:
                                 name = pp.ensure_plan(kind, numel, dtype, forced_algo or "twoshot", forced_ch)
-                                call = lambda: pp.all_to_all(nccl_out, full, algorithm=forced_algo or "twoshot", channels=forced_ch)
+                                call = lambda: pp.all_to_all(nccl_out, full, algorithm=forced_algo or "twoshot", channels=forced_ch,
+                                                            async_op=True)
                         except Exception as err:  # noqa: BLE001
                             if rank == 0:
                                 print(json.dumps({"collective": kind, "algo": algo, "bytes": nbytes, "skipped": str(err)[:120]}))

@@ -42,6 +42,14 @@ OPTIONS: Dict[str, tuple] = {
     "PCCL_ALGO": ("algo", str, None, "force ring|rhd|tree|oneshot|twoshot|nvls"),
     "PCCL_CHANNELS": ("channels", int, None, "force the channel count of generated plans"),
     "PCCL_EXECUTOR": ("executor", str, None, "sm (default) | ce (copy engine) | cpu (gloo replay)"),
+    "PCCL_LL_MAX_BYTES": ("ll_max_bytes", _size, 256 << 10,
+                          "largest all-reduce taken by the packet-protocol kernel (0 = never)"),
+    "PCCL_MOVER_TUNING": ("mover_tuning", int, 0,
+                          "data-mover bits: 1 = two register tiles in flight, 2 = one tile in multimem steps"),
+    "PCCL_CE_MIN_BYTES": ("ce_min_bytes", _size, 64 << 10, "copy-engine executor: smaller copies stay on the SM path"),
+    "PCCL_CLOSING_BARRIER": ("closing_barrier", _flag, True,
+                             "append an all-pairs barrier to pull-style plans (ring, rhd, tree, hand-built)"),
+    "PCCL_RDMA": ("rdma", _flag, False, "build option: compile the verbs transport of the RDMA executor"),
     "PCCL_TUNING_FILE": ("tuning_file", str, None, "JSON with measured algorithm crossovers"),
     "PCCL_LOG_LEVEL": ("log_level", str, "WARN", "TRACE|DEBUG|INFO|WARN|ERROR|CRITICAL"),
     "PCCL_JOB_ID": ("job_id", str, None, "namespace of the fd-passing sockets"),
@@ -64,6 +72,11 @@ class PcclConfig:
     algo: Optional[str] = None
     channels: Optional[int] = None
     executor: Optional[str] = None
+    ll_max_bytes: int = 256 << 10
+    mover_tuning: int = 0
+    ce_min_bytes: int = 64 << 10
+    closing_barrier: bool = True
+    rdma: bool = False
     tuning_file: Optional[str] = None
     log_level: str = "WARN"
     job_id: Optional[str] = None

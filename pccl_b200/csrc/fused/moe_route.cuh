@@ -108,10 +108,20 @@ __global__ void __launch_bounds__(kMoeRouteWarps * 32) moe_route_kernel(const Mo
           *reinterpret_cast<uint2*>(p.base[dest] + p.meta_off + row_index * sizeof(uint2)) = m;
         }
       }
-      for (int v = lane; v < vecs; v += 32) {
-        const uint4 xv = row[v];
-        if (dst[0]) ptx::st_v4(dst[0] + v * 16, xv);
-        if (dst[1]) ptx::st_v4(dst[1] + v * 16, xv);
+      // Four row vectors per lane are loaded before the first store (the row was just read for the
+      // logits, so these hit in cache); loads are unconditional, the tail re-reads the last vector.
+      for (int v0 = lane; v0 < vecs; v0 += 128) {
+        uint4 xv[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) xv[u] = row[min(v0 + 32 * u, vecs - 1)];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int v = v0 + 32 * u;
+          if (v < vecs) {
+            if (dst[0]) ptx::st_v4(dst[0] + v * 16, xv[u]);
+            if (dst[1]) ptx::st_v4(dst[1] + v * 16, xv[u]);
+          }
+        }
       }
     }
   }

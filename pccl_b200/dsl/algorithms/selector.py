@@ -30,11 +30,16 @@ from .tree import TreeAllreduce
 
 _is_power_of_2 = is_power_of_two
 
-#: message-size crossovers (bytes) on a switched fabric, by world size: (one-shot up to, two-shot up to)
+#: message-size crossovers (bytes) on a switched fabric, by world size:
+#: (one-shot up to, in-switch reduction from, in-switch reduction up to); two-shot elsewhere.
+#: Measured on B200 / NVLink 5: with two ranks NVLS moves 1.5x the bytes of two-shot and never wins;
+#: with four it wins between a few MB and a few tens of MB; eight is set from the byte counts
+#: (1.125 n against 1.75 n per direction).
+_NEVER = 1 << 62
 SWITCHED_CROSSOVERS: Dict[int, tuple] = {
-    2: (4 * 1024 * 1024, 1 << 62),       # two ranks: in-switch reduction moves 1.5x the bytes of two-shot
-    4: (256 * 1024, 8 * 1024 * 1024),
-    8: (128 * 1024, 4 * 1024 * 1024),
+    2: (4 * 1024 * 1024, _NEVER, _NEVER),
+    4: (2 * 1024 * 1024, 2 * 1024 * 1024, 32 * 1024 * 1024),
+    8: (128 * 1024, 4 * 1024 * 1024, _NEVER),
 }
 
 
@@ -63,12 +68,15 @@ def select_algorithm(world_size: int, data_bytes: int,
     if getattr(topology, "uniform_all_to_all", False):
         table = load_tuned_crossovers()
         nearest = min(table, key=lambda w: abs(w - world_size))
-        one_shot_max, two_shot_max = table[nearest]
+        entry = tuple(table[nearest])
+        if len(entry) == 2:                      # older tuning files: (one-shot up to, two-shot up to)
+            entry = (entry[0], entry[1], _NEVER)
+        one_shot_max, nvls_from, nvls_to = entry
         if data_bytes <= one_shot_max:
             return OneShotAllreduce()
-        if data_bytes <= two_shot_max or not topology.in_switch_reduction:
-            return TwoShotAllreduce()
-        return NvlsAllreduce()
+        if topology.in_switch_reduction and nvls_from < data_bytes <= nvls_to:
+            return NvlsAllreduce()
+        return TwoShotAllreduce()
 
     if not is_power_of_two(world_size) or world_size <= 2:
         return RingAllreduce()

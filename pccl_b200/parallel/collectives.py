@@ -174,29 +174,37 @@ def all_reduce(tensor: torch.Tensor, op: str = "sum", algorithm: Optional[str] =
     return tensor
 
 
+def _run(name: str, input: torch.Tensor, output: torch.Tensor, async_op: bool) -> None:
+    (_engine.execute_operation_async if async_op else _engine.execute_operation)(name, input, output)
+
+
 def reduce_scatter(output: torch.Tensor, input: torch.Tensor, op: str = "sum",
-                   algorithm: Optional[str] = None, channels: Optional[int] = None) -> torch.Tensor:
+                   algorithm: Optional[str] = None, channels: Optional[int] = None,
+                   async_op: bool = False) -> torch.Tensor:
+    """``async_op``: enqueue on the current stream and return (``synchronize`` checks the status later)."""
     name = ensure_plan("reduce_scatter", input.numel(), input.dtype, algorithm, channels, op)
-    _engine.execute_operation(name, input, output)
+    _run(name, input, output, async_op)
     return output
 
 
 def all_gather(output: torch.Tensor, input: torch.Tensor, algorithm: Optional[str] = None,
-               channels: Optional[int] = None, executor: Optional[str] = None) -> torch.Tensor:
+               channels: Optional[int] = None, executor: Optional[str] = None,
+               async_op: bool = False) -> torch.Tensor:
     """``executor="ce"`` moves the shards with the copy engines (``algorithm`` twoshot)."""
     if executor == "ce":
         algorithm = "twoshot"
     name = ensure_plan("allgather", output.numel(), output.dtype, algorithm, channels, executor=executor)
-    _engine.execute_operation(name, input, output)
+    _run(name, input, output, async_op)
     return output
 
 
 def all_to_all(output: torch.Tensor, input: torch.Tensor, algorithm: Optional[str] = None,
-               channels: Optional[int] = None, executor: Optional[str] = None) -> torch.Tensor:
+               channels: Optional[int] = None, executor: Optional[str] = None,
+               async_op: bool = False) -> torch.Tensor:
     if executor == "ce":
         algorithm = "twoshot"
     name = ensure_plan("alltoall", input.numel(), input.dtype, algorithm or "twoshot", channels, executor=executor)
-    _engine.execute_operation(name, input, output)
+    _run(name, input, output, async_op)
     return output
 
 

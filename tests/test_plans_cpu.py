@@ -154,3 +154,17 @@ def test_out_of_range_access_is_reported():
     data["params"]["remote_offset"] = 10 ** 6
     with pytest.raises(IndexError, match="outside rank"):
         simulate(plans, make_inputs("allreduce", 2, 64))
+
+
+def test_switched_fabric_selector_follows_measured_crossovers():
+    """Two ranks never take the in-switch path; four take it only in the middle sizes."""
+    from pccl_b200.dsl.algorithms.selector import select_algorithm
+    from pccl_b200.dsl.superopt import B200_PROFILE, NVLINK5_TOPOLOGY
+    pick = lambda w, b: type(select_algorithm(w, b, NVLINK5_TOPOLOGY, B200_PROFILE)).__name__
+    assert pick(2, 64 << 10) == "OneShotAllreduce"
+    assert pick(2, 512 << 20) == "TwoShotAllreduce"
+    assert pick(4, 1 << 20) == "OneShotAllreduce"
+    assert pick(4, 8 << 20) == "NvlsAllreduce"
+    assert pick(4, 512 << 20) == "TwoShotAllreduce"
+    assert pick(8, 1 << 20) == "TwoShotAllreduce"
+    assert pick(8, 512 << 20) == "NvlsAllreduce"
