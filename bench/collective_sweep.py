@@ -101,7 +101,7 @@ def run_multi(args):
 
                 nccl_ms = reduce_max(timed_loop(nccl_call, iters, torch.cuda.synchronize, dist.barrier))
                 for algo in args.algos:
-                    allowed = {"allreduce": ("auto", "ll", "ring", "rhd", "tree", "oneshot", "twoshot", "nvls"),
+                    allowed = {"allreduce": ("auto", "ll", "push", "ring", "rhd", "tree", "oneshot", "twoshot", "nvls"),
                                "allgather": ("auto", "ring", "rhd", "twoshot", "nvls"),
                                "reduce_scatter": ("auto", "ring", "rhd", "twoshot", "nvls"),
                                "alltoall": ("auto", "ring", "twoshot")}[kind]
@@ -111,6 +111,8 @@ def run_multi(args):
                         continue
                     if algo == "ll" and (kind != "allreduce" or nbytes > pp.collectives.LL_MAX_BYTES):
                         continue
+                    if algo == "push" and (kind != "allreduce" or nbytes > pp.collectives.PUSH_MAX_BYTES):
+                        continue
                     if algo in ("rhd", "tree") and world & (world - 1):
                         continue
                     for ch in args.channels:
@@ -119,8 +121,11 @@ def run_multi(args):
                         try:
                             uses_ll = kind == "allreduce" and algo in ("auto", "ll") and \
                                 pp.collectives._ll_eligible(full, "sum", forced_algo)
+                            uses_push = kind == "allreduce" and not uses_ll and algo in ("auto", "push") and \
+                                pp.collectives._push_eligible(full, "sum", forced_algo)
                             if kind == "allreduce":
-                                name = pp.ensure_plan(kind, numel, dtype, None if uses_ll else forced_algo, forced_ch)
+                                name = pp.ensure_plan(kind, numel, dtype, None if (uses_ll or uses_push) else forced_algo,
+                                                      forced_ch)
                                 call = lambda: pp.all_reduce(full, algorithm=forced_algo, channels=forced_ch, async_op=True)
                             elif kind == "allgather":
                                 name = pp.ensure_plan(kind, numel, dtype, forced_algo, forced_ch)
@@ -143,6 +148,8 @@ def run_multi(args):
                             _, real_algo, real_ch = pp.registered_plans()[name]
                             if uses_ll:
                                 real_algo, real_ch = "ll", 0
+                            elif uses_push:
+                                real_algo, real_ch = "push", 0
                             alg = numel * esize / (ms * 1e-3) / 1e9
                             print(json.dumps({
                                 "collective": kind, "dtype": dname, "bytes": numel * esize, "world": world,

@@ -120,6 +120,7 @@ void RankContext::upload(RegisteredOp& op) {
   // Templates of this library end with their own barrier; everything else gets one appended.
   const std::string& algo = op.plan.algorithm;
   const bool self_fenced = algo == "oneshot" || algo == "twoshot" || algo == "direct" || algo == "nvls";
+  lo.defer_barriers = Environs::get_flag("PCCL_DEFER_BARRIERS", true);
   lo.closing_barrier = !self_fenced && !op.plan.collective_type.empty() &&
                        Environs::get_flag("PCCL_CLOSING_BARRIER", true);
   op.lowered = lower_plan(op.plan, lo);

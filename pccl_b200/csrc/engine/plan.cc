@@ -454,6 +454,21 @@ LoweredProgram lower_plan(const Plan& plan, const LowerOptions& opt) {
     ch.first_cta = next_cta;
     ch.num_ctas = ctas[c];
     next_cta += ctas[c];
+    // Runs of independent pulls (peer -> distinct local ranges) or puts (local -> peers) need no
+    // completion barrier between them: nothing signals in between and no step reads what the
+    // previous one wrote.  Only for plans without cross-chain dependencies (progress counters
+    // are published per step).
+    auto independent = [&](const Step& a, const Step& b, int self_rank) {
+      if (a.kind != b.kind || (a.kind != kStepCopy && a.kind != kStepPut)) return false;
+      if (a.kind == kStepCopy) {
+        if (a.peer == self_rank || b.peer == self_rank) return false;           // a local source may alias
+        return a.off1 + a.bytes <= b.off1 || b.off1 + b.bytes <= a.off1;          // disjoint local destinations
+      }
+      return a.peer != b.peer || a.off1 + a.bytes <= b.off1 || b.off1 + b.bytes <= a.off1;
+    };
+    bool chain_has_deps = false;
+    for (auto& ps : chain_steps[c]) chain_has_deps |= !ps.dep_ops.empty();
+    const size_t first_step_of_chain = out.steps.size();
     uint32_t barriers = 0;
     for (auto& ps : chain_steps[c]) {
       Step s = ps.step;
@@ -469,11 +484,19 @@ LoweredProgram lower_plan(const Plan& plan, const LowerOptions& opt) {
       for (int d : ps.dep_ops)
         out.deps.push_back(ChainDep{static_cast<uint32_t>(chain_of[d]), static_cast<uint32_t>(step_of_op[d] + 1)});
       s.n_dep = static_cast<uint8_t>(ps.dep_ops.size());
+      out.steps.push_back(s);
+    }
+    const bool any_deps = [&] { for (auto& cs : chain_steps) for (auto& ps : cs) if (!ps.dep_ops.empty()) return true; return false; }();
+    for (size_t k = first_step_of_chain; k < out.steps.size(); ++k) {
+      Step& s = out.steps[k];
+      if (!any_deps && !chain_has_deps && opt.defer_barriers && k + 1 < out.steps.size() && s.n_notify == 0) {
+        const Step& next = out.steps[k + 1];
+        if (next.n_wait == 0 && next.n_dep == 0 && independent(s, next, opt.rank)) s.defer_barrier = 1;
+      }
       if (ch.num_ctas > 1) {
         if (s.n_wait + s.n_dep) ++barriers;
-        if (s.kind != kStepNoop) ++barriers;
+        if (s.kind != kStepNoop && !s.defer_barrier) ++barriers;
       }
-      out.steps.push_back(s);
     }
     ch.barriers_per_launch = barriers;
     out.chains.push_back(ch);

@@ -62,6 +62,7 @@ struct LowerOptions {
   bool multicast = false;         // NVLS mapping available
   uint32_t total_ctas = 16;       // CTA budget for the whole program
   uint32_t max_ctas_per_chain = 64;
+  bool defer_barriers = true;             // merge runs of independent copies / puts into barrier-free runs
   uint64_t min_bytes_per_cta = 64 << 10;   // do not spread less than this over another CTA
   bool force_copy_engine = false; // route pull copies to the copy-engine executor
   // Append an all-pairs barrier after the last step.  Pull-style templates (ring, tree,

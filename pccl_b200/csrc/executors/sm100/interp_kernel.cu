@@ -291,10 +291,12 @@ __global__ void __launch_bounds__(kInterpThreads, 1) plan_interp_kernel(const La
     // 4. completion barrier
     const bool publishes = s.n_notify != 0;
     if (multi_cta) {
-      if (s.kind != kStepNoop) {
+      if (s.kind != kStepNoop && !s.defer_barrier) {
         ++barrier_no;
         if (!chain_barrier(sync_counter, barrier_no * chain.num_ctas, s.writes_remote != 0, w, &s_ok))
           return;
+      } else if (s.defer_barrier) {
+        __syncthreads();                       // the shared step descriptor is about to be rewritten
       }
     } else {
       __syncthreads();

@@ -54,7 +54,9 @@ struct ChainDep {     // "chain `chain` must have finished `steps_done` steps of
 
 struct Step {
   uint8_t kind, red_op, n_wait, n_notify;
-  uint8_t n_dep, writes_remote, reserved[2];
+  uint8_t n_dep, writes_remote;
+  uint8_t defer_barrier;   // 1: the next step is an independent copy / put, no completion barrier here
+  uint8_t reserved;
   int32_t peer;
   uint32_t peer_mask;
   uint32_t sig_begin;    // waits are sigs[sig_begin .. +n_wait), notifies follow

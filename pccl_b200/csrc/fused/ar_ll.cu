@@ -151,9 +151,9 @@ void allreduce_ll(const PeerBases& peers, uint64_t buf_off, uint64_t capacity_by
   p.flag = epoch;
   p.error = error_word();
   p.timeout_ns = timeout_ms * 1000000ull;
-  // One unit per thread up to 64 CTAs, then a grid-stride loop.
+  // One unit per thread up to 128 CTAs, then a grid-stride loop.
   uint64_t grid = (p.units + kLLThreads - 1) / kLLThreads;
-  if (grid > 64) grid = 64;
+  if (grid > 128) grid = 128;
   switch (dtype) {
     case 0: allreduce_ll_kernel<0><<<static_cast<unsigned>(grid), kLLThreads, 0, stream>>>(p); break;
     case 1: allreduce_ll_kernel<1><<<static_cast<unsigned>(grid), kLLThreads, 0, stream>>>(p); break;

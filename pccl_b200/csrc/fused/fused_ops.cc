@@ -114,6 +114,25 @@ void bind_fused_ops(py::module_& m) {
                              static_cast<uint32_t>(epoch), c10::cuda::getCurrentCUDAStream().stream());
         },
         py::arg("input"), py::arg("output"), py::arg("buf_off"), py::arg("capacity_bytes"), py::arg("epoch"));
+  // Fused push all-reduce (sum) for medium messages; out may be the input tensor.
+  f.def("allreduce_push",
+        [](const torch::Tensor& in, torch::Tensor& out, int64_t area_off, int64_t capacity_bytes, int64_t flags_off,
+           torch::Tensor& counters, int64_t epoch, int ctas) {
+          TORCH_CHECK(in.is_cuda() && out.is_cuda() && in.is_contiguous() && out.is_contiguous() &&
+                          in.scalar_type() == out.scalar_type() && in.numel() == out.numel(),
+                      "allreduce_push: contiguous CUDA tensors of one dtype and size");
+          int dtype = -1;
+          if (in.scalar_type() == torch::kFloat32) dtype = 0;
+          else if (in.scalar_type() == torch::kFloat16) dtype = 1;
+          else if (in.scalar_type() == torch::kBFloat16) dtype = 2;
+          TORCH_CHECK(dtype >= 0, "allreduce_push: float32, float16 or bfloat16");
+          gemm::allreduce_push(peer_bases(), static_cast<uint64_t>(area_off), static_cast<uint64_t>(capacity_bytes),
+                               static_cast<uint64_t>(flags_off), as_u32(counters, 2, "counters"), in.data_ptr(),
+                               out.data_ptr(), static_cast<uint64_t>(in.nbytes()), dtype,
+                               static_cast<uint32_t>(epoch), c10::cuda::getCurrentCUDAStream().stream(), ctas);
+        },
+        py::arg("input"), py::arg("output"), py::arg("area_off"), py::arg("capacity_bytes"), py::arg("flags_off"),
+        py::arg("counters"), py::arg("epoch"), py::arg("ctas"));
   // MoE router on its own: top-2 expert indices, renormalised gates, the row each choice claims
   // in its expert's batch, and the per-expert token counts.  scratch: int32[experts + 1].
   f.def("moe_route",

@@ -48,17 +48,30 @@ def init(group: Optional[dist.ProcessGroup] = None):
     else:
         _engine.get_engine()
     _setup_ll(group)
+    _setup_push(group)
     return _engine.get_engine()
 
 
-#: largest message (bytes) the packet-protocol all-reduce takes; its payload doubles on the wire
-LL_MAX_BYTES = int(os.environ.get("PCCL_LL_MAX_BYTES", 256 << 10))
+#: largest message (bytes) the packet-protocol all-reduce takes.  Its payload doubles on the wire and
+#: every rank sends to every peer, so the default shrinks with the world size: 4 MB / world
+#: (2 MB for two ranks, 512 KB for eight); PCCL_LL_MAX_BYTES overrides it.
+LL_MAX_BYTES = 256 << 10
+
+
+def _ll_limit(world: int) -> int:
+    forced = os.environ.get("PCCL_LL_MAX_BYTES")
+    if forced:
+        from ..config import _size
+        return _size(forced)
+    return (4 << 20) // max(2, world)
 
 
 def _setup_ll(group) -> None:
     """Receive buffer of the small-message all-reduce: [2 parities][world][2 x LL_MAX_BYTES], zeroed."""
+    global LL_MAX_BYTES
     eng = _engine.get_engine()
     _state["ll"] = None
+    LL_MAX_BYTES = _ll_limit(_state["world"])
     if _state["world"] < 2 or not torch.cuda.is_available() or not hasattr(eng, "empty_symmetric") \
             or LL_MAX_BYTES <= 0 or os.environ.get("PCCL_EXECUTOR") == "cpu":
         return
@@ -67,6 +80,44 @@ def _setup_ll(group) -> None:
     torch.cuda.synchronize()
     dist.barrier(group=group)
     _state["ll"] = {"buf": buf, "epoch": 0, "native": _engine.load_native().fused}
+
+
+#: largest message (bytes) taken by the fused push all-reduce (PCCL_PUSH_MAX_BYTES); larger ones run as
+#: plans, zero-copy on symmetric tensors
+PUSH_MAX_BYTES = 32 << 20
+_PUSH_CTAS = 96
+
+
+def _setup_push(group) -> None:
+    """Receive areas of the push all-reduce: [2 parities][A | B][world][slot], flags, counters."""
+    global PUSH_MAX_BYTES
+    _state["push"] = None
+    forced = os.environ.get("PCCL_PUSH_MAX_BYTES")
+    if forced:
+        from ..config import _size
+        PUSH_MAX_BYTES = _size(forced)
+    eng = _engine.get_engine()
+    world = _state["world"]
+    if world < 2 or not torch.cuda.is_available() or not hasattr(eng, "empty_symmetric") \
+            or PUSH_MAX_BYTES <= 0 or os.environ.get("PCCL_EXECUTOR") == "cpu":
+        return
+    slot = ((PUSH_MAX_BYTES // 16 + world - 1) // world) * 16
+    areas = eng.empty_symmetric((4 * world * slot,), torch.uint8)
+    flags = eng.empty_symmetric((2 * world,), torch.int32)
+    flags.zero_()
+    torch.cuda.synchronize()
+    dist.barrier(group=group)
+    _state["push"] = {"areas": areas, "flags": flags, "epoch": 0, "native": _engine.load_native().fused,
+                      "counters": torch.zeros(2, dtype=torch.int32, device="cuda")}
+
+
+def _push_eligible(tensor: torch.Tensor, op: str, algorithm: Optional[str]) -> bool:
+    push = _state.get("push")
+    if push is None or op != "sum" or algorithm not in (None, "push"):
+        return False
+    nbytes = tensor.numel() * tensor.element_size()
+    return (tensor.is_cuda and tensor.is_contiguous() and nbytes % 16 == 0 and 0 < nbytes <= PUSH_MAX_BYTES
+            and tensor.data_ptr() % 16 == 0 and tensor.dtype in (torch.float32, torch.float16, torch.bfloat16))
 
 
 def _ll_eligible(tensor: torch.Tensor, op: str, algorithm: Optional[str]) -> bool:
@@ -157,14 +208,24 @@ def all_reduce(tensor: torch.Tensor, op: str = "sum", algorithm: Optional[str] =
                channels: Optional[int] = None, async_op: bool = False) -> torch.Tensor:
     """In-place all-reduce of ``tensor`` (sum / max / min / avg).
 
-    Sums of up to ``LL_MAX_BYTES`` go through the packet-protocol kernel (no plan, no staging copy,
-    asynchronous on the current stream) unless an algorithm is forced.
+    Unless an algorithm is forced, sums of up to ``LL_MAX_BYTES`` go through the packet-protocol kernel
+    and sums of up to ``PUSH_MAX_BYTES`` through the fused push kernel (both: no plan, no staging copy,
+    asynchronous on the current stream); everything else runs as a plan.
     """
     if _ll_eligible(tensor, op, algorithm):
         ll = _state["ll"]
         ll["epoch"] += 1
         ll["native"].allreduce_ll(tensor, tensor, ll["buf"].heap_offset, LL_MAX_BYTES, ll["epoch"])
         return tensor
+    if _push_eligible(tensor, op, algorithm):
+        push = _state["push"]
+        push["epoch"] += 1
+        push["native"].allreduce_push(tensor, tensor, push["areas"].heap_offset, PUSH_MAX_BYTES,
+                                      push["flags"].heap_offset, push["counters"], push["epoch"], _PUSH_CTAS)
+        return tensor
+    if algorithm == "push":
+        raise ValueError("the push all-reduce takes contiguous, 16-byte aligned f32/f16/bf16 sums of at most "
+                         f"{PUSH_MAX_BYTES} bytes")
     if algorithm == "ll":
         raise ValueError("the packet-protocol all-reduce takes contiguous f32/f16/bf16 sums of at most "
                          f"{LL_MAX_BYTES} bytes")

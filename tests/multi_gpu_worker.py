@@ -115,6 +115,27 @@ def main():
                 torch.testing.assert_close(y.float(), ref, atol=atol, rtol=2e-2,
                                            msg=lambda t: f"ll allreduce {dtype} n={numel} call {call} rank {rank}: {t}")
         report["checked"] += 1
+    # fused push all-reduce: ordinary tensors, in place, sizes that do not divide evenly over the ranks
+    for dtype in (torch.float32, torch.bfloat16, torch.float16):
+        for numel in (8, 4096 + 8, 300000, 1 << 21):
+            for call in range(3):
+                gen = torch.Generator(device="cuda").manual_seed(2000 * call + 31 * rank + numel)
+                x = torch.randn(numel, device="cuda", generator=gen).to(dtype)
+                ref = x.float().clone()
+                dist.all_reduce(ref)
+                y = pp.all_reduce(x.clone(), algorithm="push")
+                torch.cuda.synchronize()
+                __import__("pccl_b200.ops.gemm", fromlist=["check"]).check()
+                atol = 1e-5 if dtype == torch.float32 else 0.06
+                torch.testing.assert_close(y.float(), ref, atol=atol, rtol=2e-2,
+                                           msg=lambda t: f"push allreduce {dtype} n={numel} call {call} rank {rank}: {t}")
+        report["checked"] += 1
+    x = torch.randn(100000, device="cuda", generator=torch.Generator(device="cuda").manual_seed(9 + rank))
+    y = pp.all_reduce(x.clone(), algorithm="push")
+    gathered = [torch.empty_like(y) for _ in range(world)]
+    dist.all_gather(gathered, y)
+    assert all(torch.equal(gathered[0], g) for g in gathered), "push allreduce differs between ranks"
+
     # every rank must hold bit-identical results (sums are taken in rank order)
     x = torch.randn(4096, device="cuda", generator=torch.Generator(device="cuda").manual_seed(5 + rank))
     y = pp.all_reduce(x.clone(), algorithm="ll")
