@@ -35,7 +35,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 MESSAGE_BYTES = 512 << 20
-PUBLISHED = {2: 246.4, 4: 274.8, 8: 282.0}     # reference, bf16, H100
+PUBLISHED = {2: 246.4, 4: 274.8, 8: 282.0}     # the reference's published 512 MB bus GB/s (bf16, H100; its README.md:97-99)
 
 
 class ClockSampler:

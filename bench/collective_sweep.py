@@ -102,42 +102,46 @@ def run_multi(args):
                 nccl_ms = reduce_max(timed_loop(nccl_call, iters, torch.cuda.synchronize, dist.barrier))
                 for algo in args.algos:
                     allowed = {"allreduce": ("auto", "ll", "push", "ring", "rhd", "tree", "oneshot", "twoshot", "nvls"),
-                               "allgather": ("auto", "ring", "rhd", "twoshot", "nvls"),
-                               "reduce_scatter": ("auto", "ring", "rhd", "twoshot", "nvls"),
-                               "alltoall": ("auto", "ring", "twoshot")}[kind]
+                               "allgather": ("auto", "push", "ring", "rhd", "twoshot", "nvls"),
+                               "reduce_scatter": ("auto", "push", "ring", "rhd", "twoshot", "nvls"),
+                               "alltoall": ("auto", "push", "ring", "twoshot")}[kind]
                     if algo not in allowed:
                         continue
                     if algo == "oneshot" and nbytes > (4 << 20):
                         continue
                     if algo == "ll" and (kind != "allreduce" or nbytes > pp.collectives.LL_MAX_BYTES):
                         continue
-                    if algo == "push" and (kind != "allreduce" or nbytes > pp.collectives.PUSH_MAX_BYTES):
+                    if algo == "push" and nbytes > pp.collectives.PUSH_MAX_BYTES:
                         continue
                     if algo in ("rhd", "tree") and world & (world - 1):
                         continue
                     for ch in args.channels:
                         forced_algo = None if algo == "auto" else algo
                         forced_ch = None if ch == "auto" else int(ch)
+                        plan_algo = None if forced_algo == "push" else forced_algo      # plan registered for reporting
                         try:
                             uses_ll = kind == "allreduce" and algo in ("auto", "ll") and \
                                 pp.collectives._ll_eligible(full, "sum", forced_algo)
                             uses_push = kind == "allreduce" and not uses_ll and algo in ("auto", "push") and \
                                 pp.collectives._push_eligible(full, "sum", forced_algo)
                             if kind == "allreduce":
-                                name = pp.ensure_plan(kind, numel, dtype, None if (uses_ll or uses_push) else forced_algo,
+                                name = pp.ensure_plan(kind, numel, dtype, None if (uses_ll or uses_push) else plan_algo,
                                                       forced_ch)
                                 call = lambda: pp.all_reduce(full, algorithm=forced_algo, channels=forced_ch, async_op=True)
                             elif kind == "allgather":
-                                name = pp.ensure_plan(kind, numel, dtype, forced_algo, forced_ch)
+                                name = pp.ensure_plan(kind, numel, dtype, plan_algo, forced_ch)
                                 mine = full[rank * shard:(rank + 1) * shard]
+                                uses_push = pp.collectives._push_ok(full, mine, forced_algo)
                                 call = lambda: pp.all_gather(full, mine, algorithm=forced_algo, channels=forced_ch, async_op=True)
                             elif kind == "reduce_scatter":
-                                name = pp.ensure_plan(kind, numel, dtype, forced_algo, forced_ch)
+                                name = pp.ensure_plan(kind, numel, dtype, plan_algo, forced_ch)
                                 mine = full[rank * shard:(rank + 1) * shard]
+                                uses_push = pp.collectives._push_ok(full, mine, forced_algo)
                                 call = lambda: pp.reduce_scatter(mine, full, algorithm=forced_algo, channels=forced_ch, async_op=True)
                             else:
-                                name = pp.ensure_plan(kind, numel, dtype, forced_algo or "twoshot", forced_ch)
-                                call = lambda: pp.all_to_all(nccl_out, full, algorithm=forced_algo or "twoshot", channels=forced_ch,
+                                name = pp.ensure_plan(kind, numel, dtype, plan_algo or "twoshot", forced_ch)
+                                uses_push = pp.collectives._push_ok(full, nccl_out, forced_algo)
+                                call = lambda: pp.all_to_all(nccl_out, full, algorithm=forced_algo, channels=forced_ch,
                                                             async_op=True)
                         except Exception as err:  # noqa: BLE001
                             if rank == 0:

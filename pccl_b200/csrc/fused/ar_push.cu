@@ -11,6 +11,9 @@
 // are two flag rounds in total.  Areas are double-buffered by call parity and flags count calls
 // (a rank can be at most one call ahead of a peer), so nothing is reset between calls.
 // Every wait is bounded; a timeout sets the error word and the kernel returns.
+// The same kernel serves reduce-scatter (stops after step 2, keeps only its own slice), all-gather
+// (step 1 pushes the whole shard to every peer, step 2 is skipped, step 3 copies from A) and
+// all-to-all (step 1 as is, step 3 copies from A), selected by `mode`.
 // The plan interpreter runs the same algorithm as a chain of steps with a barrier after each;
 // this kernel is its fused form for sizes where those barriers dominate.  The reference's
 // counterpart is its fused-step kernel (csrc/plugins/cuda/cuda_executor.cu:963-1057).
@@ -42,10 +45,31 @@ struct PushParams {
   uint64_t vecs;             // 16-byte vectors in the message
   uint64_t per;              // vectors per slice (the last slice may be shorter)
   int dtype;                 // 0 f32, 1 f16, 2 bf16
+  int mode;                  // PushMode
   uint32_t epoch;
   uint32_t* error;
   uint64_t timeout_ns;
 };
+
+// Copy `len` 16-byte vectors, the whole grid cooperating; loads unconditional, stores predicated.
+template <bool kRemoteDst>
+__device__ __forceinline__ void grid_copy(const uint4* src, uint4* dst, uint64_t len, uint64_t tid, uint64_t nthreads) {
+  for (uint64_t i = tid; i < len; i += nthreads * kPushUnroll) {
+    uint4 v[kPushUnroll];
+#pragma unroll
+    for (int u = 0; u < kPushUnroll; ++u) {
+      const uint64_t j = i + u * nthreads;
+      v[u] = ptx::ld_local_v4(src + (j < len ? j : len - 1));
+    }
+#pragma unroll
+    for (int u = 0; u < kPushUnroll; ++u) {
+      const uint64_t j = i + u * nthreads;
+      if (j < len) {
+        if (kRemoteDst) ptx::st_v4(dst + j, v[u]); else dst[j] = v[u];
+      }
+    }
+  }
+}
 
 __device__ __forceinline__ bool wait_ge(const uint32_t* flag, uint32_t want, uint64_t deadline,
                                         const volatile uint32_t* abort_flag) {
@@ -146,31 +170,21 @@ __global__ void __launch_bounds__(kPushThreads) allreduce_push_kernel(const Push
   const uint4* in = reinterpret_cast<const uint4*>(p.in);
   uint4* out = reinterpret_cast<uint4*>(p.out);
 
-  // 1. push slice `peer` of my input into the peer's A[me]
+  // 1. push slice `peer` of my input (all-gather: my whole shard) into the peer's A[me]
   for (int k = 1; k < world; ++k) {
     const int peer = (me + k) % world;
-    const uint64_t len = slice_len(peer);
-    const uint4* src = in + static_cast<uint64_t>(peer) * p.per;
+    const bool whole = p.mode == kPushAllGather;
+    const uint64_t len = whole ? slice_len(me) : slice_len(peer);
+    const uint4* src = whole ? in : in + static_cast<uint64_t>(peer) * p.per;
     uint4* dst = reinterpret_cast<uint4*>(p.peers.base[peer] + a_off + static_cast<uint64_t>(me) * p.slice_cap);
-    for (uint64_t i = tid; i < len; i += nthreads * kPushUnroll) {
-      uint4 v[kPushUnroll];
-#pragma unroll
-      for (int u = 0; u < kPushUnroll; ++u) {                 // unconditional loads, clamped index
-        const uint64_t j = i + u * nthreads;
-        v[u] = ptx::ld_local_v4(src + (j < len ? j : len - 1));
-      }
-#pragma unroll
-      for (int u = 0; u < kPushUnroll; ++u) {
-        const uint64_t j = i + u * nthreads;
-        if (j < len) ptx::st_v4(dst + j, v[u]);
-      }
-    }
+    grid_copy<true>(src, dst, len, tid, nthreads);
   }
   arrive_and_post(p, 0);
   if (!wait_peers(p, 0, deadline, &ok)) return;
 
-  // 2. reduce my slice in rank order; result to my output and to every peer's B[me]
-  {
+  // 2. reduce my slice in rank order; result to my output and (all-reduce) to every peer's B[me]
+  if (p.mode == kPushAllReduce || p.mode == kPushReduceScatter) {
+    const bool scatter_only = p.mode == kPushReduceScatter;
     const uint64_t len = slice_len(me);
     const uint64_t base = static_cast<uint64_t>(me) * p.per;
     const uint8_t* a_mine = p.peers.base[me] + a_off;
@@ -198,6 +212,10 @@ __global__ void __launch_bounds__(kPushThreads) allreduce_push_kernel(const Push
         for (int s = 0; s < kW; ++s)
           if (s < world) add_into<DT>(acc, raw[v][s]);
         const uint4 r = pack<DT>(acc);
+        if (scatter_only) {
+          out[i] = r;                                          // the output is this rank's shard only
+          continue;
+        }
         out[base + i] = r;
         for (int k = 1; k < world; ++k) {
           const int peer = (me + k) % world;
@@ -206,37 +224,43 @@ __global__ void __launch_bounds__(kPushThreads) allreduce_push_kernel(const Push
       }
     }
   }
-  arrive_and_post(p, 1);
-  if (!wait_peers(p, 1, deadline, &ok)) return;
+  // All modes share the counters and flags (they count calls), so the modes with a single flag
+  // round still tick the second one; nobody waits for it.
+  if (p.mode == kPushReduceScatter) {
+    arrive_and_post(p, 1);
+    return;
+  }
+  uint64_t from_off = a_off;                                 // all-gather / all-to-all read what step 1 delivered
+  if (p.mode == kPushAllReduce) {
+    arrive_and_post(p, 1);
+    if (!wait_peers(p, 1, deadline, &ok)) return;
+    from_off = b_off;
+  } else {
+    // my own part goes straight from the input to the output
+    const uint4* src = p.mode == kPushAllGather ? in : in + static_cast<uint64_t>(me) * p.per;
+    grid_copy<false>(src, out + static_cast<uint64_t>(me) * p.per, slice_len(me), tid, nthreads);
+  }
 
-  // 3. gather the other slices from B into my output
+  // 3. gather the other slices into my output
   for (int k = 1; k < world; ++k) {
     const int s = (me + k) % world;
-    const uint64_t len = slice_len(s);
-    const uint4* src = reinterpret_cast<const uint4*>(p.peers.base[me] + b_off + static_cast<uint64_t>(s) * p.slice_cap);
-    uint4* dst = out + static_cast<uint64_t>(s) * p.per;
-    for (uint64_t i = tid; i < len; i += nthreads * kPushUnroll) {
-      uint4 v[kPushUnroll];
-#pragma unroll
-      for (int u = 0; u < kPushUnroll; ++u) {
-        const uint64_t j = i + u * nthreads;
-        v[u] = ptx::ld_local_v4(src + (j < len ? j : len - 1));
-      }
-#pragma unroll
-      for (int u = 0; u < kPushUnroll; ++u) {
-        const uint64_t j = i + u * nthreads;
-        if (j < len) dst[j] = v[u];
-      }
-    }
+    const uint4* src = reinterpret_cast<const uint4*>(p.peers.base[me] + from_off + static_cast<uint64_t>(s) * p.slice_cap);
+    grid_copy<false>(src, out + static_cast<uint64_t>(s) * p.per, slice_len(s), tid, nthreads);
   }
+  if (p.mode != kPushAllReduce) arrive_and_post(p, 1);
 }
 
 }  // namespace
 
-void allreduce_push(const PeerBases& peers, uint64_t area_off, uint64_t capacity_bytes, uint64_t flags_off,
-                    uint32_t* counters, const void* in, void* out, uint64_t bytes, int dtype, uint32_t epoch,
-                    cudaStream_t stream, int ctas, uint64_t timeout_ms) {
+void collective_push(PushMode mode, const PeerBases& peers, uint64_t area_off, uint64_t capacity_bytes,
+                     uint64_t flags_off, uint32_t* counters, const void* in, void* out, uint64_t bytes, int dtype,
+                     uint32_t epoch, cudaStream_t stream, int ctas, uint64_t timeout_ms) {
+  // `bytes` is the size of the full message: the all-reduce tensor, the reduce-scatter input, the
+  // all-gather output, either side of the all-to-all.
   PCCL_CHECK(bytes % 16 == 0 && bytes > 0, "push all-reduce: size must be a positive multiple of 16 bytes");
+  PCCL_CHECK(mode == kPushAllReduce || bytes % (16ull * peers.world) == 0,
+             "push collective: every rank's part must be a multiple of 16 bytes");
+  PCCL_CHECK(mode != kPushAllToAll || in != out, "push all-to-all cannot run in place");
   PCCL_CHECK(bytes <= capacity_bytes, "push all-reduce: " << bytes << " bytes exceed the areas' " << capacity_bytes);
   PCCL_CHECK(reinterpret_cast<uintptr_t>(in) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0,
              "push all-reduce: tensors must be 16-byte aligned");
@@ -255,6 +279,7 @@ void allreduce_push(const PeerBases& peers, uint64_t area_off, uint64_t capacity
   p.vecs = bytes / 16;
   p.per = (p.vecs + peers.world - 1) / peers.world;
   p.dtype = dtype;
+  p.mode = mode;
   p.epoch = epoch;
   p.error = error_word();
   p.timeout_ns = timeout_ms * 1000000ull;

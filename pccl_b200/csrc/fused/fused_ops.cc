@@ -114,25 +114,32 @@ void bind_fused_ops(py::module_& m) {
                              static_cast<uint32_t>(epoch), c10::cuda::getCurrentCUDAStream().stream());
         },
         py::arg("input"), py::arg("output"), py::arg("buf_off"), py::arg("capacity_bytes"), py::arg("epoch"));
-  // Fused push all-reduce (sum) for medium messages; out may be the input tensor.
-  f.def("allreduce_push",
-        [](const torch::Tensor& in, torch::Tensor& out, int64_t area_off, int64_t capacity_bytes, int64_t flags_off,
-           torch::Tensor& counters, int64_t epoch, int ctas) {
+  // Fused push collectives (mode: 0 all-reduce, 1 reduce-scatter, 2 all-gather, 3 all-to-all).
+  f.def("collective_push",
+        [](int mode, const torch::Tensor& in, torch::Tensor& out, int64_t area_off, int64_t capacity_bytes,
+           int64_t flags_off, torch::Tensor& counters, int64_t epoch, int ctas) {
           TORCH_CHECK(in.is_cuda() && out.is_cuda() && in.is_contiguous() && out.is_contiguous() &&
-                          in.scalar_type() == out.scalar_type() && in.numel() == out.numel(),
-                      "allreduce_push: contiguous CUDA tensors of one dtype and size");
+                          in.scalar_type() == out.scalar_type(), "collective_push: contiguous CUDA tensors of one dtype");
+          TORCH_CHECK(mode >= 0 && mode <= 3, "collective_push: mode 0..3");
           int dtype = -1;
           if (in.scalar_type() == torch::kFloat32) dtype = 0;
           else if (in.scalar_type() == torch::kFloat16) dtype = 1;
           else if (in.scalar_type() == torch::kBFloat16) dtype = 2;
-          TORCH_CHECK(dtype >= 0, "allreduce_push: float32, float16 or bfloat16");
-          gemm::allreduce_push(peer_bases(), static_cast<uint64_t>(area_off), static_cast<uint64_t>(capacity_bytes),
-                               static_cast<uint64_t>(flags_off), as_u32(counters, 2, "counters"), in.data_ptr(),
-                               out.data_ptr(), static_cast<uint64_t>(in.nbytes()), dtype,
-                               static_cast<uint32_t>(epoch), c10::cuda::getCurrentCUDAStream().stream(), ctas);
+          TORCH_CHECK(dtype >= 0, "collective_push: float32, float16 or bfloat16");
+          const gemm::PeerBases peers = peer_bases();
+          const int64_t full = mode == gemm::kPushAllGather ? out.nbytes() : in.nbytes();
+          const int64_t want_out = mode == gemm::kPushReduceScatter ? full / peers.world : full;
+          const int64_t want_in = mode == gemm::kPushAllGather ? full / peers.world : full;
+          TORCH_CHECK(static_cast<int64_t>(out.nbytes()) == want_out && static_cast<int64_t>(in.nbytes()) == want_in,
+                      "collective_push: tensor sizes do not match the collective");
+          gemm::collective_push(static_cast<gemm::PushMode>(mode), peers, static_cast<uint64_t>(area_off),
+                                static_cast<uint64_t>(capacity_bytes), static_cast<uint64_t>(flags_off),
+                                as_u32(counters, 2, "counters"), in.data_ptr(), out.data_ptr(),
+                                static_cast<uint64_t>(full), dtype, static_cast<uint32_t>(epoch),
+                                c10::cuda::getCurrentCUDAStream().stream(), ctas);
         },
-        py::arg("input"), py::arg("output"), py::arg("area_off"), py::arg("capacity_bytes"), py::arg("flags_off"),
-        py::arg("counters"), py::arg("epoch"), py::arg("ctas"));
+        py::arg("mode"), py::arg("input"), py::arg("output"), py::arg("area_off"), py::arg("capacity_bytes"),
+        py::arg("flags_off"), py::arg("counters"), py::arg("epoch"), py::arg("ctas"));
   // MoE router on its own: top-2 expert indices, renormalised gates, the row each choice claims
   // in its expert's batch, and the per-expert token counts.  scratch: int32[experts + 1].
   f.def("moe_route",

@@ -60,13 +60,18 @@ void ar_residual_rmsnorm(const PeerBases& peers, uint8_t* mc_base, uint64_t x_of
 void allreduce_ll(const PeerBases& peers, uint64_t buf_off, uint64_t capacity_bytes, const void* in, void* out,
                   uint64_t bytes, int dtype, uint32_t epoch, cudaStream_t stream, uint64_t timeout_ms = 2000);
 
-// Medium-size all-reduce (sum): push reduce-scatter, reduce, push all-gather in one kernel; in / out
-// are ordinary device tensors (out may alias in).  area_off: symmetric bytes
-// [2][2][world][ceil(capacity / 16 / world) * 16]; flags_off: symmetric u32[2 * world], zeroed once;
-// counters: local zero-initialised u32[2].  `ctas` must be the same for every call of an instance.
-void allreduce_push(const PeerBases& peers, uint64_t area_off, uint64_t capacity_bytes, uint64_t flags_off,
-                    uint32_t* counters, const void* in, void* out, uint64_t bytes, int dtype, uint32_t epoch,
-                    cudaStream_t stream, int ctas, uint64_t timeout_ms = 2000);
+// Fused push collectives for small and medium messages; in / out are ordinary device tensors.
+//   kPushAllReduce      sum; push reduce-scatter, reduce, push all-gather; out may alias in
+//   kPushReduceScatter  sum; in [bytes], out [bytes / world] = this rank's slice
+//   kPushAllGather      in [bytes / world], out [bytes]
+//   kPushAllToAll       in [bytes] (part p goes to rank p), out [bytes] (part s came from rank s)
+// `bytes` is the full message.  area_off: symmetric bytes [2][2][world][ceil(capacity / 16 / world) * 16];
+// flags_off: symmetric u32[2 * world], zeroed once; counters: local zero-initialised u32[2].
+// `ctas` must be the same for every call that shares the counters.
+enum PushMode : int { kPushAllReduce = 0, kPushReduceScatter = 1, kPushAllGather = 2, kPushAllToAll = 3 };
+void collective_push(PushMode mode, const PeerBases& peers, uint64_t area_off, uint64_t capacity_bytes,
+                     uint64_t flags_off, uint32_t* counters, const void* in, void* out, uint64_t bytes, int dtype,
+                     uint32_t epoch, cudaStream_t stream, int ctas, uint64_t timeout_ms = 2000);
 
 // ---- expert-parallel MoE feed-forward (top-2 routing) ------------------------------------------------
 // Symmetric-heap offsets (identical on every rank) of the buffers the three kernels share.

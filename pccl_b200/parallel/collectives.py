@@ -120,6 +120,29 @@ def _push_eligible(tensor: torch.Tensor, op: str, algorithm: Optional[str]) -> b
             and tensor.data_ptr() % 16 == 0 and tensor.dtype in (torch.float32, torch.float16, torch.bfloat16))
 
 
+def _push(mode: int, input: torch.Tensor, output: torch.Tensor) -> None:
+    push = _state["push"]
+    push["epoch"] += 1
+    push["native"].collective_push(mode, input, output, push["areas"].heap_offset, PUSH_MAX_BYTES,
+                                   push["flags"].heap_offset, push["counters"], push["epoch"], _PUSH_CTAS)
+
+
+def _push_ok(full: torch.Tensor, part: torch.Tensor, algorithm: Optional[str], executor: Optional[str] = None,
+             op: str = "sum") -> bool:
+    """Reduce-scatter / all-gather / all-to-all through the push kernel: `full` is the whole message.
+
+    The answer depends only on things that are the same on every rank (sizes, dtype, arguments); the part
+    may be this rank's slice of `full` (the in-place conventions of all-gather and reduce-scatter)."""
+    if _state.get("push") is None or algorithm not in (None, "push") or executor is not None or op != "sum":
+        return False
+    world = _state["world"]
+    nbytes = full.numel() * full.element_size()
+    return (full.is_cuda and part.is_cuda and full.is_contiguous() and part.is_contiguous()
+            and full.dtype == part.dtype and full.dtype in (torch.float32, torch.float16, torch.bfloat16)
+            and 0 < nbytes <= PUSH_MAX_BYTES and nbytes % (16 * world) == 0
+            and full.data_ptr() % 16 == 0 and part.data_ptr() % 16 == 0)
+
+
 def _ll_eligible(tensor: torch.Tensor, op: str, algorithm: Optional[str]) -> bool:
     ll = _state.get("ll")
     if ll is None or op != "sum" or algorithm not in (None, "ll"):
@@ -220,8 +243,7 @@ def all_reduce(tensor: torch.Tensor, op: str = "sum", algorithm: Optional[str] =
     if _push_eligible(tensor, op, algorithm):
         push = _state["push"]
         push["epoch"] += 1
-        push["native"].allreduce_push(tensor, tensor, push["areas"].heap_offset, PUSH_MAX_BYTES,
-                                      push["flags"].heap_offset, push["counters"], push["epoch"], _PUSH_CTAS)
+        _push(0, tensor, tensor)
         return tensor
     if algorithm == "push":
         raise ValueError("the push all-reduce takes contiguous, 16-byte aligned f32/f16/bf16 sums of at most "
@@ -242,7 +264,12 @@ def _run(name: str, input: torch.Tensor, output: torch.Tensor, async_op: bool) -
 def reduce_scatter(output: torch.Tensor, input: torch.Tensor, op: str = "sum",
                    algorithm: Optional[str] = None, channels: Optional[int] = None,
                    async_op: bool = False) -> torch.Tensor:
-    """``async_op``: enqueue on the current stream and return (``synchronize`` checks the status later)."""
+    """``async_op``: enqueue on the current stream and return (``synchronize`` checks the status later).
+
+    Sums of up to ``PUSH_MAX_BYTES`` run in the fused push kernel unless an algorithm is forced."""
+    if output.numel() * _state["world"] == input.numel() and _push_ok(input, output, algorithm, op=op):
+        _push(1, input, output)
+        return output
     name = ensure_plan("reduce_scatter", input.numel(), input.dtype, algorithm, channels, op)
     _run(name, input, output, async_op)
     return output
@@ -252,6 +279,9 @@ def all_gather(output: torch.Tensor, input: torch.Tensor, algorithm: Optional[st
                channels: Optional[int] = None, executor: Optional[str] = None,
                async_op: bool = False) -> torch.Tensor:
     """``executor="ce"`` moves the shards with the copy engines (``algorithm`` twoshot)."""
+    if input.numel() * _state["world"] == output.numel() and _push_ok(output, input, algorithm, executor):
+        _push(2, input, output)
+        return output
     if executor == "ce":
         algorithm = "twoshot"
     name = ensure_plan("allgather", output.numel(), output.dtype, algorithm, channels, executor=executor)
@@ -262,6 +292,9 @@ def all_gather(output: torch.Tensor, input: torch.Tensor, algorithm: Optional[st
 def all_to_all(output: torch.Tensor, input: torch.Tensor, algorithm: Optional[str] = None,
                channels: Optional[int] = None, executor: Optional[str] = None,
                async_op: bool = False) -> torch.Tensor:
+    if input.numel() == output.numel() and _push_ok(input, output, algorithm, executor):
+        _push(3, input, output)
+        return output
     if executor == "ce":
         algorithm = "twoshot"
     name = ensure_plan("alltoall", input.numel(), input.dtype, algorithm or "twoshot", channels, executor=executor)

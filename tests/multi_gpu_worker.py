@@ -136,6 +136,32 @@ def main():
     dist.all_gather(gathered, y)
     assert all(torch.equal(gathered[0], g) for g in gathered), "push allreduce differs between ranks"
 
+    # push reduce-scatter / all-gather / all-to-all on ordinary tensors, against NCCL
+    for dtype in (torch.float32, torch.bfloat16):
+        for shard in (8, 1000 * 8, 1 << 18):
+            n = shard * world
+            gen = torch.Generator(device="cuda").manual_seed(77 + rank + shard)
+            full_in = torch.randn(n, device="cuda", generator=gen).to(dtype)
+            mine = torch.randn(shard, device="cuda", generator=gen).to(dtype)
+            for call in range(2):
+                ref = torch.empty(shard, device="cuda", dtype=torch.float32)
+                dist.reduce_scatter_tensor(ref, full_in.float())
+                got = pp.reduce_scatter(torch.empty(shard, device="cuda", dtype=dtype), full_in, algorithm="push")
+                ref_g = torch.empty(n, device="cuda", dtype=dtype)
+                dist.all_gather_into_tensor(ref_g, mine)
+                got_g = pp.all_gather(torch.empty(n, device="cuda", dtype=dtype), mine, algorithm="push")
+                ref_a = torch.empty(n, device="cuda", dtype=dtype)
+                dist.all_to_all_single(ref_a, full_in)
+                got_a = pp.all_to_all(torch.empty(n, device="cuda", dtype=dtype), full_in, algorithm="push")
+                torch.cuda.synchronize()
+                __import__("pccl_b200.ops.gemm", fromlist=["check"]).check()
+                atol = 1e-5 if dtype == torch.float32 else 0.06
+                torch.testing.assert_close(got.float(), ref, atol=atol, rtol=2e-2,
+                                           msg=lambda t: f"push reduce_scatter {dtype} shard={shard} rank {rank}: {t}")
+                assert torch.equal(got_g, ref_g), f"push all_gather {dtype} shard={shard} rank {rank}"
+                assert torch.equal(got_a, ref_a), f"push all_to_all {dtype} shard={shard} rank {rank}"
+        report["checked"] += 1
+
     # every rank must hold bit-identical results (sums are taken in rank order)
     x = torch.randn(4096, device="cuda", generator=torch.Generator(device="cuda").manual_seed(5 + rank))
     y = pp.all_reduce(x.clone(), algorithm="ll")
