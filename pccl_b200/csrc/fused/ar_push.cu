@@ -197,8 +197,10 @@ __global__ void __launch_bounds__(kPushThreads) allreduce_push_kernel(const Push
 #pragma unroll
         for (int s = 0; s < kW; ++s) {
           const int ss = s < world ? s : me;
-          raw[v][s] = ss == me ? ptx::ld_local_v4(in + base + i)
-                               : ptx::ld_local_v4(reinterpret_cast<const uint4*>(a_mine + static_cast<uint64_t>(ss) * p.slice_cap) + i);
+          // select the address, then load unconditionally (one instruction, no branch around it)
+          const uint4* ptr = ss == me ? in + base + i
+                                      : reinterpret_cast<const uint4*>(a_mine + static_cast<uint64_t>(ss) * p.slice_cap) + i;
+          raw[v][s] = ptx::ld_local_v4(ptr);
         }
       }
 #pragma unroll

@@ -165,7 +165,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       for (uint32_t k = 0; k < c.step_count; ++k) {
         const Step& s = lp.steps[c.step_begin + k];
         steps.append(py::make_tuple(static_cast<int>(s.kind), static_cast<int>(s.n_wait), static_cast<int>(s.n_notify),
-                                    static_cast<int>(s.n_dep), s.peer, s.bytes));
+                                    static_cast<int>(s.n_dep), s.peer, s.bytes, static_cast<int>(s.defer_barrier)));
       }
       py::dict cd;
       cd["ctas"] = c.num_ctas; cd["barriers"] = c.barriers_per_launch; cd["steps"] = steps;

@@ -46,3 +46,18 @@ def test_config_describes_every_option():
     cfg = config.PcclConfig.from_env({"PCCL_LL_MAX_BYTES": "64K", "PCCL_NUM_BLOCKS": "64"})
     assert cfg.ll_max_bytes == 64 << 10 and cfg.num_blocks == 64
     assert config.PcclConfig.from_env(cfg.to_env()).num_blocks == 64
+
+
+def test_lowering_runs_independent_gather_copies_without_barriers():
+    """Two-shot's W-1 gather copies form one barrier-free run; the reduce before them keeps its barrier."""
+    from pccl_b200 import Compiler, engine
+    from pccl_b200.dsl.algorithms import TwoShotAllreduce
+    native = engine.load_native()
+    world, numel = 4, 1 << 20
+    plan = Compiler().compile_to_json(TwoShotAllreduce().build_allreduce(1, world, numel, "float32", "sm", 1))
+    summary = native.lower_plan_summary(plan, 1, world, 64 << 20, 16, False)
+    steps = summary["chain_list"][0]["steps"]
+    copies = [s for s in steps if s[0] == 1 and s[5] > 0]        # kind 1 = pull copy
+    assert len(copies) == world - 1
+    assert [s[6] for s in copies] == [1] * (world - 2) + [0]     # all but the last defer their barrier
+    assert all(s[6] == 0 for s in steps if s[0] not in (1, 2))   # nothing else does
