@@ -241,8 +241,6 @@ def all_reduce(tensor: torch.Tensor, op: str = "sum", algorithm: Optional[str] =
         ll["native"].allreduce_ll(tensor, tensor, ll["buf"].heap_offset, LL_MAX_BYTES, ll["epoch"])
         return tensor
     if _push_eligible(tensor, op, algorithm):
-        push = _state["push"]
-        push["epoch"] += 1
         _push(0, tensor, tensor)
         return tensor
     if algorithm == "push":
