@@ -61,6 +61,23 @@ class ExpertParallelMoE:
         return self.op(x, out)
 
 
+def partition_buckets(sizes: Sequence[int], bucket_elems: int) -> List[List[int]]:
+    """Greedy in-order packing: indices of consecutive tensors whose element counts sum to at most
+    ``bucket_elems`` (a tensor larger than that gets a bucket of its own)."""
+    buckets: List[List[int]] = []
+    current: List[int] = []
+    used = 0
+    for i, n in enumerate(sizes):
+        if current and used + n > bucket_elems:
+            buckets.append(current)
+            current, used = [], 0
+        current.append(i)
+        used += n
+    if current:
+        buckets.append(current)
+    return buckets
+
+
 class GradientBuckets:
     """Average gradients over the data-parallel ranks through the plan engine.
 
@@ -75,18 +92,8 @@ class GradientBuckets:
         self.params: List[torch.nn.Parameter] = [p for p in params if p.requires_grad]
         self.dtype = dtype
         esize = torch.empty((), dtype=dtype).element_size()
-        world = _c.init().world
-        self.buckets: List[Sequence[int]] = []
-        current, used = [], 0
-        for i, p in enumerate(self.params):
-            n = p.numel()
-            if current and (used + n) * esize > bucket_bytes:
-                self.buckets.append(current)
-                current, used = [], 0
-            current.append(i)
-            used += n
-        if current:
-            self.buckets.append(current)
+        world = int(_c._state["world"])          # the engine is already connected (pccl_b200.parallel.init)
+        self.buckets: List[Sequence[int]] = partition_buckets([p.numel() for p in self.params], bucket_bytes // esize)
         # every bucket's element count is rounded up so that it divides over ranks and 16-byte vectors
         self.sizes = []
         for idxs in self.buckets:

@@ -61,3 +61,12 @@ def test_lowering_runs_independent_gather_copies_without_barriers():
     assert len(copies) == world - 1
     assert [s[6] for s in copies] == [1] * (world - 2) + [0]     # all but the last defer their barrier
     assert all(s[6] == 0 for s in steps if s[0] not in (1, 2))   # nothing else does
+
+
+def test_gradient_bucket_partition():
+    from pccl_b200.parallel.layers import partition_buckets
+    assert partition_buckets([10, 10, 10, 50, 5], 25) == [[0, 1], [2], [3], [4]]
+    assert partition_buckets([], 8) == []
+    assert partition_buckets([100], 8) == [[0]]
+    flat = [i for b in partition_buckets(list(range(1, 40)), 64) for i in b]
+    assert flat == list(range(39))
