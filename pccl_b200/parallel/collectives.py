@@ -37,7 +37,10 @@ _state: Dict[str, object] = {"group": None, "rank": 0, "world": 1, "registered":
 
 
 def init(group: Optional[dist.ProcessGroup] = None):
-    """Connect the engine over ``group`` (default group when None)."""
+    """Connect the engine over ``group`` (default group when None).  Collective; a second call with the
+    engine already connected returns it without allocating anything again."""
+    if _state.get("connected"):
+        return _engine.get_engine()
     _state["group"] = group
     if dist.is_initialized():
         _state["rank"], _state["world"] = dist.get_rank(group), dist.get_world_size(group)
@@ -49,6 +52,7 @@ def init(group: Optional[dist.ProcessGroup] = None):
         _engine.get_engine()
     _setup_ll(group)
     _setup_push(group)
+    _state["connected"] = True
     return _engine.get_engine()
 
 
