@@ -115,21 +115,22 @@ __device__ __forceinline__ uint4 pack(const float* acc) {
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-// All CTAs arrive; the one that completes the count posts `flag_row[me]` at every peer.
+// All CTAs arrive; the one that completes the count posts `flag_row[me]` at every peer, one thread
+// per peer so that the W - 1 release operations travel in parallel.
 __device__ __forceinline__ void arrive_and_post(const PushParams& p, int phase) {
+  __shared__ uint32_t is_last;
   __syncthreads();
   if (threadIdx.x == 0) {
     ptx::fence_sys();
     const uint32_t seen = atomicAdd(p.counters + phase, 1u) + 1u;
-    if (seen == p.epoch * gridDim.x) {
-      ptx::fence_sys();
-      const int me = p.peers.rank;
-      for (int k = 1; k < p.peers.world; ++k) {
-        const int peer = (me + k) % p.peers.world;
-        uint32_t* flags = reinterpret_cast<uint32_t*>(p.peers.base[peer] + p.flags_off) + phase * p.peers.world;
-        ptx::red_release_sys_add(flags + me, 1u);
-      }
-    }
+    is_last = seen == p.epoch * gridDim.x ? 1u : 0u;
+  }
+  __syncthreads();
+  const int me = p.peers.rank, peer = static_cast<int>(threadIdx.x);
+  if (is_last && peer < p.peers.world && peer != me) {
+    ptx::fence_sys();
+    uint32_t* flags = reinterpret_cast<uint32_t*>(p.peers.base[peer] + p.flags_off) + phase * p.peers.world;
+    ptx::red_release_sys_add(flags + me, 1u);
   }
 }
 
