@@ -1,5 +1,7 @@
 #include "engine.h"
 
+#include "../common/launch.h"
+
 #include <unistd.h>
 
 #include <algorithm>
@@ -64,6 +66,7 @@ RankContext::RankContext(int rank, int world, int device, size_t buffer_bytes, s
   PCCL_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&h_status_), sizeof(DeviceStatus), cudaHostAllocMapped));
   std::memset(h_status_, 0, sizeof(DeviceStatus));
   PCCL_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&h_status_dev_), h_status_, 0));
+  trace_ = Environs::get_flag("PCCL_TRACE", false);
   PCCL_CHECK(set_mover_tuning(static_cast<uint32_t>(Environs::get_int("PCCL_MOVER_TUNING", 0))) == 0,
              "cannot set the data-mover tuning word");
 }
@@ -74,6 +77,7 @@ RankContext::~RankContext() {
     if (op.d_tables) cudaFree(op.d_tables);
     if (op.d_program) cudaFree(op.d_program);
     if (op.chain_sync) cudaFree(op.chain_sync);
+    if (op.d_trace) cudaFree(op.d_trace);
   }
   if (h_status_) cudaFreeHost(h_status_);
 }
@@ -99,6 +103,7 @@ RegisteredOp& RankContext::register_op(const std::string& name, const std::strin
     if (o.d_tables) cudaFree(o.d_tables);
     if (o.d_program) cudaFree(o.d_program);
     if (o.chain_sync) cudaFree(o.chain_sync);
+    if (o.d_trace) cudaFree(o.d_trace);
     ops_.erase(old);
   }
   RegisteredOp& ref = *fresh;
@@ -113,13 +118,16 @@ void RankContext::upload(RegisteredOp& op) {
   lo.rank = rank_;
   lo.world = world_;
   lo.multicast = heap_.multicast_ready();
-  const uint32_t cap = cta_cap_ ? cta_cap_ : static_cast<uint32_t>(Environs::get_int("PCCL_NUM_BLOCKS", 128));
+  uint32_t cap = cta_cap_ ? cta_cap_ : static_cast<uint32_t>(Environs::get_int("PCCL_NUM_BLOCKS", 128));
+  // Never more CTAs than can be resident at once (the interpreter's CTAs wait on one another).
+  const int resident = plan_interp_max_ctas(kInterpThreads);
+  if (resident > 0) cap = std::min<uint32_t>(cap, static_cast<uint32_t>(resident));
   const int64_t forced = Environs::get_int("PCCL_FORCE_BLOCKS", 0);
   lo.total_ctas = forced > 0 ? std::min<uint32_t>(static_cast<uint32_t>(forced), cap) : auto_ctas(op.plan, cap);
   lo.min_bytes_per_cta = static_cast<uint64_t>(Environs::get_int("PCCL_MIN_BYTES_PER_BLOCK", 16 << 10));
   // Templates of this library end with their own barrier; everything else gets one appended.
   const std::string& algo = op.plan.algorithm;
-  const bool self_fenced = algo == "oneshot" || algo == "twoshot" || algo == "direct" || algo == "nvls";
+  const bool self_fenced = algo == "oneshot" || algo == "twoshot" || algo == "direct" || algo == "nvls" || algo == "hybrid";
   lo.defer_barriers = Environs::get_flag("PCCL_DEFER_BARRIERS", true);
   lo.closing_barrier = !self_fenced && !op.plan.collective_type.empty() &&
                        Environs::get_flag("PCCL_CLOSING_BARRIER", true);
@@ -174,6 +182,13 @@ void RankContext::upload(RegisteredOp& op) {
   P.status = d_status_;
   P.host_status = h_status_dev_;
   P.timeout_ns = timeout_ns_;
+  if (op.d_trace) { cudaFree(op.d_trace); op.d_trace = nullptr; }
+  if (trace_ && !lp.steps.empty()) {
+    const size_t bytes = lp.steps.size() * kTraceStamps * sizeof(uint64_t);
+    PCCL_CUDA(cudaMalloc(reinterpret_cast<void**>(&op.d_trace), bytes));
+    PCCL_CUDA(cudaMemset(op.d_trace, 0, bytes));
+  }
+  P.trace = op.d_trace;
   if (op.d_program == nullptr) PCCL_CUDA(cudaMalloc(reinterpret_cast<void**>(&op.d_program), sizeof(RankProgram)));
   PCCL_CUDA(cudaMemcpy(op.d_program, &P, sizeof P, cudaMemcpyHostToDevice));
 
@@ -280,6 +295,30 @@ void RankContext::check_status(const std::string& op_name) {
   throw TimeoutError(msg.str());
 }
 
+std::vector<TraceStep> RankContext::read_trace(const RegisteredOp& op) {
+  std::vector<TraceStep> out;
+  if (op.d_trace == nullptr) return out;
+  const LoweredProgram& lp = op.lowered;
+  std::vector<uint64_t> raw(lp.steps.size() * kTraceStamps);
+  PCCL_CUDA(cudaMemcpy(raw.data(), op.d_trace, raw.size() * sizeof(uint64_t), cudaMemcpyDeviceToHost));
+  uint64_t origin = ~0ull;
+  for (uint64_t v : raw) if (v != 0 && v < origin) origin = v;
+  for (size_t c = 0; c < lp.chains.size(); ++c) {
+    const Chain& ch = lp.chains[c];
+    for (uint32_t k = 0; k < ch.step_count; ++k) {
+      const Step& s = lp.steps[ch.step_begin + k];
+      TraceStep t{};
+      t.chain = static_cast<uint32_t>(c); t.step = k; t.kind = s.kind; t.ctas = ch.num_ctas; t.bytes = s.bytes;
+      for (int i = 0; i < kTraceStamps; ++i) {
+        const uint64_t v = raw[(ch.step_begin + k) * kTraceStamps + i];
+        t.t[i] = v ? v - origin : 0;
+      }
+      out.push_back(t);
+    }
+  }
+  return out;
+}
+
 void RankContext::reset_op_counters(RegisteredOp& op) {
   const size_t counters = std::max<size_t>(1, op.lowered.chains.size());
   PCCL_CUDA(cudaMemset(op.chain_sync, 0, 2 * counters * sizeof(uint32_t)));
@@ -319,7 +358,7 @@ Engine::Engine() {
   Environs::register_option("WORLD_SIZE", "number of ranks (default 1)");
   Environs::register_option("PCCL_BUFFER_SIZE", "bytes of the plan working buffer (default 1G)");
   Environs::register_option("PCCL_ARENA_SIZE", "bytes of symmetric memory for fused operators (default 1G)");
-  Environs::register_option("PCCL_NUM_BLOCKS", "upper bound of CTAs per launch (default 96)");
+  Environs::register_option("PCCL_NUM_BLOCKS", "upper bound of CTAs per launch (default 128, never more than can be resident at once)");
   Environs::register_option("PCCL_FORCE_BLOCKS", "exact CTA count per launch (overrides the heuristic)");
   Environs::register_option("PCCL_WAIT_TIMEOUT_MS", "budget of device-side waits per launch (default 10000)");
   Environs::register_option("PCCL_NVLS_ENABLE", "0 disables NVLS multicast (default: on when supported)");
@@ -389,7 +428,13 @@ void Engine::exeOp(const std::string& name, const void* in, size_t in_bytes, voi
       op.ce->run(op.host_program.data, rank_, op.launch_index, stream);
     } else {
       LaunchParams lp{op.d_program, op.launch_index};
-      LaunchConfig cfg{std::max<uint32_t>(1, op.lowered.total_ctas), op.threads, 1, false, op.host_program.dtype};
+      // Chains use multi-CTA barriers and lead-CTA waits on peers: every CTA must be resident, also
+      // next to a compute kernel that holds part of the GPU, hence a cooperative launch.
+      // (A plan with more chains than resident CTAs cannot be launched that way; it keeps the
+      // ordinary launch and needs the GPU to itself.)
+      const uint32_t grid = std::max<uint32_t>(1, op.lowered.total_ctas);
+      const bool coop = cooperative_launches() && static_cast<int>(grid) <= plan_interp_max_ctas(op.threads);
+      LaunchConfig cfg{grid, op.threads, 1, coop, op.host_program.dtype};
       const int err = launch_plan_interp(lp, cfg, stream);
       PCCL_CHECK(err == 0, "kernel launch failed: " << cudaGetErrorString(static_cast<cudaError_t>(err)));
     }

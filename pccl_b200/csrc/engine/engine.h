@@ -42,6 +42,7 @@ struct RegisteredOp {
   RankProgram* d_program = nullptr;     // device copy (Engine mode)
   uint32_t* chain_sync = nullptr;       // control-area counters
   uint32_t* chain_progress = nullptr;
+  uint64_t* d_trace = nullptr;          // kTraceStamps timestamps per step when tracing is on
   uint32_t launch_index = 0;
   uint32_t threads = kInterpThreads;
   std::unique_ptr<CeSchedule> ce;       // set when the copy-engine executor runs this operation
@@ -49,6 +50,13 @@ struct RegisteredOp {
 };
 
 struct IoSegment { size_t heap_offset, user_offset, bytes; };
+
+// One step of the most recent launch as the device saw it (times in ns since the launch's first stamp).
+struct TraceStep {
+  uint32_t chain, step, kind, ctas;
+  uint64_t bytes;
+  uint64_t t[kTraceStamps];
+};
 
 class RankContext {
  public:
@@ -83,9 +91,17 @@ class RankContext {
   void reset();
   void reset_op_counters(RegisteredOp& op);
 
+  // Device timeline (optional, PCCL_TRACE=1 or set_trace): every step of a launch stamps
+  // %globaltimer four times; read_trace returns the most recent launch of `op` after a
+  // synchronize.  The replacement for an external timeline profiler (the reference relies on
+  // nsys + tests/parse_nsys.py:18-143).
+  void set_trace(bool on) { if (on != trace_) { trace_ = on; tables_dirty_ = true; } }
+  bool tracing() const { return trace_; }
+  std::vector<TraceStep> read_trace(const RegisteredOp& op);
+
   uint64_t timeout_ns() const { return timeout_ns_; }
   void set_timeout_ms(uint64_t ms) { timeout_ns_ = ms * 1000000ull; tables_dirty_ = true; }
-  // Upper bound of CTAs per launch for programs of this rank (0 = PCCL_NUM_BLOCKS, default 96).
+  // Upper bound of CTAs per launch for programs of this rank (0 = PCCL_NUM_BLOCKS, default 128).
   void set_cta_cap(uint32_t cap) { cta_cap_ = cap; }
   void mark_dirty() { tables_dirty_ = true; }
   bool dirty() const { return tables_dirty_; }
@@ -109,6 +125,7 @@ class RankContext {
   DeviceStatus* h_status_dev_ = nullptr; // device-visible address of the mirror
   uint64_t timeout_ns_;
   bool tables_dirty_ = false;
+  bool trace_ = false;
   uint32_t cta_cap_ = 0;
   friend class Engine;
   friend class LocalCluster;

@@ -234,10 +234,14 @@ __global__ void __launch_bounds__(kInterpThreads, 1) plan_interp_kernel(const La
   w.chain = chain_id;
 
   uint32_t* my_signals = P.signals[P.rank];
+  // Timeline stamps of this chain's steps (lead CTA, thread 0), when tracing is on.
+  uint64_t* trace = (P.trace != nullptr && lead && threadIdx.x == 0)
+                        ? P.trace + static_cast<uint64_t>(chain.step_begin) * kTraceStamps : nullptr;
 
   for (uint32_t k = 0; k < chain.step_count; ++k) {
     const Step s = P.steps[chain.step_begin + k];
     w.step = k;
+    if (trace) trace[k * kTraceStamps + 0] = ptx::globaltimer();
 
     // 1. waits (lead CTA, one lane per wait)
     const uint32_t nwait = s.n_wait + s.n_dep;
@@ -281,6 +285,8 @@ __global__ void __launch_bounds__(kInterpThreads, 1) plan_interp_kernel(const La
       }
     }
 
+    if (trace) trace[k * kTraceStamps + 1] = ptx::globaltimer();
+
     // 3. data
     if (s.kind != kStepNoop && s.bytes) {
       if (threadIdx.x == 0) s_dst = describe_step(P, s, &s_src);
@@ -302,6 +308,8 @@ __global__ void __launch_bounds__(kInterpThreads, 1) plan_interp_kernel(const La
       __syncthreads();
     }
 
+    if (trace) trace[k * kTraceStamps + 2] = ptx::globaltimer();
+
     // 5. notifies + progress (lead CTA)
     if (lead) {
       if (publishes && threadIdx.x < s.n_notify) {
@@ -315,6 +323,7 @@ __global__ void __launch_bounds__(kInterpThreads, 1) plan_interp_kernel(const La
         ptx::st_release_sys(P.chain_progress + chain_id, progress_base + k + 1);
       }
     }
+    if (trace) trace[k * kTraceStamps + 3] = ptx::globaltimer();
   }
 }
 
@@ -356,11 +365,16 @@ int set_mover_tuning(uint32_t word) {
 }
 
 int plan_interp_max_ctas(int threads) {
+  // Asked on every launch: remember the answer per device (the block size is always kInterpThreads).
+  static int cached[64] = {};
   int dev = 0, sms = 0, per_sm = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  const bool cacheable = dev >= 0 && dev < 64 && threads == static_cast<int>(kInterpThreads);
+  if (cacheable && cached[dev] > 0) return cached[dev];
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, plan_interp_kernel<kF32>, threads, 0) != cudaSuccess)
     return 0;
+  if (cacheable) cached[dev] = sms * per_sm;
   return sms * per_sm;
 }
 

@@ -103,7 +103,14 @@ struct RankProgram {
   DeviceStatus* status;            // device copy: abort flag polled by every wait
   DeviceStatus* host_status;       // pinned host mirror, written once by the failing thread
   uint64_t timeout_ns;
+  // Optional timeline of the most recent launch (null = tracing off): kTraceStamps
+  // %globaltimer values per step, written by thread 0 of the chain's lead CTA.
+  uint64_t* trace;
 };
+
+// Stamps of one step: [0] step reached, [1] waits satisfied and followers released (data starts),
+// [2] completion barrier passed (every CTA's data is written), [3] signals posted.
+constexpr int kTraceStamps = 4;
 
 struct LaunchParams {
   const RankProgram* programs;     // [gridDim.y]

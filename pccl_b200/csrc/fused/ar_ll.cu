@@ -16,6 +16,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include "../common/launch.h"
 #include "../common/util.h"
 #include "../engine/cuda_driver.h"
 #include "../ptx/sync.cuh"
@@ -154,12 +155,14 @@ void allreduce_ll(const PeerBases& peers, uint64_t buf_off, uint64_t capacity_by
   // One unit per thread up to 128 CTAs, then a grid-stride loop.
   uint64_t grid = (p.units + kLLThreads - 1) / kLLThreads;
   if (grid > 128) grid = 128;
+  // Every CTA polls for packets that the same CTA of each peer pushes: all CTAs must be resident.
+  // (The grid follows from the message size alone, so it is the same on every rank; 128 CTAs of
+  // 256 threads are far below the resident limit.)
   switch (dtype) {
-    case 0: allreduce_ll_kernel<0><<<static_cast<unsigned>(grid), kLLThreads, 0, stream>>>(p); break;
-    case 1: allreduce_ll_kernel<1><<<static_cast<unsigned>(grid), kLLThreads, 0, stream>>>(p); break;
-    default: allreduce_ll_kernel<2><<<static_cast<unsigned>(grid), kLLThreads, 0, stream>>>(p); break;
+    case 0: launch_coresident(allreduce_ll_kernel<0>, static_cast<uint32_t>(grid), kLLThreads, 0, stream, p, true); break;
+    case 1: launch_coresident(allreduce_ll_kernel<1>, static_cast<uint32_t>(grid), kLLThreads, 0, stream, p, true); break;
+    default: launch_coresident(allreduce_ll_kernel<2>, static_cast<uint32_t>(grid), kLLThreads, 0, stream, p, true); break;
   }
-  PCCL_CUDA(cudaGetLastError());
 }
 
 }  // namespace gemm

@@ -21,6 +21,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include "../common/launch.h"
 #include "../common/util.h"
 #include "../engine/cuda_driver.h"
 #include "../ptx/sync.cuh"
@@ -287,11 +288,13 @@ void collective_push(PushMode mode, const PeerBases& peers, uint64_t area_off, u
   p.error = error_word();
   p.timeout_ns = timeout_ms * 1000000ull;
   // The grid is part of the completion count: it is the same for every call of an instance.
-#define PCCL_PUSH_LAUNCH(DT)                                                                      \
-  do {                                                                                            \
-    if (peers.world <= 2) allreduce_push_kernel<DT, 2><<<ctas, kPushThreads, 0, stream>>>(p);      \
-    else if (peers.world <= 4) allreduce_push_kernel<DT, 4><<<ctas, kPushThreads, 0, stream>>>(p); \
-    else allreduce_push_kernel<DT, 8><<<ctas, kPushThreads, 0, stream>>>(p);                       \
+  // Every CTA spins on flags that a peer posts when its last CTA arrives: the whole grid must be
+  // resident, here and on the peer.
+#define PCCL_PUSH_LAUNCH(DT)                                                                                  \
+  do {                                                                                                        \
+    if (peers.world <= 2) launch_coresident(allreduce_push_kernel<DT, 2>, ctas, kPushThreads, 0, stream, p, true);      \
+    else if (peers.world <= 4) launch_coresident(allreduce_push_kernel<DT, 4>, ctas, kPushThreads, 0, stream, p, true); \
+    else launch_coresident(allreduce_push_kernel<DT, 8>, ctas, kPushThreads, 0, stream, p, true);                       \
   } while (0)
   switch (dtype) {
     case 0: PCCL_PUSH_LAUNCH(0); break;
@@ -299,7 +302,6 @@ void collective_push(PushMode mode, const PeerBases& peers, uint64_t area_off, u
     default: PCCL_PUSH_LAUNCH(2); break;
   }
 #undef PCCL_PUSH_LAUNCH
-  PCCL_CUDA(cudaGetLastError());
 }
 
 }  // namespace gemm

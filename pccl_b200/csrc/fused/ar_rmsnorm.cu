@@ -16,6 +16,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include "../common/launch.h"
 #include "../common/util.h"
 #include "../engine/cuda_driver.h"
 #include "../ptx/multimem.cuh"
@@ -223,7 +224,7 @@ void ar_residual_rmsnorm(const PeerBases& peers, uint8_t* mc_base, uint64_t x_of
   if (smem > 48 * 1024)
     PCCL_CUDA(cudaFuncSetAttribute(ar_residual_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(smem)));
-  ar_residual_rmsnorm_kernel<<<grid, kThreadsNorm, smem, stream>>>(p);
+  launch_coresident(ar_residual_rmsnorm_kernel, static_cast<uint32_t>(grid), kThreadsNorm, smem, stream, p, true);
   PCCL_CUDA(cudaGetLastError());
 }
 

@@ -4,6 +4,7 @@
 #include <algorithm>
 #include <mutex>
 
+#include "../common/launch.h"
 #include "../engine/cuda_driver.h"
 #include "gemm_host.h"
 #include "moe_policies.cuh"
@@ -97,8 +98,13 @@ void launch(const MatrixDesc& a, const MatrixDesc& b, const typename Policy::Par
   if (grid > sm_count()) grid = sm_count();
   if (groups == 1 && grid - aux_ctas > tiles) grid = tiles + aux_ctas;
   if (grid - aux_ctas < 1) grid = aux_ctas + 1;
-  kernel<<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, g, params);
-  PCCL_CUDA(cudaGetLastError());
+  // Policies make CTAs wait on flags posted by other CTAs of this launch (reducers, copiers) and by
+  // the same kernel on the peers, so the grid must be resident as a whole.
+  CUtensorMap ta_arg = ta, tb_arg = tb;
+  Problem g_arg = g;
+  typename Policy::Params params_arg = params;
+  void* args[] = {&ta_arg, &tb_arg, &g_arg, &params_arg};
+  launch_coresident_args(kernel, static_cast<uint32_t>(grid), kThreads, kSmemBytes, stream, args, true);
   (void)attr_once;
 }
 

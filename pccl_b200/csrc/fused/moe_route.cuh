@@ -70,10 +70,17 @@ __global__ void __launch_bounds__(kMoeRouteWarps * 32) moe_route_kernel(const Mo
       for (int o = 16; o > 0; o >>= 1) logit[e] += __shfl_xor_sync(0xffffffffu, logit[e], o);
 
     // Top-2 of the softmax = top-2 of the logits; renormalised gates need only those two.
-    int e1 = 0, e2 = -1;
-    float l1 = logit[0], l2 = -INFINITY;
+    // The selection is total: a non-finite logit (a NaN or Inf activation makes the whole row
+    // non-finite) counts as the lowest value, and the two picks start as experts 0 and 1, so both
+    // are always valid, distinct expert numbers whatever the input holds.
 #pragma unroll
-    for (int e = 1; e < kE; ++e) {
+    for (int e = 0; e < kE; ++e)
+      if (!(fabsf(logit[e]) <= 3.0e38f)) logit[e] = -3.0e38f;
+    int e1 = 0, e2 = 1;
+    float l1 = logit[0], l2 = logit[1];
+    if (l2 > l1) { e1 = 1; e2 = 0; l1 = logit[1]; l2 = logit[0]; }
+#pragma unroll
+    for (int e = 2; e < kE; ++e) {
       if (logit[e] > l1) { l2 = l1; e2 = e1; l1 = logit[e]; e1 = e; }
       else if (logit[e] > l2) { l2 = logit[e]; e2 = e; }
     }

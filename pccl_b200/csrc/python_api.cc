@@ -54,6 +54,20 @@ int64_t numel_of(const std::vector<int64_t>& shape) {
   return n;
 }
 
+py::list trace_list(RankContext& ctx, const std::string& name) {
+  static const char* kinds[] = {"noop", "copy", "reduce", "put", "reduce_multi", "multimem.reduce",
+                                "multimem.store", "multimem.allreduce", "scale"};
+  py::list out;
+  for (const TraceStep& t : ctx.read_trace(ctx.op(name))) {
+    py::dict d;
+    d["chain"] = t.chain; d["step"] = t.step; d["kind"] = kinds[t.kind < 9 ? t.kind : 0];
+    d["ctas"] = t.ctas; d["bytes"] = t.bytes;
+    d["t_reached_ns"] = t.t[0]; d["t_data_ns"] = t.t[1]; d["t_done_ns"] = t.t[2]; d["t_posted_ns"] = t.t[3];
+    out.append(d);
+  }
+  return out;
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -81,6 +95,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("world", &Engine::world)
       .def("stats", &Engine::statsJson)
       .def("setTimeoutMs", [](Engine& e, uint64_t ms) { e.context().set_timeout_ms(ms); })
+      // Device timeline: setTrace(True), run, synchronize, then trace(name) lists every step of the
+      // last launch with its four %globaltimer stamps (ns since the launch's first stamp).
+      .def("setTrace", [](Engine& e, bool on) { e.context().set_trace(on); })
+      .def("trace", [](Engine& e, const std::string& name) { return trace_list(e.context(), name); })
       .def("bufferBytes", [](Engine& e) { return e.context().buffer_bytes(); })
       // View of the plan working buffer: collectives on it run without staging copies.
       .def("workingBuffer",
@@ -115,6 +133,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("regOp", &LocalCluster::regOp)
       .def("setTimeoutMs", &LocalCluster::set_timeout_ms)
       .def("setCtas", &LocalCluster::set_ctas)
+      .def("setTrace", [](LocalCluster& c, bool on) { for (int r = 0; r < c.world(); ++r) c.context(r).set_trace(on); })
+      .def("trace", [](LocalCluster& c, const std::string& name, int rank) { return trace_list(c.context(rank), name); })
       .def("reset", &LocalCluster::reset)
       .def("opInfo",
            [](LocalCluster& c, const std::string& name, int rank) {

@@ -30,7 +30,7 @@ from typing import Callable, List
 from ..decorators import CommunicationOp, Stream
 from ..graph import PrimitiveIRGraph
 from ..nodes import DeviceType
-from .base import CollectiveAlgorithm, all_pairs_barrier, channel_slices, finish
+from .base import SIGNAL_STRIDE, CollectiveAlgorithm, all_pairs_barrier, channel_slices, finish
 
 _BARRIER_A, _BARRIER_B, _BARRIER_C = 200, 300, 400
 
@@ -155,12 +155,20 @@ class TwoShotAllreduce(CollectiveAlgorithm):
 
 
 class NvlsAllreduce(CollectiveAlgorithm):
-    """In-switch reduction.  ``multimem.reduce`` reads a slice through the
-    multicast address (the switch returns the sum over all ranks' copies) and
-    stores it locally; ``multimem.store`` writes a local slice through the
-    multicast address (the switch delivers it to every rank)."""
+    """In-switch reduction.
+
+    All-reduce is one pass per rank over its 1/N slice: ``multimem.allreduce`` fetches each vector
+    with ``multimem.ld_reduce`` (the switch returns the sum over all ranks' copies) and writes it
+    straight back with ``multimem.st`` (the switch delivers it to every rank).  Per GPU and
+    direction (1 + 1/N) of the message crosses NVLink, and the outbound reduce traffic overlaps
+    the inbound broadcast traffic.  ``one_pass=False`` keeps the two halves apart
+    (``multimem.reduce`` into local memory, barrier, ``multimem.store``), which serialises an
+    outbound-bound phase and an inbound-bound phase and measured about twice as slow; it remains
+    as ``nvls_twopass`` for comparison.  Reduce-scatter and all-gather are those halves on their own.
+    """
 
     name: str = "nvls"
+    one_pass: bool = True
 
     @property
     def step_count(self) -> str:
@@ -172,14 +180,19 @@ class NvlsAllreduce(CollectiveAlgorithm):
 
     def build_allreduce(self, rank, world_size, tensor_size, dtype="bfloat16",
                         executor="multimem", num_channels=1) -> PrimitiveIRGraph:
+        one_pass = self.one_pass
+
         def body(op, base, span, sig, c=0, nc=1):
             piece = span // world_size
             mine = base + rank * piece
             all_pairs_barrier(op, rank, world_size, sig + _BARRIER_A)
-            op.multimem_reduce(source_rank=rank, src_offset=mine, dst_offset=mine,
-                               remote_offset=mine, count=piece)
-            all_pairs_barrier(op, rank, world_size, sig + _BARRIER_B)
-            op.multimem_store(source_rank=rank, src_offset=mine, dst_offset=mine, size=piece)
+            if one_pass:
+                op.multimem_allreduce(offset=mine, count=piece)
+            else:
+                op.multimem_reduce(source_rank=rank, src_offset=mine, dst_offset=mine,
+                                   remote_offset=mine, count=piece)
+                all_pairs_barrier(op, rank, world_size, sig + _BARRIER_B)
+                op.multimem_store(source_rank=rank, src_offset=mine, dst_offset=mine, size=piece)
             all_pairs_barrier(op, rank, world_size, sig + _BARRIER_C)
         return _per_channel("nvls_ar", "allreduce", "nvls", rank, world_size, tensor_size,
                             dtype, num_channels, body)
@@ -206,6 +219,110 @@ class NvlsAllreduce(CollectiveAlgorithm):
             all_pairs_barrier(op, rank, world_size, sig + _BARRIER_B)
         return _per_channel("nvls_ag", "allgather", "nvls", rank, world_size, tensor_size,
                             dtype, num_channels, body)
+
+
+class NvlsTwoPassAllreduce(NvlsAllreduce):
+    """The in-switch all-reduce as two separate passes (reduce, barrier, broadcast)."""
+
+    name: str = "nvls_twopass"
+    one_pass: bool = False
+
+
+def hybrid_split(tensor_size: int, world_size: int, fraction: float, nvls_channels: int,
+                 peer_channels: int, align: int = 16):
+    """Element ranges of the hybrid all-reduce: ``[(channel, base, span, kind), ...]``.
+
+    The first ``fraction`` of the tensor (rounded so that every channel's span splits into
+    ``world_size`` pieces of a multiple of ``align`` elements) goes to the in-switch channels,
+    the rest to the peer (two-shot) channels; what rounding leaves over joins the last peer
+    channel's range as a tail that is reduced by the two-shot steps of that channel."""
+    unit = world_size * align
+    out = []
+    nvls_elems = int(tensor_size * max(0.0, min(1.0, fraction)))
+    per_nvls = (nvls_elems // max(1, nvls_channels)) // unit * unit if nvls_channels else 0
+    base = 0
+    for c in range(nvls_channels):
+        if per_nvls:
+            out.append((len(out), base, per_nvls, "nvls"))
+            base += per_nvls
+    rest = tensor_size - base
+    per_peer = (rest // max(1, peer_channels)) // unit * unit if peer_channels else 0
+    for c in range(peer_channels):
+        if per_peer:
+            out.append((len(out), base, per_peer, "peer"))
+            base += per_peer
+    return out, base
+
+
+class HybridAllreduce(CollectiveAlgorithm):
+    """In-switch and peer-memory all-reduce side by side in one launch.
+
+    Channels ``[0, k)`` run the one-pass ``multimem.allreduce`` on the first ``nvls_fraction`` of
+    the message; channels ``[k, C)`` run the two-shot schedule (``sm.reduce_multi`` of this rank's
+    piece from every peer, then pulls of the finished pieces) on the rest.  The two paths load
+    different parts of the fabric (the switch's reduction engines and multicast replication
+    against plain unicast reads), so where the in-switch path alone does not fill the links the
+    peer path uses what is left.  ``nvls_fraction`` (``PCCL_NVLS_FRACTION``) is the *byte* split;
+    the CTA split follows it because the engine hands CTAs to chains in proportion to their bytes.
+    Elements that the rounding of the split leaves over (fewer than ``C * world * 16``) are
+    reduced by a small two-shot tail on the last channel.
+    """
+
+    name: str = "hybrid"
+
+    def __init__(self, nvls_fraction: float = None):
+        import os
+        if nvls_fraction is None:
+            nvls_fraction = float(os.environ.get("PCCL_NVLS_FRACTION", "0.7"))
+        self.nvls_fraction = nvls_fraction
+
+    @property
+    def step_count(self) -> str:
+        return "O(1)"
+
+    @property
+    def bandwidth_optimal(self) -> bool:
+        return True
+
+    def build_allreduce(self, rank, world_size, tensor_size, dtype="bfloat16", executor="multimem",
+                        num_channels=2) -> PrimitiveIRGraph:
+        num_channels = max(2, num_channels)
+        k = min(num_channels - 1, max(1, round(num_channels * self.nvls_fraction)))
+        ranges, covered = hybrid_split(tensor_size, world_size, self.nvls_fraction, k, num_channels - k)
+        with CommunicationOp(name=f"hybrid_ar_c{num_channels}_rank{rank}", device=DeviceType.CUDA) as op:
+            op.tensor(dtype=dtype, shape=(tensor_size,))
+
+            def two_shot(base, span, sig):
+                piece = span // world_size
+                mine = base + rank * piece
+                op.sm_reduce_multi(source_ranks=_rotated(rank, world_size, True),
+                                   remote_offset=mine, dst_offset=mine, count=piece)
+                all_pairs_barrier(op, rank, world_size, sig + _BARRIER_B)
+                for peer in _rotated(rank, world_size, False):
+                    off = base + peer * piece
+                    op.sm_copy(source_rank=peer, src_offset=off, dst_offset=off, size=piece)
+
+            for c, base, span, kind in ranges:
+                sig = c * SIGNAL_STRIDE
+                with Stream(f"ch{c}"):
+                    op.set_channel(c)
+                    all_pairs_barrier(op, rank, world_size, sig + _BARRIER_A)
+                    if kind == "nvls":
+                        piece = span // world_size
+                        op.multimem_allreduce(offset=base + rank * piece, count=piece)
+                    else:
+                        two_shot(base, span, sig)
+                    if c == len(ranges) - 1 and covered < tensor_size:
+                        # Tail left by rounding: rank 0 reduces it, everyone pulls it.
+                        tail = tensor_size - covered
+                        if rank == 0:
+                            op.sm_reduce_multi(source_ranks=list(range(world_size)), remote_offset=covered,
+                                               dst_offset=covered, count=tail)
+                        all_pairs_barrier(op, rank, world_size, sig + 500)
+                        if rank != 0:
+                            op.sm_copy(source_rank=0, src_offset=covered, dst_offset=covered, size=tail)
+                    all_pairs_barrier(op, rank, world_size, sig + _BARRIER_C)
+            return finish(op, "allreduce", "hybrid")
 
 
 #: direct RS / AG / A2A live on the two-shot class; this alias names them for what they are

@@ -223,6 +223,9 @@ class CommunicationOp:
         return self._emit(N.MultimemStoreNode, source_rank=source_rank, src_offset=src_offset,
                           dst_offset=dst_offset, size=size)
 
+    def multimem_allreduce(self, offset: int, count: int, reduce_op: str = "sum"):
+        return self._emit(N.MultimemAllreduceNode, reduce_op=reduce_op, offset=offset, count=count)
+
     def sm_put(self, target_rank: int, src_offset: int, dst_offset: int, size: int):
         return self._emit(N.SmPutNode, target_rank=target_rank, src_offset=src_offset,
                           dst_offset=dst_offset, size=size)

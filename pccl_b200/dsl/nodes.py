@@ -58,6 +58,7 @@ class PrimitiveOpType(Enum):
     # Additions of this library (additive to the plan format).
     SM_PUT = "sm.put"
     SM_REDUCE_MULTI = "sm.reduce_multi"
+    MULTIMEM_ALLREDUCE = "multimem.allreduce"
 
 
 class ReduceOp(Enum):
@@ -77,6 +78,7 @@ _EXECUTOR_OF: Dict[PrimitiveOpType, ExecutorType] = {
     PrimitiveOpType.CE_COPY: ExecutorType.CE,
     PrimitiveOpType.MULTIMEM_REDUCE: ExecutorType.MULTIMEM,
     PrimitiveOpType.MULTIMEM_STORE: ExecutorType.MULTIMEM,
+    PrimitiveOpType.MULTIMEM_ALLREDUCE: ExecutorType.MULTIMEM,
     PrimitiveOpType.RDMA_WRITE: ExecutorType.RDMA,
     PrimitiveOpType.RDMA_READ: ExecutorType.RDMA,
     PrimitiveOpType.OCS_BARRIER: ExecutorType.HOST,
@@ -307,6 +309,37 @@ class SmReduceMultiNode(IRNode):
 
 
 @dataclass
+class MultimemAllreduceNode(IRNode):
+    """buffer_r[offset:offset+count] = (op) over all ranks s of buffer_s[offset:offset+count], for every r.
+
+    One pass through the switch: each 16-byte vector is fetched with ``multimem.ld_reduce``
+    (the switch folds every rank's copy) and written straight back with ``multimem.st`` (the
+    switch delivers it to every rank), so the reduce traffic (outbound) and the broadcast
+    traffic (inbound) share the link at the same time instead of one after the other.  Ranks
+    must run it on disjoint ranges between two barriers.
+    """
+
+    reduce_op: str = "sum"
+    offset: int = 0
+    count: int = 0
+
+    def __post_init__(self):
+        if self.op_type is None:
+            self.op_type = PrimitiveOpType.MULTIMEM_ALLREDUCE
+        self._finish_identity()
+
+    def validate(self) -> bool:
+        if self.reduce_op not in _REDUCE_NAMES:
+            raise ValueError(f"MultimemAllreduceNode: invalid reduce_op '{self.reduce_op}'")
+        if self.offset < 0 or self.count < 0:
+            raise ValueError("MultimemAllreduceNode: offset and count must be non-negative")
+        return True
+
+    def to_params(self) -> Dict[str, Any]:
+        return {"reduce_op": self.reduce_op, "offset": self.offset, "count": self.count}
+
+
+@dataclass
 class OcsBarrierNode(IRNode):
     """Host-side control point at which the optical-circuit-switch topology may change.
 
@@ -409,7 +442,7 @@ IRNodeVariant = Union[
     MultimemReduceNode, MultimemStoreNode,
     CeCopyNode, RdmaWriteNode, RdmaReadNode,
     NotifyNode, WaitNotifyNode, OcsBarrierNode,
-    SmPutNode, SmReduceMultiNode,
+    SmPutNode, SmReduceMultiNode, MultimemAllreduceNode,
 ]
 
 #: primitive name -> node class, for code that rebuilds nodes from plan JSON.
@@ -427,6 +460,7 @@ NODE_CLASS_BY_OP: Dict[PrimitiveOpType, type] = {
     PrimitiveOpType.WAIT_NOTIFY: WaitNotifyNode,
     PrimitiveOpType.SM_PUT: SmPutNode,
     PrimitiveOpType.SM_REDUCE_MULTI: SmReduceMultiNode,
+    PrimitiveOpType.MULTIMEM_ALLREDUCE: MultimemAllreduceNode,
     PrimitiveOpType.OCS_BARRIER: OcsBarrierNode,
 }
 

@@ -150,7 +150,7 @@ _COPY_OPS = frozenset({
 })
 _REDUCE_OPS = frozenset({
     PrimitiveOpType.SM_REDUCE, PrimitiveOpType.TMA_REDUCE, PrimitiveOpType.MULTIMEM_REDUCE,
-    PrimitiveOpType.SM_REDUCE_MULTI,
+    PrimitiveOpType.SM_REDUCE_MULTI, PrimitiveOpType.MULTIMEM_ALLREDUCE,
 })
 _SYNC_OPS = frozenset({PrimitiveOpType.NOTIFY, PrimitiveOpType.WAIT_NOTIFY, PrimitiveOpType.NOOP})
 _DEFAULT_BW = 10.0
@@ -297,10 +297,14 @@ def plan_cost(graph, profile: GpuProfile, topology: TopologyProfile, elem_bytes:
             if op == PrimitiveOpType.SM_REDUCE_MULTI:
                 amount *= max(1, len(params.get("source_ranks", ())) - 1)
             rate = profile.bandwidth_gb_s.get(key, _DEFAULT_BW)
+            extra = 0.0
             if key == "multimem":
                 amount *= max(1, world_size)
+                # A multimem access is answered by the switch after it has gathered (or delivered)
+                # every rank's copy: two more fabric hops than a peer load before the first byte.
+                extra = 2.0 * topology.latency_us if topology is not None else 0.0
             else:
                 rate = min(rate, link)
-            own = profile.launch_overhead_us + _us(amount, rate)
+            own = profile.launch_overhead_us + extra + _us(amount, rate)
         finish[node.op_id] = start + own
     return max(finish.values(), default=0.0)

@@ -131,6 +131,18 @@ class Engine:
     def set_timeout_ms(self, ms: int) -> None:
         self._engine.setTimeoutMs(int(ms))
 
+    def set_trace(self, on: bool = True) -> None:
+        """Device timeline on / off (also ``PCCL_TRACE=1``): while on, every step of a plan stamps
+        ``%globaltimer`` when it is reached, when its data movement starts and ends and when its
+        signals are posted.  The next launch after a change rebuilds the operation's tables."""
+        self._engine.setTrace(bool(on))
+
+    def trace(self, name: str) -> List[Dict[str, Any]]:
+        """Steps of the most recent launch of ``name`` (after a synchronize): chain, step, kind,
+        CTAs, bytes and the four stamps in nanoseconds since the launch's first stamp.
+        ``pccl_b200.utils.trace.summarize`` turns it into a per-phase table."""
+        return list(self._engine.trace(name))
+
     @property
     def rank(self) -> int:
         return self._engine.rank()

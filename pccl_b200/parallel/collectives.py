@@ -199,10 +199,15 @@ def ensure_plan(kind: str, numel: int, dtype: torch.dtype, algorithm: Optional[s
         # does not match the contiguous shard the engine reads / writes for these collectives.
         channels = 1
     # Every channel's slice must split evenly over the ranks, in 16-byte units where possible.
-    while channels > 1 and numel % (channels * world):
-        channels //= 2
+    if algorithm == "hybrid":
+        channels = max(2, channels)              # at least one in-switch and one peer channel; it rounds by itself
+    else:
+        while channels > 1 and numel % (channels * world):
+            channels //= 2
     name = _plan_name(kind, algorithm, dtype_name, numel, channels) + ("" if reduce_op == "sum" else "_" + reduce_op) \
         + ("" if executor in (None, "sm") else "_" + executor)
+    if algorithm == "hybrid":
+        name += "_f" + os.environ.get("PCCL_NVLS_FRACTION", "0.7")
     if name in _state["registered"]:
         return name
     template = ALGORITHMS[algorithm]()

@@ -25,6 +25,7 @@ for the parameter mapping and csrc/engine_c.cc:468-548 for the I/O placement):
     reduce_multi self[dst:+count]    = (op) over r in source_ranks of buf[r][remote:+count]
     multimem.reduce self[dst:+count] = (op) over all ranks r of buf[r][remote:+count]
     multimem.store  buf[r][dst:+size] = self[src:+size] for every rank r
+    multimem.allreduce buf[r][off:+count] = (op) over all ranks s of buf[s][off:+count], for every r
     notify      signals[target_rank][signal_id] += 1
     wait_notify block until signals[self][signal_id] > 0, then -= 1
 
@@ -211,6 +212,13 @@ class _World:
             for dst in range(self.world):
                 self._check(dst, p["dst_offset"], p["size"], tag)
                 self.buffers[dst][p["dst_offset"]:p["dst_offset"] + p["size"]] = value
+        elif name == "multimem.allreduce":
+            n, off = p["count"], p["offset"]
+            for s in range(self.world):
+                self._check(s, off, n, tag)
+            value = self._fold(p.get("reduce_op", "sum"), [self._read(s, off, n) for s in range(self.world)], me)
+            for dst in range(self.world):
+                self.buffers[dst][off:off + n] = value
         elif name == "notify":
             target = self.ranks[self._peer(p["target_rank"], tag)]
             target.signals[p["signal_id"]] = target.signals.get(p["signal_id"], 0) + 1
@@ -396,6 +404,21 @@ class GlooPlanExecutor:
                     got = self._fetch(r, p["src_offset"], p["size"], dst, per, bufs)
                     if dst in bufs:
                         put(dst, p["dst_offset"], got)
+            elif name == "multimem.allreduce":
+                total = None
+                for s in range(world):
+                    got = self._fetch(s, p["offset"], p["count"], r, per, bufs)
+                    if here:
+                        total = got.to(acc) if total is None else _combine(
+                            p.get("reduce_op", "sum"), total, got.to(acc))
+                if here:
+                    put(r, p["offset"], total)
+                for dst in range(world):
+                    if dst == r:
+                        continue
+                    got = self._fetch(r, p["offset"], p["count"], dst, per, bufs)
+                    if dst in bufs:
+                        put(dst, p["offset"], got)
             # notify / wait_notify / noop: ordering is already in the schedule
 
         outputs = {}

@@ -30,7 +30,8 @@ def main():
     def tol(dtype):
         return dict(atol=1e-4, rtol=1e-5) if dtype == torch.float32 else dict(atol=0.1, rtol=2 ** -6)
 
-    algos = ["ring", "twoshot", "oneshot", "nvls"] + (["rhd", "tree"] if world & (world - 1) == 0 else [])
+    algos = ["ring", "twoshot", "oneshot", "nvls", "nvls_twopass", "hybrid"] + \
+        (["rhd", "tree"] if world & (world - 1) == 0 else [])
     for dtype in (torch.float32, torch.bfloat16):
         for numel in (world * 1024, world * 100003, 4 << 20):
             gen = torch.Generator(device="cuda").manual_seed(1000 + rank)
@@ -41,7 +42,7 @@ def main():
                 if algo == "oneshot" and numel > (1 << 20):
                     continue
                 for channels in (1, 4):
-                    if numel % (channels * world):
+                    if numel % (channels * world) and algo != "hybrid":   # hybrid reduces the ragged tail itself
                         continue
                     y = x.clone()
                     pp.all_reduce(y, algorithm=algo, channels=channels)

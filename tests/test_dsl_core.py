@@ -166,3 +166,24 @@ def test_barrier_must_cut_the_whole_graph():
     with pytest.raises(ValueError, match="must depend on every node"):
         g.validate()
     del stray
+
+
+def test_trace_summary_reports_phase_rates():
+    """The timeline reader: per-kind spans and per-direction link rates from raw stamps."""
+    from pccl_b200.utils.trace import phases, summarize, waits
+    mb = 1 << 20
+    trace = [
+        {"chain": 0, "step": 0, "kind": "noop", "ctas": 4, "bytes": 0,
+         "t_reached_ns": 0, "t_data_ns": 2000, "t_done_ns": 2000, "t_posted_ns": 2500},
+        {"chain": 0, "step": 1, "kind": "multimem.allreduce", "ctas": 4, "bytes": 8 * mb,
+         "t_reached_ns": 2500, "t_data_ns": 3000, "t_done_ns": 103000, "t_posted_ns": 103500},
+        {"chain": 1, "step": 0, "kind": "reduce_multi", "ctas": 4, "bytes": 4 * mb,
+         "t_reached_ns": 0, "t_data_ns": 3000, "t_done_ns": 53000, "t_posted_ns": 53200},
+    ]
+    rows = {r["kind"]: r for r in phases(trace, world=8)}
+    assert abs(rows["multimem.allreduce"]["span_us"] - 100.0) < 1e-6
+    assert abs(rows["multimem.allreduce"]["tx_gbs"] - 8 * mb * 9 / 100000) < 1e-6      # (W + 1) slices per direction
+    assert abs(rows["reduce_multi"]["rx_gbs"] - 4 * mb * 7 / 50000) < 1e-6
+    w = waits(trace)
+    assert w["chains"] == 2 and abs(w["total_us"] - 103.5) < 1e-6
+    assert "multimem.allreduce" in summarize(trace, 8)

@@ -39,6 +39,32 @@ def test_router_matches_torch(tokens, hidden, experts):
         assert torch.equal(s, torch.arange(s.numel(), device="cuda"))
 
 
+@pytest.mark.parametrize("experts", [2, 8])
+def test_router_with_non_finite_rows_stays_inside_its_outputs(experts):
+    """NaN / Inf activations give arbitrary but valid routing: two distinct experts in range per
+    token, counts that add up, and nothing written outside the output arrays."""
+    from pccl_b200.ops import moe
+    tokens, hidden = 300, 256
+    x = torch.randn(tokens, hidden, device="cuda").to(torch.bfloat16)
+    x[3] = float("nan")
+    x[17, 5] = float("inf")
+    x[40, :] = float("-inf")
+    x[41, 0], x[41, 1] = float("inf"), float("-inf")
+    wg = (torch.randn(experts, hidden, device="cuda") * 0.5).to(torch.bfloat16)
+    idx, gate, slot, counts = moe.route(x, wg)
+    torch.cuda.synchronize()
+    assert int(idx.min()) >= 0 and int(idx.max()) < experts
+    assert bool((idx[:, 0] != idx[:, 1]).all())
+    assert int(counts.sum()) == 2 * tokens
+    assert torch.equal(counts.long(), torch.bincount(idx.long().flatten(), minlength=experts))
+    finite = torch.isfinite(x.float()).all(dim=-1)
+    assert torch.isfinite(gate[finite]).all()
+    logits = x[finite].float() @ wg.float().t()
+    top, ref_idx = logits.topk(2, dim=-1)
+    clear = (top[:, 0] - top[:, 1]) > 1e-3
+    assert torch.equal(idx[finite][clear][:, 0].long(), ref_idx[clear][:, 0])
+
+
 @pytest.mark.parametrize("tokens,hidden,ffn,experts", [(512, 512, 1024, 8), (200, 256, 400, 4), (1024, 1024, 2048, 8)])
 def test_fused_moe_single_gpu(tokens, hidden, ffn, experts):
     from pccl_b200.ops import moe

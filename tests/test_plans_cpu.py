@@ -168,3 +168,29 @@ def test_switched_fabric_selector_follows_measured_crossovers():
     assert pick(4, 512 << 20) == "TwoShotAllreduce"
     assert pick(8, 1 << 20) == "TwoShotAllreduce"
     assert pick(8, 512 << 20) == "NvlsAllreduce"
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("fraction", [0.0, 0.3, 0.7, 1.0])
+def test_hybrid_allreduce_covers_ragged_sizes(world, fraction):
+    """In-switch channels, two-shot channels and the rounding tail together reduce every element."""
+    from pccl_b200.dsl.algorithms import HybridAllreduce
+    n = 5 * world * 16 * 4 + 24          # not a multiple of channels * world * 16
+    plans = build_plans(HybridAllreduce(fraction), "allreduce", world, n, channels=4)
+    kinds = {op["primitive"] for op in plans[0]["operations"]}
+    if 0.0 < fraction < 1.0:
+        assert {"multimem.allreduce", "sm.reduce_multi", "sm.copy"} <= kinds
+    xs = make_inputs("allreduce", world, n)
+    outs, sim = simulate(plans, xs, return_world=True)
+    for out in outs:
+        torch.testing.assert_close(out.double(), sum(x.double() for x in xs), atol=1e-5, rtol=1e-5)
+    assert sim.leftover_signals() == {}
+
+
+def test_nvls_allreduce_is_one_pass_and_two_pass_variant_remains():
+    from pccl_b200.dsl.algorithms import NvlsTwoPassAllreduce
+    one = build_plans(NvlsAllreduce(), "allreduce", 4, 256)[0]
+    two = build_plans(NvlsTwoPassAllreduce(), "allreduce", 4, 256)[0]
+    assert [op["primitive"] for op in one["operations"] if "multimem" in op["primitive"]] == ["multimem.allreduce"]
+    assert [op["primitive"] for op in two["operations"] if "multimem" in op["primitive"]] == \
+        ["multimem.reduce", "multimem.store"]

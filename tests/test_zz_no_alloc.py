@@ -56,6 +56,33 @@ def test_static_router_matches_allocating_entry_point(tokens, hidden, experts):
         assert _slots_are_permutations(ref_idx, ref_slot, experts)
 
 
+def test_static_router_with_optional_outputs_left_out_and_non_finite_rows():
+    """Every output pointer is optional, and rows holding NaN / Inf must not push the counters
+    outside the module's scratch array: the words on either side of the counts stay untouched."""
+    lib, fn = _entry()
+    tokens, hidden, experts = 333, 256, 8
+    x = torch.randn(tokens, hidden, device="cuda").to(torch.bfloat16)
+    x[7] = float("nan")
+    x[8, 3] = float("-inf")
+    wg = (torch.randn(experts, hidden, device="cuda") * 0.5).to(torch.bfloat16)
+    stream = torch.cuda.current_stream().cuda_stream
+    assert fn(x.data_ptr(), wg.data_ptr(), tokens, hidden, experts, None, None, None, None, stream) == 0
+    guarded = torch.full((experts + 8,), -7, dtype=torch.int32, device="cuda")
+    counts = guarded[4:4 + experts]
+    idx = torch.empty(tokens, 2, dtype=torch.int32, device="cuda")
+    assert fn(x.data_ptr(), wg.data_ptr(), tokens, hidden, experts, idx.data_ptr(), None, None,
+              counts.data_ptr(), stream) == 0
+    torch.cuda.synchronize()
+    assert int(counts.sum()) == 2 * tokens
+    assert bool((guarded[:4] == -7).all()) and bool((guarded[4 + experts:] == -7).all())
+    assert int(idx.min()) >= 0 and int(idx.max()) < experts and bool((idx[:, 0] != idx[:, 1]).all())
+    logits = x.float() @ wg.float().t()
+    finite = torch.isfinite(logits).all(dim=-1)
+    top, ref_idx = logits[finite].topk(2, dim=-1)
+    clear = (top[:, 0] - top[:, 1]) > 1e-3
+    assert torch.equal(idx[finite][clear][:, 0].long(), ref_idx[clear][:, 0])
+
+
 def test_static_router_rejects_oversize_shapes():
     lib, fn = _entry()
     x = torch.zeros(8, 256, dtype=torch.bfloat16, device="cuda")
