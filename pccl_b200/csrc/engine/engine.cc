@@ -571,6 +571,16 @@ LocalCluster::~LocalCluster() {
 
 void LocalCluster::regOp(const std::string& name, const std::vector<std::string>& json_per_rank) {
   PCCL_CHECK(static_cast<int>(json_per_rank.size()) == world_, "need one plan per rank");
+  if (protocol_check_) {
+    // All ranks' plans are at hand: run their signal protocol abstractly before anything launches.
+    std::vector<Plan> all;
+    for (const std::string& text : json_per_rank) all.push_back(load_plan(text));
+    const WorldReport rep = check_world(all);
+    PCCL_CHECK(!rep.deadlock, "operation '" << name << "' would deadlock: " << rep.detail);
+    if (rep.leftover_signals)
+      PCCL_LOG_WARN("operation '" << name << "' leaves " << rep.leftover_signals
+                                  << " signals non-zero (reset_signals needed between runs): " << rep.detail);
+  }
   // All virtual ranks must be co-resident in one cooperative launch.
   const int resident = plan_interp_max_ctas(kInterpThreads);
   PCCL_CHECK(resident > 0, "no CUDA device");

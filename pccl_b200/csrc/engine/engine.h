@@ -182,6 +182,9 @@ class LocalCluster {
   void reset();
   void set_timeout_ms(uint64_t ms);
   void set_ctas(uint32_t ctas) { ctas_override_ = ctas; }
+  // regOp runs all ranks' signal protocol abstractly and refuses a plan set that would deadlock;
+  // off only for tests of the device-side wait limit, which need such a plan to reach the GPU.
+  void set_protocol_check(bool on) { protocol_check_ = on; }
   RankContext& context(int r) { return *ranks_[r]; }
   // Status of the last launch per rank: code 0 = ok.
   std::vector<DeviceStatus> last_status() const { return last_status_; }
@@ -192,6 +195,7 @@ class LocalCluster {
   std::map<std::string, RankProgram*> d_programs_;     // [world] arrays
   std::vector<DeviceStatus> last_status_;
   uint32_t ctas_override_ = 0;
+  bool protocol_check_ = true;
 };
 
 }  // namespace pccl

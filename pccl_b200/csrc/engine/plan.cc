@@ -3,6 +3,7 @@
 #include <algorithm>
 #include <map>
 #include <set>
+#include <sstream>
 
 #include "../common/util.h"
 
@@ -219,6 +220,92 @@ void validate_plan(const Plan& plan, const PlanLimits& lim) {
         break;
     }
   }
+}
+
+WorldReport check_world(const std::vector<Plan>& plans) {
+  WorldReport rep;
+  const int world = static_cast<int>(plans.size());
+  struct RankState {
+    std::vector<int> missing;       // unmet dependencies per operation
+    std::vector<char> done;
+    std::vector<int> ready;
+    std::map<uint32_t, int64_t> signals;
+    size_t finished = 0;
+  };
+  std::vector<RankState> st(world);
+  for (int r = 0; r < world; ++r) {
+    const Plan& plan = plans[r];
+    st[r].missing.resize(plan.ops.size());
+    st[r].done.assign(plan.ops.size(), 0);
+    const int esize = dtype_bytes(plan.dtype);
+    for (size_t i = 0; i < plan.ops.size(); ++i) {
+      const PlanOp& op = plan.ops[i];
+      st[r].missing[i] = static_cast<int>(op.deps.size());
+      if (op.deps.empty()) st[r].ready.push_back(static_cast<int>(i));
+      if (op.primitive == Primitive::kNotify) ++rep.notifies;
+      if (op.primitive == Primitive::kWait) ++rep.waits;
+      if (is_data(op.primitive)) {
+        const int64_t fields[4] = {op.off_src, op.off_dst, op.off_remote, op.count};
+        for (int64_t f : fields)
+          if ((f * esize) % 16 != 0) { ++rep.misaligned_ops; break; }
+      }
+    }
+  }
+  // Successor lists from the dependency lists (next_ops in the file may be truncated or absent).
+  std::vector<std::vector<std::vector<int>>> succ(world);
+  for (int r = 0; r < world; ++r) {
+    succ[r].resize(plans[r].ops.size());
+    for (const PlanOp& op : plans[r].ops)
+      for (int d : op.deps) succ[r][d].push_back(op.index);
+  }
+  bool progressed = true;
+  while (progressed) {
+    progressed = false;
+    for (int r = 0; r < world; ++r) {
+      RankState& s = st[r];
+      for (size_t k = 0; k < s.ready.size();) {
+        const int i = s.ready[k];
+        const PlanOp& op = plans[r].ops[i];
+        if (op.primitive == Primitive::kWait) {
+          auto it = s.signals.find(op.signal_id);
+          if (it == s.signals.end() || it->second <= 0) { ++k; continue; }
+          --it->second;
+        } else if (op.primitive == Primitive::kNotify) {
+          if (op.peer >= 0 && op.peer < world) ++st[op.peer].signals[op.signal_id];
+        }
+        s.done[i] = 1;
+        ++s.finished;
+        s.ready.erase(s.ready.begin() + static_cast<long>(k));
+        for (int n : succ[r][i])
+          if (--s.missing[n] == 0) s.ready.push_back(n);
+        progressed = true;
+      }
+    }
+  }
+  std::ostringstream detail;
+  for (int r = 0; r < world; ++r) {
+    if (st[r].finished == plans[r].ops.size()) continue;
+    rep.deadlock = true;
+    detail << "rank " << r << " blocked at";
+    int shown = 0;
+    for (int i : st[r].ready) {
+      const PlanOp& op = plans[r].ops[i];
+      detail << " op " << i << " (" << op.primitive_name;
+      if (op.primitive == Primitive::kWait) detail << " signal " << op.signal_id << " from rank " << op.peer;
+      detail << ")";
+      if (++shown == 4) break;
+    }
+    detail << "; ";
+  }
+  for (int r = 0; r < world; ++r)
+    for (const auto& kv : st[r].signals)
+      if (kv.second != 0) {
+        if (rep.leftover_signals < 4 && !rep.deadlock)
+          detail << "rank " << r << " signal " << kv.first << " left at " << kv.second << "; ";
+        ++rep.leftover_signals;
+      }
+  rep.detail = detail.str();
+  return rep;
 }
 
 // ---- lowering ---------------------------------------------------------------------------------

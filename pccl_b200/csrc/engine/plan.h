@@ -5,7 +5,9 @@
 //                emits, including bare "notify" / "wait_notify" / "noop"
 //                (reference: csrc/engine/graph_builder.cc:12-107 and the channel
 //                parsers csrc/plugins/cuda/channels/*.h for the field mapping).
-// validate_plan  bounds of every range, peer and signal id; notify/wait balance.
+// validate_plan  one rank's plan on its own: bounds of every range, peer and signal id.
+// check_world    all ranks' plans together: abstract execution of the signal protocol (deadlock,
+//                signals left over, posts nobody consumes) and a 16-byte alignment report.
 // lower_plan     Plan -> LoweredProgram: chains of steps in plan order (program.h).
 #pragma once
 #include <cstdint>
@@ -56,6 +58,19 @@ struct PlanLimits {
 };
 // Throws pccl::Error describing the first violation.
 void validate_plan(const Plan& plan, const PlanLimits& limits);
+
+// Result of executing the signal protocol of all ranks' plans together, data left out: an operation
+// runs when its dependencies ran, a wait_notify when its semaphore is positive.
+struct WorldReport {
+  bool deadlock = false;          // some rank could not finish
+  std::string detail;             // who is blocked on what (deadlock), or which signals are left over
+  int leftover_signals = 0;       // semaphores non-zero at the end: the plan cannot be re-run without a reset
+  int misaligned_ops = 0;         // data operations whose offsets or size are not multiples of 16 bytes
+                                  // (they run on the element-wise path, and never on multimem)
+  int64_t notifies = 0, waits = 0;
+};
+// `plans[r]` is rank r's plan.  Never throws for protocol errors: the caller decides.
+WorldReport check_world(const std::vector<Plan>& plans);
 
 struct LowerOptions {
   int rank = 0, world = 1;

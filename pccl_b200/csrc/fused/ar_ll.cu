@@ -134,7 +134,8 @@ __global__ void __launch_bounds__(kLLThreads) allreduce_ll_kernel(const LLParams
 }  // namespace
 
 void allreduce_ll(const PeerBases& peers, uint64_t buf_off, uint64_t capacity_bytes, const void* in, void* out,
-                  uint64_t bytes, int dtype, uint32_t epoch, cudaStream_t stream, uint64_t timeout_ms) {
+                  uint64_t bytes, int dtype, uint32_t epoch, cudaStream_t stream, uint64_t timeout_ms,
+                  uint32_t* error) {
   PCCL_CHECK(bytes % 8 == 0 && bytes > 0, "LL all-reduce: size must be a positive multiple of 8 bytes");
   PCCL_CHECK(bytes <= capacity_bytes, "LL all-reduce: " << bytes << " bytes exceed the buffer's " << capacity_bytes);
   PCCL_CHECK(reinterpret_cast<uintptr_t>(in) % 8 == 0 && reinterpret_cast<uintptr_t>(out) % 8 == 0,
@@ -150,7 +151,7 @@ void allreduce_ll(const PeerBases& peers, uint64_t buf_off, uint64_t capacity_by
   p.units = bytes / 8;
   p.dtype = dtype;
   p.flag = epoch;
-  p.error = error_word();
+  p.error = error ? error : error_word();
   p.timeout_ns = timeout_ms * 1000000ull;
   // One unit per thread up to 128 CTAs, then a grid-stride loop.
   uint64_t grid = (p.units + kLLThreads - 1) / kLLThreads;

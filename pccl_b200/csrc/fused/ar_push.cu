@@ -258,13 +258,23 @@ __global__ void __launch_bounds__(kPushThreads) allreduce_push_kernel(const Push
 
 void collective_push(PushMode mode, const PeerBases& peers, uint64_t area_off, uint64_t capacity_bytes,
                      uint64_t flags_off, uint32_t* counters, const void* in, void* out, uint64_t bytes, int dtype,
-                     uint32_t epoch, cudaStream_t stream, int ctas, uint64_t timeout_ms) {
+                     uint32_t epoch, cudaStream_t stream, int ctas, uint64_t timeout_ms, uint32_t* error) {
   // `bytes` is the size of the full message: the all-reduce tensor, the reduce-scatter input, the
   // all-gather output, either side of the all-to-all.
   PCCL_CHECK(bytes % 16 == 0 && bytes > 0, "push all-reduce: size must be a positive multiple of 16 bytes");
   PCCL_CHECK(mode == kPushAllReduce || bytes % (16ull * peers.world) == 0,
              "push collective: every rank's part must be a multiple of 16 bytes");
   PCCL_CHECK(mode != kPushAllToAll || in != out, "push all-to-all cannot run in place");
+  if (mode == kPushReduceScatter) {
+    // Step 2 writes the output while other CTAs of this rank may still push input slices to the
+    // peers in step 1; only this rank's own slice is never read by step 1.
+    const uintptr_t in_lo = reinterpret_cast<uintptr_t>(in), in_hi = in_lo + bytes;
+    const uintptr_t shard = bytes / peers.world;
+    const uintptr_t out_lo = reinterpret_cast<uintptr_t>(out), out_hi = out_lo + shard;
+    const bool overlaps = out_lo < in_hi && in_lo < out_hi;
+    PCCL_CHECK(!overlaps || out_lo == in_lo + static_cast<uintptr_t>(peers.rank) * shard,
+               "push reduce-scatter: the output may alias the input only at this rank's own slice");
+  }
   PCCL_CHECK(bytes <= capacity_bytes, "push all-reduce: " << bytes << " bytes exceed the areas' " << capacity_bytes);
   PCCL_CHECK(reinterpret_cast<uintptr_t>(in) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0,
              "push all-reduce: tensors must be 16-byte aligned");
@@ -285,7 +295,7 @@ void collective_push(PushMode mode, const PeerBases& peers, uint64_t area_off, u
   p.dtype = dtype;
   p.mode = mode;
   p.epoch = epoch;
-  p.error = error_word();
+  p.error = error ? error : error_word();
   p.timeout_ns = timeout_ms * 1000000ull;
   // The grid is part of the completion count: it is the same for every call of an instance.
   // Every CTA spins on flags that a peer posts when its last CTA arrives: the whole grid must be

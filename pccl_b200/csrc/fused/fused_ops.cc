@@ -100,7 +100,8 @@ void bind_fused_ops(py::module_& m) {
         py::arg("use_nvls") = true, py::arg("ctas") = 0);
   // Packet-protocol all-reduce (sum) for small messages; out may be the input tensor.
   f.def("allreduce_ll",
-        [](const torch::Tensor& in, torch::Tensor& out, int64_t buf_off, int64_t capacity_bytes, int64_t epoch) {
+        [](const torch::Tensor& in, torch::Tensor& out, int64_t buf_off, int64_t capacity_bytes, int64_t epoch,
+           c10::optional<torch::Tensor> error) {
           TORCH_CHECK(in.is_cuda() && out.is_cuda() && in.is_contiguous() && out.is_contiguous() &&
                           in.scalar_type() == out.scalar_type() && in.numel() == out.numel(),
                       "allreduce_ll: contiguous CUDA tensors of one dtype and size");
@@ -111,13 +112,15 @@ void bind_fused_ops(py::module_& m) {
           TORCH_CHECK(dtype >= 0, "allreduce_ll: float32, float16 or bfloat16");
           gemm::allreduce_ll(peer_bases(), static_cast<uint64_t>(buf_off), static_cast<uint64_t>(capacity_bytes),
                              in.data_ptr(), out.data_ptr(), static_cast<uint64_t>(in.nbytes()), dtype,
-                             static_cast<uint32_t>(epoch), c10::cuda::getCurrentCUDAStream().stream());
+                             static_cast<uint32_t>(epoch), c10::cuda::getCurrentCUDAStream().stream(), 2000,
+                             error.has_value() ? as_u32(*error, 1, "error") : nullptr);
         },
-        py::arg("input"), py::arg("output"), py::arg("buf_off"), py::arg("capacity_bytes"), py::arg("epoch"));
+        py::arg("input"), py::arg("output"), py::arg("buf_off"), py::arg("capacity_bytes"), py::arg("epoch"),
+        py::arg("error") = py::none());
   // Fused push collectives (mode: 0 all-reduce, 1 reduce-scatter, 2 all-gather, 3 all-to-all).
   f.def("collective_push",
         [](int mode, const torch::Tensor& in, torch::Tensor& out, int64_t area_off, int64_t capacity_bytes,
-           int64_t flags_off, torch::Tensor& counters, int64_t epoch, int ctas) {
+           int64_t flags_off, torch::Tensor& counters, int64_t epoch, int ctas, c10::optional<torch::Tensor> error) {
           TORCH_CHECK(in.is_cuda() && out.is_cuda() && in.is_contiguous() && out.is_contiguous() &&
                           in.scalar_type() == out.scalar_type(), "collective_push: contiguous CUDA tensors of one dtype");
           TORCH_CHECK(mode >= 0 && mode <= 3, "collective_push: mode 0..3");
@@ -136,10 +139,11 @@ void bind_fused_ops(py::module_& m) {
                                 static_cast<uint64_t>(capacity_bytes), static_cast<uint64_t>(flags_off),
                                 as_u32(counters, 2, "counters"), in.data_ptr(), out.data_ptr(),
                                 static_cast<uint64_t>(full), dtype, static_cast<uint32_t>(epoch),
-                                c10::cuda::getCurrentCUDAStream().stream(), ctas);
+                                c10::cuda::getCurrentCUDAStream().stream(), ctas, 2000,
+                                error.has_value() ? as_u32(*error, 1, "error") : nullptr);
         },
         py::arg("mode"), py::arg("input"), py::arg("output"), py::arg("area_off"), py::arg("capacity_bytes"),
-        py::arg("flags_off"), py::arg("counters"), py::arg("epoch"), py::arg("ctas"));
+        py::arg("flags_off"), py::arg("counters"), py::arg("epoch"), py::arg("ctas"), py::arg("error") = py::none());
   // MoE router on its own: top-2 expert indices, renormalised gates, the row each choice claims
   // in its expert's batch, and the per-expert token counts.  scratch: int32[experts + 1].
   f.def("moe_route",

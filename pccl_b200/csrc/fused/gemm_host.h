@@ -57,8 +57,10 @@ void ar_residual_rmsnorm(const PeerBases& peers, uint8_t* mc_base, uint64_t x_of
 // Small-message all-reduce (sum) with flag-carrying packets; in / out are ordinary device tensors
 // (out may alias in).  buf_off: symmetric uint4 [2][world][capacity_bytes / 8], zeroed once before
 // the first call on every rank.  dtype: 0 f32, 1 f16, 2 bf16.  epoch = 1, 2, 3, ... per call.
+// error: device word this call aborts on and reports to (null = the family's shared word).
 void allreduce_ll(const PeerBases& peers, uint64_t buf_off, uint64_t capacity_bytes, const void* in, void* out,
-                  uint64_t bytes, int dtype, uint32_t epoch, cudaStream_t stream, uint64_t timeout_ms = 2000);
+                  uint64_t bytes, int dtype, uint32_t epoch, cudaStream_t stream, uint64_t timeout_ms = 2000,
+                  uint32_t* error = nullptr);
 
 // Fused push collectives for small and medium messages; in / out are ordinary device tensors.
 //   kPushAllReduce      sum; push reduce-scatter, reduce, push all-gather; out may alias in
@@ -69,9 +71,13 @@ void allreduce_ll(const PeerBases& peers, uint64_t buf_off, uint64_t capacity_by
 // flags_off: symmetric u32[2 * world], zeroed once; counters: local zero-initialised u32[2].
 // `ctas` must be the same for every call that shares the counters.
 enum PushMode : int { kPushAllReduce = 0, kPushReduceScatter = 1, kPushAllGather = 2, kPushAllToAll = 3 };
+// A reduce-scatter may alias its output with slice `rank` of its input (the in-place convention) and
+// with nothing else of it: other ranks' slices are still being read while the output is written.
+// error: device word this call aborts on and reports to (null = the family's shared word).
 void collective_push(PushMode mode, const PeerBases& peers, uint64_t area_off, uint64_t capacity_bytes,
                      uint64_t flags_off, uint32_t* counters, const void* in, void* out, uint64_t bytes, int dtype,
-                     uint32_t epoch, cudaStream_t stream, int ctas, uint64_t timeout_ms = 2000);
+                     uint32_t epoch, cudaStream_t stream, int ctas, uint64_t timeout_ms = 2000,
+                     uint32_t* error = nullptr);
 
 // ---- expert-parallel MoE feed-forward (top-2 routing) ------------------------------------------------
 // Symmetric-heap offsets (identical on every rank) of the buffers the three kernels share.

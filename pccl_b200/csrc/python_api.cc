@@ -10,9 +10,11 @@
 #include <pybind11/stl.h>
 #include <torch/extension.h>
 
+#include "common/launch.h"
 #include "common/util.h"
 #include "engine/engine.h"
 #include "fused/fused_ops.h"
+#include "ocs/signal_board.h"
 namespace pccl { void bind_rdma(pybind11::module_& m); }
 
 namespace py = pybind11;
@@ -133,6 +135,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("regOp", &LocalCluster::regOp)
       .def("setTimeoutMs", &LocalCluster::set_timeout_ms)
       .def("setCtas", &LocalCluster::set_ctas)
+      .def("setProtocolCheck", &LocalCluster::set_protocol_check)
       .def("setTrace", [](LocalCluster& c, bool on) { for (int r = 0; r < c.world(); ++r) c.context(r).set_trace(on); })
       .def("trace", [](LocalCluster& c, const std::string& name, int rank) { return trace_list(c.context(rank), name); })
       .def("reset", &LocalCluster::reset)
@@ -165,6 +168,50 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         c.exeOp(name, ip, ib, op, ob, current_stream());
       });
 
+  // OCS control-plane exchange over NVLink (see ocs/signal_board.h).  Records are lists of at most
+  // 14 unsigned 32-bit words.  Each call returns (ok, missing_rank, host_us, records).
+  py::class_<SignalBoard>(m, "OcsSignalBoard")
+      .def(py::init([]() { return new SignalBoard(Engine::instance().context()); }))
+      .def("all_gather",
+           [](SignalBoard& b, const std::vector<uint32_t>& words, uint64_t timeout_us) {
+             std::array<uint32_t, kBoardWords> mine{};
+             TORCH_CHECK(words.size() <= kBoardWords, "a record holds at most ", kBoardWords, " words");
+             std::copy(words.begin(), words.end(), mine.begin());
+             std::vector<std::array<uint32_t, kBoardWords>> records;
+             BoardStatus st;
+             {
+               py::gil_scoped_release release;
+               st = b.all_gather(mine, &records, timeout_us);
+             }
+             py::list out;
+             for (const auto& r : records) out.append(std::vector<uint32_t>(r.begin(), r.end()));
+             return py::make_tuple(st.ok, st.missing_rank, st.host_us, out);
+           },
+           py::arg("words"), py::arg("timeout_us") = 1000000)
+      .def("broadcast",
+           [](SignalBoard& b, int root, const std::vector<uint32_t>& words, uint64_t timeout_us) {
+             std::array<uint32_t, kBoardWords> record{};
+             TORCH_CHECK(words.size() <= kBoardWords, "a record holds at most ", kBoardWords, " words");
+             std::copy(words.begin(), words.end(), record.begin());
+             BoardStatus st;
+             {
+               py::gil_scoped_release release;
+               st = b.broadcast(root, &record, timeout_us);
+             }
+             return py::make_tuple(st.ok, st.missing_rank, st.host_us, std::vector<uint32_t>(record.begin(), record.end()));
+           },
+           py::arg("root"), py::arg("words"), py::arg("timeout_us") = 1000000)
+      .def("barrier",
+           [](SignalBoard& b, uint64_t timeout_us) {
+             py::gil_scoped_release release;
+             const BoardStatus st = b.barrier(timeout_us);
+             return std::make_tuple(st.ok, st.missing_rank, st.host_us);
+           },
+           py::arg("timeout_us") = 1000000)
+      .def("reset", &SignalBoard::reset)
+      .def("rounds", &SignalBoard::rounds)
+      .def("world", &SignalBoard::world);
+
   // Host-only helpers usable without a GPU (plan loader / validator / lowering).
   m.def("lower_plan_summary", [](const std::string& json_text, int rank, int world, int64_t buffer_bytes,
                                  uint32_t ctas, bool multicast) {
@@ -194,6 +241,24 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     d["chain_list"] = chains;
     return d;
   });
+
+  // All ranks' plans together: abstract execution of the signal protocol (no GPU needed).
+  m.def("check_world", [](const std::vector<std::string>& plans_json) {
+    std::vector<Plan> plans;
+    for (const std::string& text : plans_json) plans.push_back(load_plan(text));
+    const WorldReport rep = check_world(plans);
+    py::dict d;
+    d["deadlock"] = rep.deadlock;
+    d["detail"] = rep.detail;
+    d["leftover_signals"] = rep.leftover_signals;
+    d["misaligned_ops"] = rep.misaligned_ops;
+    d["notifies"] = rep.notifies;
+    d["waits"] = rep.waits;
+    return d;
+  });
+  // Largest grid whose CTAs are all resident at once, and a request clamped to it.
+  m.def("coresident_limit", &coresident_limit);
+  m.def("clamp_coresident", &clamp_coresident);
 
   // Raises the engine's timeout error from host code (exercises the exception mapping without a GPU).
   m.def("_raise_timeout", [](const std::string& text) { throw TimeoutError(text); });

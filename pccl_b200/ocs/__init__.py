@@ -11,8 +11,8 @@ from .protocol import (OCS_CONTROL_MAGIC, OCS_CONTROL_MAX_PAYLOAD_BYTES, OCS_CON
                        OCSControlMessage, OCSControlMessageKey, OCSControlMessageType,
                        OCSControlStatus, ack_target, build_ack, build_ready, build_release,
                        plan_digest)
-from .runtime import (OCSBarrierState, OCSLinkState, OCSRuntime, OCSSwitchResult, SwitchConnector,
-                      TensorSwitchConnector, TorchDistributedSwitchConnector, ocs_all_reduce,
+from .runtime import (NvlinkSwitchConnector, OCSBarrierState, OCSLinkState, OCSRuntime, OCSSwitchResult,
+                      SwitchConnector, TensorSwitchConnector, TorchDistributedSwitchConnector, ocs_all_reduce,
                       ocs_barrier_switch)
 from .torch_plan import (OcsTorchPlanRunner, TorchCollectivePhase, TorchCollectivePlan,
                          build_torch_allreduce_alltoall_plan)
@@ -23,7 +23,7 @@ __all__ = [
     "OCSRuntime", "OCSBarrierState", "OCSLinkState", "OCSSwitchResult", "OcsPhaseRunner",
     "OcsCollectivePlanRunner", "PreparedOcsCollectivePlan", "PreparedOcsGraph",
     "StaticPlanController", "SwitchConnector", "TorchDistributedSwitchConnector",
-    "TensorSwitchConnector", "build_ring_allreduce_alltoall_plan", "OcsTorchPlanRunner",
+    "TensorSwitchConnector", "NvlinkSwitchConnector", "build_ring_allreduce_alltoall_plan", "OcsTorchPlanRunner",
     "TorchCollectivePhase", "TorchCollectivePlan", "build_torch_allreduce_alltoall_plan",
     "OCS_CONTROL_MAGIC", "OCS_CONTROL_MAX_PAYLOAD_BYTES", "OCS_CONTROL_VERSION",
     "OCSControlMessage", "OCSControlMessageKey", "OCSControlMessageType", "OCSControlStatus",

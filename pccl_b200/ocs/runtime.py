@@ -237,6 +237,92 @@ class TensorSwitchConnector(TorchDistributedSwitchConnector):
                                error_message="mock link did not reach alignment")
 
 
+class NvlinkSwitchConnector(TensorSwitchConnector):
+    """READY exchange and RELEASE delivery as signals between the GPUs, without a host collective.
+
+    Both rounds of a barrier run on the engine's *signal board* (native ``OcsSignalBoard``): one
+    single-CTA kernel per round stores this rank's words straight into every peer's symmetric
+    memory over NVLink, waits (bounded) for the peers' words, and hands all of them to the host
+    through mapped pinned memory, so the host neither launches a collective nor synchronises a
+    stream.  Each rank contributes its rank, arrival sequence number, arrival time and the
+    128-bit digest of its plan's consistency fields; the host compares the digests out of the
+    mapped memory and rebuilds the peers' records from the local plan, exactly like
+    ``TensorSwitchConnector`` (a mismatching digest poisons ``topology_id`` so that validation
+    raises ``OCSPlanMismatchError``).  A source whose words do not arrive within ``timeout``
+    simply stays absent from the returned records, which the runtime reports as
+    ``OCSBarrierTimeout`` naming the missing ranks.
+
+    The board spans the engine's whole world; barriers over other groups, and processes
+    without a connected native engine, use the tensor path of the parent class.  Construction
+    is collective (the board's slots come from the symmetric arena).  The reference's
+    connector is two pickled-object collectives (pccl/ocs/runtime.py:139-203).
+    """
+
+    def __init__(self, board: Any = None, default_timeout_s: float = 1.0, **mock_switch) -> None:
+        super().__init__(**mock_switch)
+        self.default_timeout_s = float(default_timeout_s)
+        self.host_us: List[float] = []           # per round, launch to completion on the host
+        if board is None:
+            from .. import engine as _engine
+            _engine.get_engine()                  # the native engine must be up (and connected) first
+            board = _engine.load_native().OcsSignalBoard()
+            if _dist_ready():
+                dist.barrier()                    # nobody signals a rank whose slots are not zeroed yet
+        self.board = board
+
+    def _usable(self, group) -> bool:
+        return self.board is not None and (not _dist_ready() or
+                                           dist.get_world_size(group) == self.board.world())
+
+    def _timeout_us(self, timeout: Optional[float]) -> int:
+        return max(1, int((self.default_timeout_s if timeout is None else timeout) * 1e6))
+
+    @staticmethod
+    def _split64(value: int) -> Tuple[int, int]:
+        return value & 0xffffffff, (value >> 32) & 0xffffffff
+
+    def exchange_ready(self, ready_record, group=None, timeout=None):
+        if not self._usable(group):
+            return super().exchange_ready(ready_record, group=group, timeout=timeout)
+        d0, d1 = self._digest_words(ready_record)
+        words = [int(ready_record["src_rank"]) & 0xffffffff, int(ready_record["arrive_seq"]) & 0xffffffff,
+                 *self._split64(int(ready_record["arrival_time_us"])), *self._split64(d0), *self._split64(d1)]
+        ok, missing, host_us, rows = self.board.all_gather(words, self._timeout_us(timeout))
+        self.host_us.append(host_us)
+        if not ok:
+            # Out of step with at least one peer: report the barrier as incomplete (the sender is
+            # the only record known to be good).  The board needs reset() before the next barrier.
+            return [ready_record]
+        records = []
+        for row in rows:
+            peer = dict(ready_record, src_rank=row[0], src_gpu_id=row[0], arrive_seq=row[1],
+                        arrival_time_us=row[2] | (row[3] << 32))
+            if (row[4] | (row[5] << 32), row[6] | (row[7] << 32)) != (d0, d1):
+                peer["topology_id"] = -1 - int(peer.get("topology_id", 0))
+            records.append(peer)
+        return records
+
+    def commit_switch(self, plan, ready_records, group=None, timeout=None):
+        if not self._usable(group):
+            return super().commit_switch(plan, ready_records, group=group, timeout=timeout)
+        rank, _ = _rank_world_size(group)
+        leader = min(plan.participant_ranks)
+        words = [0] * 7
+        if rank == leader:
+            r = self._simulate_commit()
+            words = [int(r.is_link_ready), *self._split64(r.switch_start_time_us),
+                     *self._split64(r.switch_done_time_us), *self._split64(r.link_ready_time_us or 0)]
+        ok, _, host_us, got = self.board.broadcast(leader, words, self._timeout_us(timeout))
+        self.host_us.append(host_us)
+        if not ok:
+            raise OCSBarrierTimeout(f"barrier {plan.barrier_id}: no RELEASE from leader rank {leader}")
+        start_us, done_us, ready_us = (got[1] | (got[2] << 32), got[3] | (got[4] << 32), got[5] | (got[6] << 32))
+        if got[0]:
+            return OCSSwitchResult(OCSLinkState.LINK_ALIGNED, start_us, done_us, ready_us)
+        return OCSSwitchResult(OCSLinkState.LINK_NOT_READY, start_us, done_us, None, error_code=1,
+                               error_message="mock link did not reach alignment")
+
+
 class OCSRuntime:
     """Runs the barrier state machine and keeps a history of its outcomes."""
 

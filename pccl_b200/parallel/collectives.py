@@ -50,6 +50,12 @@ def init(group: Optional[dist.ProcessGroup] = None):
         _engine.initialize_engine(group)
     else:
         _engine.get_engine()
+    # Error words of this layer's fused kernels: [0] packet all-reduce, [1] push collectives.  Each
+    # kernel family aborts on its own word only, so one timeout does not poison the others.
+    _state["errors"] = torch.zeros(4, dtype=torch.int32, device="cuda") if torch.cuda.is_available() \
+        and os.environ.get("PCCL_EXECUTOR") != "cpu" else None
+    _state["err_ll"] = _state["errors"][0:1] if _state["errors"] is not None else None
+    _state["err_push"] = _state["errors"][1:2] if _state["errors"] is not None else None
     _setup_ll(group)
     _setup_push(group)
     _state["connected"] = True
@@ -116,19 +122,36 @@ def _setup_push(group) -> None:
 
 
 def _push_eligible(tensor: torch.Tensor, op: str, algorithm: Optional[str]) -> bool:
+    """Sizes, dtype and arguments only: the same answer on every rank whatever view each rank passes.
+    A view that the kernel cannot take directly (not contiguous, not 16-byte aligned) is staged through
+    an aligned copy by ``_aligned``; it never changes which kernel runs."""
     push = _state.get("push")
     if push is None or op != "sum" or algorithm not in (None, "push"):
         return False
     nbytes = tensor.numel() * tensor.element_size()
-    return (tensor.is_cuda and tensor.is_contiguous() and nbytes % 16 == 0 and 0 < nbytes <= PUSH_MAX_BYTES
-            and tensor.data_ptr() % 16 == 0 and tensor.dtype in (torch.float32, torch.float16, torch.bfloat16))
+    return (tensor.is_cuda and nbytes % 16 == 0 and 0 < nbytes <= PUSH_MAX_BYTES
+            and tensor.dtype in (torch.float32, torch.float16, torch.bfloat16))
+
+
+def _aligned(tensor: torch.Tensor, align: int = 16) -> torch.Tensor:
+    """``tensor`` itself when a kernel can read it in place, else a contiguous, aligned copy of it
+    (fresh allocations are at least 256-byte aligned)."""
+    if tensor.is_contiguous() and tensor.data_ptr() % align == 0:
+        return tensor
+    return tensor.contiguous().clone() if tensor.is_contiguous() else tensor.contiguous()
 
 
 def _push(mode: int, input: torch.Tensor, output: torch.Tensor) -> None:
     push = _state["push"]
     push["epoch"] += 1
-    push["native"].collective_push(mode, input, output, push["areas"].heap_offset, PUSH_MAX_BYTES,
-                                   push["flags"].heap_offset, push["counters"], push["epoch"], _PUSH_CTAS)
+    src, dst = _aligned(input), _aligned(output)
+    if mode == 0 and input.data_ptr() == output.data_ptr() and src is not input:
+        dst = src                                  # in place on the staged copy
+    push["native"].collective_push(mode, src, dst, push["areas"].heap_offset, PUSH_MAX_BYTES,
+                                   push["flags"].heap_offset, push["counters"], push["epoch"], _PUSH_CTAS,
+                                   _state["err_push"])
+    if dst is not output:
+        output.copy_(dst)
 
 
 def _push_ok(full: torch.Tensor, part: torch.Tensor, algorithm: Optional[str], executor: Optional[str] = None,
@@ -141,10 +164,9 @@ def _push_ok(full: torch.Tensor, part: torch.Tensor, algorithm: Optional[str], e
         return False
     world = _state["world"]
     nbytes = full.numel() * full.element_size()
-    return (full.is_cuda and part.is_cuda and full.is_contiguous() and part.is_contiguous()
+    return (full.is_cuda and part.is_cuda
             and full.dtype == part.dtype and full.dtype in (torch.float32, torch.float16, torch.bfloat16)
-            and 0 < nbytes <= PUSH_MAX_BYTES and nbytes % (16 * world) == 0
-            and full.data_ptr() % 16 == 0 and part.data_ptr() % 16 == 0)
+            and 0 < nbytes <= PUSH_MAX_BYTES and nbytes % (16 * world) == 0)
 
 
 def _ll_eligible(tensor: torch.Tensor, op: str, algorithm: Optional[str]) -> bool:
@@ -152,8 +174,8 @@ def _ll_eligible(tensor: torch.Tensor, op: str, algorithm: Optional[str]) -> boo
     if ll is None or op != "sum" or algorithm not in (None, "ll"):
         return False
     nbytes = tensor.numel() * tensor.element_size()
-    return (tensor.is_cuda and tensor.is_contiguous() and nbytes % 8 == 0 and 0 < nbytes <= LL_MAX_BYTES
-            and tensor.data_ptr() % 8 == 0 and tensor.dtype in (torch.float32, torch.float16, torch.bfloat16))
+    return (tensor.is_cuda and nbytes % 8 == 0 and 0 < nbytes <= LL_MAX_BYTES
+            and tensor.dtype in (torch.float32, torch.float16, torch.bfloat16))
 
 
 def working_tensor(shape, dtype=torch.float32) -> torch.Tensor:
@@ -247,16 +269,19 @@ def all_reduce(tensor: torch.Tensor, op: str = "sum", algorithm: Optional[str] =
     if _ll_eligible(tensor, op, algorithm):
         ll = _state["ll"]
         ll["epoch"] += 1
-        ll["native"].allreduce_ll(tensor, tensor, ll["buf"].heap_offset, LL_MAX_BYTES, ll["epoch"])
+        work = _aligned(tensor, 8)
+        ll["native"].allreduce_ll(work, work, ll["buf"].heap_offset, LL_MAX_BYTES, ll["epoch"], _state["err_ll"])
+        if work is not tensor:
+            tensor.copy_(work)
         return tensor
     if _push_eligible(tensor, op, algorithm):
         _push(0, tensor, tensor)
         return tensor
     if algorithm == "push":
-        raise ValueError("the push all-reduce takes contiguous, 16-byte aligned f32/f16/bf16 sums of at most "
+        raise ValueError("the push all-reduce takes f32/f16/bf16 sums of a multiple of 16 and at most "
                          f"{PUSH_MAX_BYTES} bytes")
     if algorithm == "ll":
-        raise ValueError("the packet-protocol all-reduce takes contiguous f32/f16/bf16 sums of at most "
+        raise ValueError("the packet-protocol all-reduce takes f32/f16/bf16 sums of a multiple of 8 and at most "
                          f"{LL_MAX_BYTES} bytes")
     name = ensure_plan("allreduce", tensor.numel(), tensor.dtype, algorithm, channels, op)
     run = _engine.execute_operation_async if async_op else _engine.execute_operation
@@ -309,8 +334,57 @@ def all_to_all(output: torch.Tensor, input: torch.Tensor, algorithm: Optional[st
     return output
 
 
+_FUSED_CODES = {0x701: "packet all-reduce: a peer's packets did not arrive",
+                0x801: "push collective: a peer's first flag did not arrive",
+                0x802: "push collective: a peer's second flag did not arrive"}
+
+
+def check_errors() -> None:
+    """Raise ``PCCLTimeoutError`` if a fused collective of this layer gave up waiting since the last check.
+    Synchronises the current stream's device (it reads the kernels' error words)."""
+    errors = _state.get("errors")
+    if errors is None:
+        return
+    codes = errors.tolist()
+    if any(codes):
+        what = "; ".join(_FUSED_CODES.get(c, hex(c)) for c in codes if c)
+        raise _engine.PCCLTimeoutError(f"rank {_state['rank']}: {what}; call pccl_b200.parallel.reset() on every rank "
+                                       "before running collectives again")
+
+
 def synchronize(name: str = "") -> None:
+    """Wait for the current stream and surface device-side timeouts: of plans (the engine's status
+    block) and of the fused packet / push kernels (their error words)."""
     _engine.sync_operation(name)
+    check_errors()
+
+
+def reset() -> None:
+    """Bring every rank's collective state back to its initial value after an error (a timeout leaves
+    call counters, flags and receive buffers out of step between ranks).  Collective: every rank calls
+    it; it synchronises the device and the group."""
+    group = _state["group"]
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    if dist.is_initialized() and _state["world"] > 1:
+        dist.barrier(group=group)
+    ll, push, errors = _state.get("ll"), _state.get("push"), _state.get("errors")
+    if ll is not None:
+        ll["buf"].zero_()
+        ll["epoch"] = 0
+    if push is not None:
+        push["flags"].zero_()
+        push["counters"].zero_()
+        push["epoch"] = 0
+    if errors is not None:
+        errors.zero_()
+    engine = _engine.get_engine()
+    if hasattr(engine, "reset"):
+        engine.reset()
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    if dist.is_initialized() and _state["world"] > 1:
+        dist.barrier(group=group)
 
 
 def registered_plans() -> Dict[str, Tuple[str, str, int]]:

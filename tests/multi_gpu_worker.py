@@ -299,6 +299,51 @@ def main():
         torch.testing.assert_close(prm.grad.float(), want, atol=0.03, rtol=2e-2)
     report["checked"] += 1
 
+    # ---- OCS layer over the real engine, the NVLink connector, rank-uniform path choice ----
+    from pccl_b200 import selfcheck
+    ocs = selfcheck.run(only=["misaligned_view_same_path", "ocs_barrier_nvlink_connector",
+                              "ocs_collective_plan_over_engine", "ocs_phase_runner_over_engine"])
+    assert not ocs["failed"] and ocs["passed"] == 4, f"OCS / path-choice cases: {ocs}"
+    report["checked"] += ocs["passed"]
+
+    # A rank that never joins a barrier: the others' wait runs out (a short limit), they get a
+    # timeout naming the missing rank, and after a collective reset the board works again.
+    from pccl_b200.ocs import OCSBarrierTimeout, OCSPlan, OCSRuntime
+    connector = selfcheck._nvlink_connector()
+    runtime = OCSRuntime(connector=connector)
+    if rank != world - 1:
+        try:
+            runtime.barrier_switch(OCSPlan(job_id="absent", barrier_id=50, epoch_id=50, next_epoch_id=51), timeout=0.3)
+        except OCSBarrierTimeout as err:
+            assert str(world - 1) in str(err), f"timeout does not name the missing rank: {err}"
+        else:
+            raise AssertionError("a barrier completed without one of its ranks")
+    torch.cuda.synchronize()
+    dist.barrier()
+    connector.board.reset()
+    dist.barrier()
+    release = runtime.barrier_switch(OCSPlan(job_id="absent", barrier_id=51, epoch_id=51, next_epoch_id=52))
+    assert release["status"] == "OK"
+    report["checked"] += 1
+
+    # A push collective whose peer never calls: bounded wait, error surfaced by synchronize(), reset, then correct.
+    if os.environ.get("PCCL_TEST_PUSH_TIMEOUT", "1") == "1":
+        probe = torch.ones(4096, device="cuda")
+        if rank == 0:
+            pp.all_reduce(probe, algorithm="push")
+            try:
+                pp.synchronize()
+            except Exception as err:  # noqa: BLE001
+                assert "push collective" in str(err), f"unexpected error text: {err}"
+            else:
+                raise AssertionError("a push all-reduce without its peers reported no timeout")
+        pp.reset()
+        probe = torch.full((4096,), float(rank + 1), device="cuda")
+        pp.all_reduce(probe, algorithm="push")
+        pp.synchronize()
+        assert torch.equal(probe, torch.full_like(probe, world * (world + 1) / 2)), "push all-reduce wrong after reset"
+        report["checked"] += 1
+
     torch.cuda.synchronize()
     dist.barrier()
     if rank == 0:

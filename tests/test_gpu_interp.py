@@ -138,13 +138,39 @@ def test_lost_notify_times_out_with_status_and_engine_recovers():
     victim["primitive"] = "noop"
     victim["params"] = {}
     xs = make_inputs("allreduce", 2, 2048)
+    # Registration sees all ranks' plans and refuses this set before anything is launched ...
+    with pytest.raises(engine_c.PCCLError, match="would deadlock"):
+        run_on_cluster(cluster, "broken", broken, xs, 2048)
+    # ... so the device-side wait limit is reached with that check switched off.
+    cluster.setProtocolCheck(False)
     with pytest.raises(engine_c.PCCLTimeoutError, match="timed out waiting for a signal"):
         run_on_cluster(cluster, "broken", broken, xs, 2048)
+    cluster.setProtocolCheck(True)
     status = cluster.lastStatus()
     assert any(s["code"] == 1 for s in status)
     cluster.reset()
     outs = run_on_cluster(cluster, "healthy", plans, xs, 2048)
     torch.testing.assert_close(outs[0].double(), xs[0].double() + xs[1].double(), atol=1e-5, rtol=1e-5)
+
+
+def test_device_timeline_of_a_launch():
+    """Tracing on: every step of the last launch carries four ordered %globaltimer stamps."""
+    from pccl_b200 import engine_c
+    from pccl_b200.utils.trace import phases, summarize
+    world, n = 2, 1 << 20
+    cluster = engine_c.LocalCluster(world, 0, 32 << 20)
+    cluster.setTrace(True)
+    plans = build_plans(TwoShotAllreduce(), "allreduce", world, n, channels=2)
+    xs = make_inputs("allreduce", world, n)
+    outs = run_on_cluster(cluster, "traced", plans, xs, n)
+    torch.testing.assert_close(outs[0].double(), xs[0].double() + xs[1].double(), atol=1e-5, rtol=1e-5)
+    trace = cluster.trace("traced", 0)
+    assert len(trace) == cluster.opInfo("traced", 0)["steps"]
+    for step in trace:
+        assert step["t_reached_ns"] <= step["t_data_ns"] <= step["t_done_ns"] <= step["t_posted_ns"]
+    rows = {r["kind"]: r for r in phases(trace, world)}
+    assert rows["reduce_multi"]["bytes"] == n * 4 // world and rows["reduce_multi"]["span_us"] > 0
+    assert "copy" in rows and "launch span" in summarize(trace, world)
 
 
 def test_single_rank_engine_round_trip(tmp_path):

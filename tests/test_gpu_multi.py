@@ -18,7 +18,9 @@ def _gpu_count():
 
 
 def _torchrun(script, nproc, extra_env=None, timeout=600):
-    env = dict(os.environ)
+    # The workers size their own heaps: settings another test left in this process must not leak in.
+    env = {k: v for k, v in os.environ.items()
+           if not k.startswith("PCCL_") and k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")}
     env.update(extra_env or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(free_port()), os.path.join(HERE, script)]

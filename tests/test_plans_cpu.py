@@ -194,3 +194,44 @@ def test_nvls_allreduce_is_one_pass_and_two_pass_variant_remains():
     assert [op["primitive"] for op in one["operations"] if "multimem" in op["primitive"]] == ["multimem.allreduce"]
     assert [op["primitive"] for op in two["operations"] if "multimem" in op["primitive"]] == \
         ["multimem.reduce", "multimem.store"]
+
+
+def _native():
+    try:
+        from pccl_b200 import engine_c
+        return engine_c
+    except ImportError:
+        pytest.skip("native extension not built")
+
+
+def test_native_world_check_accepts_templates_and_names_a_lost_notify():
+    """The engine's own abstract replay of all ranks' signal protocols (no GPU involved)."""
+    native = _native()
+    for name in ("ring", "twoshot", "nvls", "hybrid", "rhd", "tree", "oneshot"):
+        plans = build_plans(ALGORITHMS[name](), "allreduce", 4, 4 * 64 * 4, channels=2)
+        report = native.check_world([json.dumps(p) for p in plans])
+        assert not report["deadlock"] and report["leftover_signals"] == 0, (name, report)
+        assert report["notifies"] == report["waits"] > 0
+    broken = copy.deepcopy(build_plans(RingAllreduce(), "allreduce", 2, 2048))
+    victim = next(o for o in broken[1]["operations"] if o["primitive"] == "notify")
+    victim["primitive"], victim["params"] = "noop", {}
+    report = native.check_world([json.dumps(p) for p in broken])
+    assert report["deadlock"] and "blocked at" in report["detail"] and "wait_notify" in report["detail"]
+    extra = copy.deepcopy(build_plans(RingAllreduce(), "allreduce", 2, 2048))
+    extra[0]["operations"].append({"index": len(extra[0]["operations"]), "executor": "cuda_sm", "primitive": "notify",
+                                   "channel": 0, "dependencies": [], "next_ops": [],
+                                   "params": {"signal_id": 7, "target_rank": 1}})
+    report = native.check_world([json.dumps(p) for p in extra])
+    assert not report["deadlock"] and report["leftover_signals"] == 1 and "signal 7" in report["detail"]
+    odd = build_plans(RingAllreduce(), "allreduce", 2, 2 * 1001)
+    assert native.check_world([json.dumps(p) for p in odd])["misaligned_ops"] > 0
+
+
+def test_coresident_clamp():
+    """Grids of kernels whose CTAs wait on one another never exceed what is resident at once."""
+    native = _native()
+    assert native.coresident_limit(1, 148) == 148 and native.coresident_limit(2, 148) == 296
+    assert native.clamp_coresident(128, 1, 148) == 128
+    assert native.clamp_coresident(400, 2, 148) == 296
+    assert native.clamp_coresident(0, 1, 148) == 1
+    assert native.clamp_coresident(64, 0, 148) == 0      # the kernel does not fit at all
