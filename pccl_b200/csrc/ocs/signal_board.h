@@ -48,6 +48,14 @@ class SignalBoard {
                          std::vector<std::array<uint32_t, kBoardWords>>* records, uint64_t timeout_us);
   // `record` travels from `root` to every rank (in place).
   BoardStatus broadcast(int root, std::array<uint32_t, kBoardWords>* record, uint64_t timeout_us);
+  // Both rounds of an OCS barrier in one launch, for a leader that has nothing to do on the host
+  // between them: all-gather of the READY records, then the leader (`root`) sends `release` to
+  // everyone once all records are in.  The leader compares words [compare_begin, compare_end) of
+  // every record with its own and clears word 0 of the release when they differ.
+  BoardStatus gather_release(int root, const std::array<uint32_t, kBoardWords>& mine,
+                             const std::array<uint32_t, kBoardWords>& release, int compare_begin, int compare_end,
+                             std::vector<std::array<uint32_t, kBoardWords>>* records,
+                             std::array<uint32_t, kBoardWords>* released, uint64_t timeout_us);
   // A barrier with no payload: one all-gather round.
   BoardStatus barrier(uint64_t timeout_us);
 
@@ -58,13 +66,14 @@ class SignalBoard {
   uint64_t rounds() const { return gather_round_ + bcast_round_; }
 
  private:
-  BoardStatus run(int kind, int root, const uint32_t* payload, uint32_t round, uint64_t timeout_us);
+  BoardStatus run(int kind, int root, const uint32_t* payload, uint32_t round, uint64_t timeout_us,
+                  const uint32_t* release, uint32_t release_round, int compare_begin, int compare_end);
 
   RankContext& ctx_;
   int rank_, world_;
   uint64_t slots_off_ = 0;               // symmetric: u32 [2 kinds][2 parities][world][kBoardSlotWords]
   size_t slots_bytes_ = 0;
-  uint32_t* host_block_ = nullptr;       // pinned, mapped: [world][kBoardSlotWords] records | done | status
+  uint32_t* host_block_ = nullptr;       // pinned, mapped: [world + 1][kBoardSlotWords] records, release | done | status
   uint32_t* host_block_dev_ = nullptr;
   cudaStream_t stream_ = nullptr;
   uint32_t gather_round_ = 0, bcast_round_ = 0;

@@ -201,6 +201,27 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              return py::make_tuple(st.ok, st.missing_rank, st.host_us, std::vector<uint32_t>(record.begin(), record.end()));
            },
            py::arg("root"), py::arg("words"), py::arg("timeout_us") = 1000000)
+      // Both rounds of a barrier in one launch: returns (ok, missing_rank, host_us, records, release).
+      .def("gather_release",
+           [](SignalBoard& b, int root, const std::vector<uint32_t>& words, const std::vector<uint32_t>& release,
+              int compare_begin, int compare_end, uint64_t timeout_us) {
+             std::array<uint32_t, kBoardWords> mine{}, rel{}, got{};
+             TORCH_CHECK(words.size() <= kBoardWords && release.size() <= kBoardWords, "a record holds at most ",
+                         kBoardWords, " words");
+             std::copy(words.begin(), words.end(), mine.begin());
+             std::copy(release.begin(), release.end(), rel.begin());
+             std::vector<std::array<uint32_t, kBoardWords>> records;
+             BoardStatus st;
+             {
+               py::gil_scoped_release unlock;
+               st = b.gather_release(root, mine, rel, compare_begin, compare_end, &records, &got, timeout_us);
+             }
+             py::list out;
+             for (const auto& r : records) out.append(std::vector<uint32_t>(r.begin(), r.end()));
+             return py::make_tuple(st.ok, st.missing_rank, st.host_us, out, std::vector<uint32_t>(got.begin(), got.end()));
+           },
+           py::arg("root"), py::arg("words"), py::arg("release"), py::arg("compare_begin"), py::arg("compare_end"),
+           py::arg("timeout_us") = 1000000)
       .def("barrier",
            [](SignalBoard& b, uint64_t timeout_us) {
              py::gil_scoped_release release;

@@ -25,6 +25,8 @@ def _time_us() -> int:
 
 
 def _one_of(value: Any, allowed: set, what: str) -> str:
+    if value.__class__ is str and value in allowed:       # the common case, without a conversion
+        return value
     text = str(value)
     if text not in allowed:
         raise ValueError(f"unsupported {what} '{text}', expected one of {sorted(allowed)}")
@@ -53,10 +55,11 @@ class OCSPlan:
         put("route_mode", _one_of(self.route_mode, KNOWN_ROUTE_MODES, "route_mode"))
 
         ranks = tuple(int(r) for r in self.participant_ranks)
-        if any(r < 0 for r in ranks):
-            raise ValueError("participant_ranks must be non-negative")
-        if len(set(ranks)) != len(ranks):
-            raise ValueError("participant_ranks must not contain duplicates")
+        if ranks:
+            if min(ranks) < 0:
+                raise ValueError("participant_ranks must be non-negative")
+            if len(set(ranks)) != len(ranks):
+                raise ValueError("participant_ranks must not contain duplicates")
         put("participant_ranks", ranks)
 
         if self.payload is None:
@@ -77,13 +80,21 @@ class OCSPlan:
         """An empty participant list means "the whole group"."""
         if self.participant_ranks:
             return self
-        return replace(self, participant_ranks=tuple(range(int(world_size))))
+        # Every other field was validated when `self` was built: copy instead of re-validating.
+        clone = object.__new__(OCSPlan)
+        clone.__dict__.update(self.__dict__)
+        clone.__dict__.pop("_consistency", None)
+        object.__setattr__(clone, "participant_ranks", tuple(range(int(world_size))))
+        return clone
 
     def consistency_fields(self) -> Dict[str, Any]:
-        fields = {name: getattr(self, name) for name in _IDENTITY}
-        fields["participant_bitmap"] = self.participant_bitmap
-        fields.update((name, getattr(self, name)) for name in _ROUTING)
-        return fields
+        cached = self.__dict__.get("_consistency")       # the plan is immutable: computed once
+        if cached is None:
+            cached = {name: getattr(self, name) for name in _IDENTITY}
+            cached["participant_bitmap"] = self.participant_bitmap
+            cached.update((name, getattr(self, name)) for name in _ROUTING)
+            object.__setattr__(self, "_consistency", cached)
+        return dict(cached)
 
     def ready_record(self, src_rank: int, world_size: int, arrive_seq: int = 0,
                      arrival_time_us: Optional[int] = None) -> Dict[str, Any]:

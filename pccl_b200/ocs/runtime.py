@@ -21,6 +21,7 @@ from __future__ import annotations
 
 import hashlib
 import json
+import operator
 import time
 from dataclasses import dataclass
 from enum import Enum
@@ -36,6 +37,10 @@ from .plan import OCSPlan
 #: fields compared one by one between a READY record and the local plan
 CONSISTENCY_FIELDS = ("job_id", "group_id", "barrier_id", "epoch_id", "next_epoch_id",
                       "topology_id", "route_mode", "route_plan_id", "algorithm", "backend")
+
+
+_COMPARED_FIELDS = (*CONSISTENCY_FIELDS, "participant_bitmap")
+_compared_values = operator.itemgetter(*_COMPARED_FIELDS)
 
 
 def _time_us() -> int:
@@ -187,9 +192,10 @@ class TensorSwitchConnector(TorchDistributedSwitchConnector):
 
     @staticmethod
     def _digest_words(record: Dict[str, Any]) -> Tuple[int, int]:
-        core = {k: record.get(k) for k in CONSISTENCY_FIELDS}
-        core["participant_bitmap"] = record.get("participant_bitmap")
-        raw = hashlib.blake2b(json.dumps(core, sort_keys=True).encode(), digest_size=16).digest()
+        # Canonical text of the agreed fields in a fixed order (field names never vary, so only
+        # the values are hashed; "\x1f" cannot occur in any of them).
+        text = "\x1f".join([str(record.get(k)) for k in CONSISTENCY_FIELDS] + [str(record.get("participant_bitmap"))])
+        raw = hashlib.blake2b(text.encode(), digest_size=16).digest()
         # int64 tensors are signed: fold into the non-negative range.
         return (int.from_bytes(raw[:8], "big") >> 1, int.from_bytes(raw[8:], "big") >> 1)
 
@@ -281,23 +287,43 @@ class NvlinkSwitchConnector(TensorSwitchConnector):
     def _split64(value: int) -> Tuple[int, int]:
         return value & 0xffffffff, (value >> 32) & 0xffffffff
 
+    def _leader_of(self, ready_record) -> int:
+        bitmap = int(ready_record.get("participant_bitmap", 1)) or 1
+        return (bitmap & -bitmap).bit_length() - 1
+
     def exchange_ready(self, ready_record, group=None, timeout=None):
         if not self._usable(group):
             return super().exchange_ready(ready_record, group=group, timeout=timeout)
         d0, d1 = self._digest_words(ready_record)
+        split = self._split64
         words = [int(ready_record["src_rank"]) & 0xffffffff, int(ready_record["arrive_seq"]) & 0xffffffff,
-                 *self._split64(int(ready_record["arrival_time_us"])), *self._split64(d0), *self._split64(d1)]
-        ok, missing, host_us, rows = self.board.all_gather(words, self._timeout_us(timeout))
+                 *split(int(ready_record["arrival_time_us"])), *split(d0), *split(d1)]
+        self._released = None
+        if self.switch_delay_s == 0 and self.link_ready_delay_s == 0:
+            # A leader with nothing to wait for on the host between the rounds: READY gather and
+            # RELEASE delivery in one launch.  The leader's release carries its clock at launch and
+            # is cleared on the device if some rank's digest differs from the leader's.
+            now = _time_us()
+            release = [int(self.link_ready), *split(now), *split(now), *split(now)]
+            ok, missing, host_us, rows, got = self.board.gather_release(
+                self._leader_of(ready_record), words, release, 4, 8, self._timeout_us(timeout))
+            if ok:
+                self._released = got
+        else:
+            ok, missing, host_us, rows = self.board.all_gather(words, self._timeout_us(timeout))
         self.host_us.append(host_us)
         if not ok:
             # Out of step with at least one peer: report the barrier as incomplete (the sender is
             # the only record known to be good).  The board needs reset() before the next barrier.
             return [ready_record]
         records = []
+        mine = (d0, d1)
         for row in rows:
-            peer = dict(ready_record, src_rank=row[0], src_gpu_id=row[0], arrive_seq=row[1],
-                        arrival_time_us=row[2] | (row[3] << 32))
-            if (row[4] | (row[5] << 32), row[6] | (row[7] << 32)) != (d0, d1):
+            peer = dict(ready_record)
+            peer["src_rank"] = peer["src_gpu_id"] = row[0]
+            peer["arrive_seq"] = row[1]
+            peer["arrival_time_us"] = row[2] | (row[3] << 32)
+            if (row[4] | (row[5] << 32), row[6] | (row[7] << 32)) != mine:
                 peer["topology_id"] = -1 - int(peer.get("topology_id", 0))
             records.append(peer)
         return records
@@ -305,17 +331,20 @@ class NvlinkSwitchConnector(TensorSwitchConnector):
     def commit_switch(self, plan, ready_records, group=None, timeout=None):
         if not self._usable(group):
             return super().commit_switch(plan, ready_records, group=group, timeout=timeout)
-        rank, _ = _rank_world_size(group)
-        leader = min(plan.participant_ranks)
-        words = [0] * 7
-        if rank == leader:
-            r = self._simulate_commit()
-            words = [int(r.is_link_ready), *self._split64(r.switch_start_time_us),
-                     *self._split64(r.switch_done_time_us), *self._split64(r.link_ready_time_us or 0)]
-        ok, _, host_us, got = self.board.broadcast(leader, words, self._timeout_us(timeout))
-        self.host_us.append(host_us)
-        if not ok:
-            raise OCSBarrierTimeout(f"barrier {plan.barrier_id}: no RELEASE from leader rank {leader}")
+        got = getattr(self, "_released", None)
+        self._released = None
+        if got is None:
+            rank, _ = _rank_world_size(group)
+            leader = min(plan.participant_ranks)
+            words = [0] * 7
+            if rank == leader:
+                r = self._simulate_commit()
+                words = [int(r.is_link_ready), *self._split64(r.switch_start_time_us),
+                         *self._split64(r.switch_done_time_us), *self._split64(r.link_ready_time_us or 0)]
+            ok, _, host_us, got = self.board.broadcast(leader, words, self._timeout_us(timeout))
+            self.host_us.append(host_us)
+            if not ok:
+                raise OCSBarrierTimeout(f"barrier {plan.barrier_id}: no RELEASE from leader rank {leader}")
         start_us, done_us, ready_us = (got[1] | (got[2] << 32), got[3] | (got[4] << 32), got[5] | (got[6] << 32))
         if got[0]:
             return OCSSwitchResult(OCSLinkState.LINK_ALIGNED, start_us, done_us, ready_us)
@@ -440,6 +469,8 @@ class OCSRuntime:
         expected = plan.consistency_fields()
         wanted = set(plan.participant_ranks)
         seen = set()
+        names = _COMPARED_FIELDS
+        expected_row = tuple(expected[name] for name in names)
         for record in records:
             if record.get("msg_type") != "OCS_BARRIER_READY":
                 raise OCSPlanMismatchError(f"unexpected OCS message: {record!r}")
@@ -450,11 +481,16 @@ class OCSRuntime:
                 raise OCSPlanMismatchError(
                     f"duplicate READY from rank {src} for barrier {plan.barrier_id}")
             seen.add(src)
-            for name in (*CONSISTENCY_FIELDS, "participant_bitmap"):
-                if record.get(name) != expected[name]:
-                    raise OCSPlanMismatchError(
-                        f"rank {src} has inconsistent {name}: "
-                        f"{record.get(name)!r} != {expected[name]!r}")
+            try:
+                same = _compared_values(record) == expected_row      # one C-level tuple comparison
+            except KeyError:
+                same = False
+            if not same:
+                for name in names:
+                    if record.get(name) != expected[name]:
+                        raise OCSPlanMismatchError(
+                            f"rank {src} has inconsistent {name}: "
+                            f"{record.get(name)!r} != {expected[name]!r}")
         missing = sorted(wanted - seen)
         if missing:
             raise OCSBarrierTimeout(
