@@ -4,7 +4,9 @@
 
 Device timing with CUDA events; a 256 MB buffer is rewritten between iterations
 so that operands do not stay in the 126 MB L2.  Prints one JSON line per shape with
-TFLOP/s of both and the fraction of the measured cuBLAS peak in MEASURED_PEAKS.json.
+TFLOP/s of the paired-SM kernel ("ours": tcgen05.mma.cta_group::2 on 256 x 256 tiles), of the
+one-SM-per-tile kernel and of cuBLAS, and the fraction of the measured cuBLAS peak in
+MEASURED_PEAKS.json.
 """
 
 import argparse
@@ -50,13 +52,15 @@ def main():
         a = torch.randn(m, k, device="cuda").to(torch.bfloat16)
         b = torch.randn(n, k, device="cuda").to(torch.bfloat16)
         c = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
-        ours_med, ours_min = timed(lambda: gemm.matmul_nt(a, b, c), args.iters, flush)
+        one_med, _ = timed(lambda: gemm.matmul_nt(a, b, c, sms_per_tile=1), args.iters, flush)
+        ours_med, ours_min = timed(lambda: gemm.matmul_nt(a, b, c, sms_per_tile=2), args.iters, flush)
         gemm.check()
         lib_med, lib_min = timed(lambda: torch.matmul(a, b.t(), out=c), args.iters, flush)
         flops = 2.0 * m * n * k
         print(json.dumps({
             "shape": [m, n, k], "ours_ms": round(ours_med, 4), "cublas_ms": round(lib_med, 4),
             "ours_tflops": round(flops / ours_med / 1e9, 1), "cublas_tflops": round(flops / lib_med / 1e9, 1),
+            "one_sm_per_tile_tflops": round(flops / one_med / 1e9, 1),
             "ours_best_tflops": round(flops / ours_min / 1e9, 1),
             "frac_of_measured_peak": round(flops / ours_med / 1e9 / peak, 3),
             "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback"}), flush=True)

@@ -43,15 +43,17 @@ void bind_fused_ops(py::module_& m) {
   auto f = m.def_submodule("fused", "tcgen05 / TMEM fused operators");
   // c[M,N] = a[M,K] @ b[N,K]^T   (nn.Linear weight layout), bf16 in / bf16 out, fp32 accumulate.
   f.def("matmul_nt",
-        [](const torch::Tensor& a, const torch::Tensor& b, c10::optional<torch::Tensor> out, int ctas) {
+        [](const torch::Tensor& a, const torch::Tensor& b, c10::optional<torch::Tensor> out, int ctas,
+           int sms_per_tile) {
           const gemm::MatrixDesc da = as_matrix(a, "a"), db = as_matrix(b, "b");
           torch::Tensor c = out.has_value() ? *out : torch::empty({a.size(0), b.size(0)}, a.options());
           TORCH_CHECK(c.scalar_type() == torch::kBFloat16 && c.stride(1) == 1 && c.size(0) == a.size(0) &&
                           c.size(1) == b.size(0), "out has the wrong shape / dtype");
-          gemm::gemm_bf16_nt(da, db, c.data_ptr(), c.stride(0), c10::cuda::getCurrentCUDAStream().stream(), ctas);
+          gemm::gemm_bf16_nt(da, db, c.data_ptr(), c.stride(0), c10::cuda::getCurrentCUDAStream().stream(), ctas,
+                             2000, sms_per_tile);
           return c;
         },
-        py::arg("a"), py::arg("b"), py::arg("out") = py::none(), py::arg("ctas") = 0);
+        py::arg("a"), py::arg("b"), py::arg("out") = py::none(), py::arg("ctas") = 0, py::arg("sms_per_tile") = 0);
   // Fused GEMM -> reduce-scatter over the engine's ranks (see fused/gemm_host.h for the contract).
   f.def("gemm_reduce_scatter",
         [](const torch::Tensor& x, const torch::Tensor& w, torch::Tensor& out, int64_t recv_off, int64_t flags_off,

@@ -20,9 +20,11 @@ struct MatrixDesc {
 };
 
 // C[M,N] (bf16, row-major, leading dimension ldc) = A[M,K] * B[N,K]^T.
-// `ctas` = 0 uses one CTA per SM.  Throws pccl::Error on invalid arguments.
+// `ctas` = 0 uses one CTA per SM.  sms_per_tile: 2 = pairs of SMs work on 256 x 256 tiles with
+// tcgen05.mma.cta_group::2, 1 = one SM per 128 x 256 tile, 0 = PCCL_GEMM_SMS_PER_TILE (default 2).
+// Throws pccl::Error on invalid arguments.
 void gemm_bf16_nt(const MatrixDesc& a, const MatrixDesc& b, void* c, int64_t ldc, cudaStream_t stream,
-                  int ctas = 0, uint64_t timeout_ms = 2000);
+                  int ctas = 0, uint64_t timeout_ms = 2000, int sms_per_tile = 0);
 
 // Every rank's symmetric heap base as mapped into this process, plus rank / world.
 struct PeerBases {

@@ -10,6 +10,7 @@
 #include "moe_policies.cuh"
 #include "tp_policies.cuh"
 #include "umma_gemm.cuh"
+#include "umma_gemm2.cuh"
 
 namespace pccl {
 namespace gemm {
@@ -85,6 +86,7 @@ void launch(const MatrixDesc& a, const MatrixDesc& b, const typename Policy::Par
   g.M = a.rows; g.N = b.rows / groups; g.K = a.cols;
   g.tiles_m = (g.M + kBM - 1) / kBM;
   g.tiles_n = (g.N + kBN - 1) / kBN;
+  g.bn = kBN;
   g.error = error_word();
   g.timeout_ns = timeout_ms * 1000000ull;
   const CUtensorMap ta = make_map(a, kBM), tb = make_map(b, kBN);
@@ -108,6 +110,54 @@ void launch(const MatrixDesc& a, const MatrixDesc& b, const typename Policy::Par
   (void)attr_once;
 }
 
+// Tile width of the paired kernel.  Measured on 8192 x 1792 x 4096: 256 columns 1198 TFLOP/s, 224 the
+// same, 128 784, 96 638, 64 462.  A 256 x 256 x 16 step reads 8 KB of shared memory per SM in the 64
+// clocks its MMA takes; a narrower tile still reads the same 4 KB of A per step while its MMA
+// shrinks, so it turns shared-memory bound and a round costs almost the same however narrow the
+// tile.  Narrow tiles therefore never pay for the better fit of their tile count to the SM pairs:
+// the width stays 256 unless PCCL_GEMM_TILE_N (a multiple of 32) says otherwise.
+int pick_tile_n(int, int, int) { return kBN; }
+
+// The two-SM kernel: clusters of two CTAs, each CTA loading 128-row boxes of A and of B.
+template <class Policy>
+void launch_pair(const MatrixDesc& a, const MatrixDesc& b, const typename Policy::Params& params, int ctas,
+                 uint64_t timeout_ms, cudaStream_t stream, bool cooperative) {
+  PCCL_CHECK(a.cols == b.cols, "GEMM: A and B disagree on K (" << a.cols << " vs " << b.cols << ")");
+  PCCL_CHECK(a.cols % 8 == 0 && b.rows % 8 == 0, "GEMM: K and N must be multiples of 8");
+  Problem g;
+  g.M = a.rows; g.N = b.rows; g.K = a.cols;
+  g.tiles_m = (g.M + kBM - 1) / kBM;
+  int grid = ctas > 0 ? ctas : sm_count();
+  if (grid > sm_count()) grid = sm_count();
+  grid &= ~1;                                             // whole pairs only
+  if (grid < 2) grid = 2;
+  const int64_t forced_bn = Environs::get_int("PCCL_GEMM_TILE_N", 0);
+  g.bn = forced_bn >= 32 && forced_bn <= kBN && forced_bn % 32 == 0 ? static_cast<int>(forced_bn)
+                                                                      : pick_tile_n(g.M, g.N, grid / 2);
+  g.tiles_n = (g.N + g.bn - 1) / g.bn;
+  g.error = error_word();
+  g.timeout_ns = timeout_ms * 1000000ull;
+  const CUtensorMap ta = make_map(a, kBM), tb = make_map(b, g.bn / 2);
+  auto kernel = umma_gemm2_kernel<Policy>;
+  PCCL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2));
+  const int pair_tiles = (g.tiles_m + 1) / 2 * g.tiles_n;
+  if (grid > 2 * pair_tiles) grid = 2 * pair_tiles;
+  if (grid < 2) grid = 2;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kSmemBytes2;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = 2; attrs[0].val.clusterDim.y = 1; attrs[0].val.clusterDim.z = 1;
+  attrs[1].id = cudaLaunchAttributeCooperative;
+  attrs[1].val.cooperative = 1;
+  cfg.attrs = attrs;
+  cfg.numAttrs = cooperative && cooperative_launches() ? 2 : 1;
+  PCCL_CUDA(cudaLaunchKernelEx(&cfg, kernel, ta, tb, g, params));
+}
+
 }  // namespace
 
 uint32_t* error_word() {
@@ -127,10 +177,14 @@ uint32_t read_error() {
 void clear_error() { PCCL_CUDA(cudaMemset(error_word(), 0, sizeof(uint32_t))); }
 
 void gemm_bf16_nt(const MatrixDesc& a, const MatrixDesc& b, void* c, int64_t ldc, cudaStream_t stream, int ctas,
-                  uint64_t timeout_ms) {
+                  uint64_t timeout_ms, int sms_per_tile) {
   PCCL_CHECK(ldc % 8 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0, "GEMM: C must be 16-byte aligned rows");
+  PCCL_CHECK(sms_per_tile >= 0 && sms_per_tile <= 2, "GEMM: sms_per_tile is 0 (default), 1 or 2");
   StorePolicy::Params p{static_cast<__nv_bfloat16*>(c), ldc};
-  launch<StorePolicy>(a, b, p, ctas, timeout_ms, stream);
+  if (sms_per_tile == 0) sms_per_tile = static_cast<int>(Environs::get_int("PCCL_GEMM_SMS_PER_TILE", 2));
+  // A single 128-row block gains nothing from pairing two SMs.
+  if (sms_per_tile == 2 && a.rows > kBM) launch_pair<StorePolicy>(a, b, p, ctas, timeout_ms, stream, false);
+  else launch<StorePolicy>(a, b, p, ctas, timeout_ms, stream);
 }
 
 namespace {

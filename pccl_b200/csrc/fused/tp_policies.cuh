@@ -156,8 +156,8 @@ struct ReduceScatterPolicy : PolicyDefaults {
       }
       __syncthreads();
       if (!ok_flag) return;
-      const int row0 = block * kBM, col0 = nb * kBN;
-      const int rows = min(kBM, p.rows_per_rank - row0), cols = min(kBN, g.N - col0);
+      const int row0 = block * kBM, col0 = nb * g.bn;
+      const int rows = min(kBM, p.rows_per_rank - row0), cols = min(g.bn, g.N - col0);
       const int vec_per_row = cols / 8;                    // 8 bf16 per 16 bytes (N % 8 == 0)
       const int total = rows * vec_per_row;
       if (world <= 2) sum_slots<2>(p, g, me, world, row0, col0, vec_per_row, total);

@@ -43,6 +43,7 @@ constexpr uint32_t kTmemCols = 512;                             // 2 accumulator
 struct Problem {
   int M, N, K;
   int tiles_m, tiles_n;
+  int bn;                     // columns per tile: kBN, or what the paired kernel's launcher chose (a multiple of 32)
   uint32_t* error;            // device word: 0 ok, else (code << 8 | role)
   uint64_t timeout_ns;
 };
@@ -80,7 +81,7 @@ struct PolicyDefaults {
 };
 
 template <class P>
-__device__ int PolicyDefaults::b_row(const P&, const Problem&, int, int nb) { return nb * kBN; }
+__device__ int PolicyDefaults::b_row(const P&, const Problem& g, int, int nb) { return nb * g.bn; }
 
 struct RowInfo {
   uint8_t* dst;      // address of output column 0 of this row

@@ -1,0 +1,315 @@
+// The two-SM form of the persistent bf16 GEMM: one tcgen05.mma.cta_group::2 instruction drives the
+// tensor cores of a pair of SMs on a 256 x 256 tile.
+//
+// The kernel runs as clusters of two CTAs.  CTA r of a pair owns rows [128 r, 128 r + 128) of the
+// tile: it loads its own 128 x 64 block of A and its own *half* of the B block (128 of the 256
+// weight rows) per pipeline stage, keeps its half of the accumulator (128 lanes x 256 columns) in
+// its own tensor memory and stores its own rows.  The instruction, issued by one thread of the
+// even CTA, reads A and B from both CTAs' shared memory, so every byte of B is loaded and held
+// once per pair instead of once per SM: a stage costs 32 KB per CTA instead of 48 KB, which buys
+// six pipeline stages instead of four, and the shared-memory traffic per flop drops by a quarter.
+//
+// Hand-off between the CTAs (never a multicast load):
+//   * each CTA issues its own plain TMA loads, in the cta_group::2 form whose completion bytes are
+//     counted on the *even* CTA's "full" barrier (the odd CTA passes that barrier's address with
+//     the pair bit cleared), after registering its expected bytes there with a remote
+//     mbarrier.arrive.expect_tx;
+//   * tcgen05.commit with a two-CTA mask arrives on the "stage free" and "accumulator ready"
+//     barriers of both CTAs at once;
+//   * the odd CTA's epilogue warps release an accumulator with a remote mbarrier.arrive on the
+//     even CTA's barrier;
+//   * cluster-wide barriers bracket the kernel (barrier initialisation, and no CTA exits while its
+//     partner may still read its shared memory or signal its barriers).
+// Roles, policies, bounded waits and error reporting are those of umma_gemm_kernel.  Policies see
+// 128-row blocks as before: the pair processes blocks (2 i, 2 i + 1) of one n-tile together.
+// The tile width is a launch parameter (Problem::bn, a multiple of 32 up to 256): the launcher
+// picks the width whose tile count divides best over the SM pairs, because with whole 256-column
+// tiles a shape like 8192 x 1792 leaves 3.03 rounds of work to be done in 4.
+#pragma once
+#include "umma_gemm.cuh"
+
+namespace pccl {
+namespace gemm {
+
+constexpr int kStages2 = 6;
+constexpr uint32_t kBytesA2 = kBM * kBK * 2;                     // this CTA's 128 x 64 block of A
+constexpr uint32_t kBytesB2 = (kBN / 2) * kBK * 2;               // this CTA's half of the 256 x 64 block of B
+constexpr uint32_t kStageBytes2 = kBytesA2 + kBytesB2;           // 32 KB
+constexpr uint32_t kSmemBytes2 = kStages2 * kStageBytes2 + 4 * kEpiWarpBytes + 1024;
+constexpr uint32_t kPeerMask = 0xFEFFFFFFu;                      // clears the bit that tells the pair's CTAs apart
+
+namespace ptx2 {
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of the same shared-memory object in the even CTA of the pair.
+__device__ __forceinline__ uint32_t leader_addr(const void* p) { return ptx::smem_u32(p) & kPeerMask; }
+
+__device__ __forceinline__ void mbar_expect_tx_leader(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(leader_addr(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(leader_addr(bar)) : "memory");
+}
+// Plain (non-multicast) tile load into this CTA's shared memory; completion bytes go to the even
+// CTA's barrier.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(ptx::smem_u32(smem_dst)), "l"(map), "r"(leader_addr(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_out, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ptx::smem_u32(smem_out)),
+               "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// D[tmem of both CTAs] (+)= A * B^T with M = 256 over the pair.  One thread of the even CTA issues.
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on `bar` (same offset) in both CTAs once all MMAs issued so far have completed.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(ptx::smem_u32(bar)), "h"(mask) : "memory");
+}
+
+}  // namespace ptx2
+
+struct Pipe2 {
+  uint64_t full[kStages2];      // used in the even CTA: 2 arrivals (one per CTA's producer) + 64 KB
+  uint64_t empty[kStages2];     // one per CTA, released by the pair-wide commit
+  uint64_t acc_full[2];         // one per CTA, released by the pair-wide commit
+  uint64_t acc_empty[2];        // used in the even CTA: 8 arrivals (4 epilogue warps of each CTA)
+  uint32_t tmem_base;
+  uint32_t stored_count;
+};
+
+template <class Policy>
+__global__ void __launch_bounds__(kThreads, 1)
+umma_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                  const Problem g, const typename Policy::Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ Pipe2 pipe;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const volatile uint32_t* abort_flag = g.error;
+  const uint64_t deadline = ptx::globaltimer() + g.timeout_ns;
+  const int half = static_cast<int>(ptx2::cluster_ctarank());      // 0 = even CTA (issues the MMAs)
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages2; ++s) { ptx::mbar_init(&pipe.full[s], 2); ptx::mbar_init(&pipe.empty[s], 1); }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(&pipe.acc_full[a], 1);
+      ptx::mbar_init(&pipe.acc_empty[a], 8);
+    }
+    pipe.stored_count = 0;
+    ptx::mbar_init_fence();
+    ptx::tma_prefetch_desc(&tma_a);
+    ptx::tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 1) {
+    ptx2::tmem_alloc_pair(&pipe.tmem_base, kTmemCols);
+    ptx2::tmem_relinquish_pair();
+  }
+  ptx::tc_fence_before_sync();
+  ptx2::cluster_sync();                      // both CTAs' barriers exist before anyone signals the partner
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = pipe.tmem_base;
+
+  // The pair walks the policy's tile order over 256-row blocks: block pair i = 128-row blocks 2i, 2i+1.
+  Problem g2 = g;
+  g2.tiles_m = (g.tiles_m + 1) / 2;
+  const int tiles_m = Policy::prepare(p, g, deadline, abort_flag);
+  const int num_tiles = tiles_m < 0 ? 0 : g2.tiles_m * g.tiles_n;
+  const int k_blocks = (g.K + kBK - 1) / kBK;
+  bool failed = false;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      for (int tile = pair; tile < num_tiles && !failed; tile += num_pairs) {
+        int mb2, nb;
+        Policy::tile_coords(p, g2, tile, &mb2, &nb);
+        const int mb = 2 * mb2 + half;
+        if (!Policy::before_load(p, g, mb, deadline, abort_flag)) { raise_error(g, kErrPolicyWait, 0); failed = true; break; }
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!ptx::mbar_wait(&pipe.empty[stage], phase ^ 1u, deadline, abort_flag)) {
+            raise_error(g, kErrProducerWait, 0); failed = true; break;
+          }
+          uint8_t* a_dst = smem + stage * kStageBytes2;
+          uint8_t* b_dst = a_dst + kBytesA2;
+          ptx2::mbar_expect_tx_leader(&pipe.full[stage], kBytesA2 + static_cast<uint32_t>(g.bn / 2) * kBK * 2);
+          ptx2::tma_load_2d_pair(a_dst, &tma_a, &pipe.full[stage], kb * kBK, mb * kBM);
+          ptx2::tma_load_2d_pair(b_dst, &tma_b, &pipe.full[stage], kb * kBK,
+                                 Policy::b_row(p, g, mb, nb) + half * (g.bn / 2));
+          if (++stage == kStages2) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer (even CTA only)
+    if (lane == 0 && half == 0) {
+      const uint32_t idesc = ptx::umma_idesc_f32(2 * kBM, static_cast<uint32_t>(g.bn), true);
+      uint32_t stage = 0, phase = 0;
+      uint32_t local_tile = 0;
+      for (int tile = pair; tile < num_tiles && !failed; tile += num_pairs, ++local_tile) {
+        const uint32_t acc = local_tile & 1u, acc_phase = (local_tile >> 1) & 1u;
+        if (!ptx::mbar_wait(&pipe.acc_empty[acc], acc_phase ^ 1u, deadline, abort_flag)) {
+          raise_error(g, kErrMmaWait, 1); failed = true; break;
+        }
+        ptx::tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + acc * kBN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!ptx::mbar_wait(&pipe.full[stage], phase, deadline, abort_flag)) {
+            raise_error(g, kErrMmaWait, 1); failed = true; break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t a_addr = ptx::smem_u32(smem + stage * kStageBytes2);
+          const uint32_t b_addr = a_addr + kBytesA2;
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            const uint64_t da = ptx::umma_desc_k_sw128(a_addr + k * kUmmaK * 2);
+            const uint64_t db = ptx::umma_desc_k_sw128(b_addr + k * kUmmaK * 2);
+            ptx2::umma_f16_pair(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          ptx2::umma_commit_pair(&pipe.empty[stage]);       // frees the stage in both CTAs
+          if (++stage == kStages2) { stage = 0; phase ^= 1u; }
+        }
+        if (!failed) ptx2::umma_commit_pair(&pipe.acc_full[acc]);   // accumulator halves complete in both CTAs
+      }
+    }
+  } else if (warp == 6) {
+    // ---------------------------------------------------------------- signal warp
+    if (Policy::kSignalsTiles && lane == 0) {
+      uint32_t local_tile = 0;
+      for (int tile = pair; tile < num_tiles; tile += num_pairs, ++local_tile) {
+        const uint32_t want = 4u * (local_tile + 1u);
+        const volatile uint32_t* count = &pipe.stored_count;
+        uint32_t spins = 0;
+        bool ok = true;
+        while (static_cast<int32_t>(*count - want) < 0) {
+          if ((++spins & 255u) == 0u && (*abort_flag || ptx::globaltimer() > deadline)) { ok = false; break; }
+        }
+        if (!ok) break;
+        __threadfence_block();
+        int mb2, nb;
+        Policy::tile_coords(p, g2, tile, &mb2, &nb);
+        if (2 * mb2 + half < g.tiles_m) Policy::tile_done(p, g, 2 * mb2 + half, nb);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (warps 2..5, both CTAs)
+    const int quarter = warp & 3;
+    uint32_t local_tile = 0;
+    for (int tile = pair; tile < num_tiles; tile += num_pairs, ++local_tile) {
+      const uint32_t acc = local_tile & 1u, acc_phase = (local_tile >> 1) & 1u;
+      int mb2, nb;
+      Policy::tile_coords(p, g2, tile, &mb2, &nb);
+      const int mb = 2 * mb2 + half;
+      uint32_t ok = 1;
+      if (lane == 0) ok = ptx::mbar_wait(&pipe.acc_full[acc], acc_phase, deadline, abort_flag) ? 1u : 0u;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) { if (lane == 0) raise_error(g, kErrEpilogueWait, 2); break; }
+      ptx::tc_fence_after_sync();
+      constexpr int kOut = Policy::kOutPer32;
+      constexpr int kRowBytes = kEpiCols / 32 * kOut * 2;
+      constexpr int kChunks = kRowBytes / 16;
+      constexpr int kRowsPerSt = 32 / kChunks;
+      RowInfo info;
+      const bool block_ok = mb < g.tiles_m;              // an odd number of row blocks leaves the last pair half empty
+      if constexpr (Policy::kRowScatter) {
+        info = Policy::row_info(p, g, block_ok ? mb : 0, quarter * 32 + lane);
+        if (!block_ok) info.valid = 0;
+      } else {
+        info.dst = Policy::tile_base(p, g, block_ok ? mb : 0) +
+                   static_cast<int64_t>(quarter * 32 + lane) * Policy::row_pitch(p, g);
+        info.scale = 1.f;
+        info.valid = block_ok && mb * kBM + quarter * 32 + lane < g.M ? 1u : 0u;
+      }
+      const int out_cols = g.N * kOut / 32;
+      const uint32_t taddr = tmem_base + acc * kBN + (static_cast<uint32_t>(quarter * 32) << 16);
+      uint8_t* stage_buf = smem + kStages2 * kStageBytes2 + (warp - 2) * kEpiWarpBytes;
+#pragma unroll 1
+      for (int c0 = 0; c0 < g.bn; c0 += kEpiCols) {
+#pragma unroll
+        for (int q = 0; q < kEpiCols / 32; ++q) {
+          if (c0 + q * 32 >= g.bn) break;                  // narrower tiles end inside a pass
+          uint32_t v[32];
+          ptx::tmem_ld_32x32b_x32(taddr + c0 + q * 32, v);
+          ptx::tmem_ld_wait();
+          float o[kOut];
+          Policy::transform(reinterpret_cast<const float*>(v), info.scale, o);
+#pragma unroll
+          for (int i = 0; i < kOut / 8; ++i) {
+            const int chunk = (q * (kOut / 8) + i) ^ (lane & (kChunks - 1));
+            *reinterpret_cast<uint4*>(stage_buf + lane * kRowBytes + chunk * 16) = pack8_bf16(o + 8 * i);
+          }
+        }
+        __syncwarp();
+        const int col_first = (nb * g.bn + c0) / 32 * kOut;
+        const int pass_cols = min(kEpiCols, g.bn - c0) / 32 * kOut;      // output columns this pass holds
+#pragma unroll 4
+        for (int it = 0; it < 32 / kRowsPerSt; ++it) {
+          const int r = it * kRowsPerSt + lane / kChunks, j = lane % kChunks;
+          const uint64_t dst_bits = __shfl_sync(0xffffffffu, reinterpret_cast<uint64_t>(info.dst), r);
+          const uint32_t row_ok = __shfl_sync(0xffffffffu, info.valid, r);
+          const int col = col_first + j * 8;
+          const uint4 val = *reinterpret_cast<const uint4*>(stage_buf + r * kRowBytes + ((j ^ (r & (kChunks - 1))) * 16));
+          if (row_ok && j * 8 < pass_cols && col < out_cols)
+            ptx::st_v4(reinterpret_cast<uint8_t*>(dst_bits) + static_cast<int64_t>(col) * 2, val);
+        }
+        __syncwarp();
+      }
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        ptx2::mbar_arrive_leader(&pipe.acc_empty[acc]);      // the even CTA's barrier collects both CTAs' warps
+        if (Policy::kSignalsTiles) {
+          __threadfence_block();
+          atomicAdd_block(&pipe.stored_count, 1u);
+        }
+      }
+    }
+  }
+
+  // A role that gave up may have left loads in flight or the partner mid-tile: give outstanding
+  // bulk copies time to land (their latency is a few microseconds) before anyone can exit.
+  if (*abort_flag) {
+    const uint64_t until = ptx::globaltimer() + 200000ull;
+    while (ptx::globaltimer() < until) __nanosleep(1000);
+  }
+  ptx::tc_fence_before_sync();
+  ptx2::cluster_sync();                      // the partner no longer reads this CTA's memory or barriers
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx2::tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+  Policy::finish(p, g, blockIdx.x, gridDim.x, deadline, abort_flag);
+}
+
+}  // namespace gemm
+}  // namespace pccl

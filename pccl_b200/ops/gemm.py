@@ -25,8 +25,11 @@ def available() -> bool:
         return False
 
 
-def matmul_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, ctas: int = 0) -> torch.Tensor:
-    return _native().matmul_nt(a, b, out, ctas)
+def matmul_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, ctas: int = 0,
+              sms_per_tile: int = 0) -> torch.Tensor:
+    """``sms_per_tile``: 2 = pairs of SMs share 256 x 256 tiles (``tcgen05.mma.cta_group::2``), 1 = one SM per
+    128 x 256 tile, 0 = the default (``PCCL_GEMM_SMS_PER_TILE``, 2)."""
+    return _native().matmul_nt(a, b, out, ctas, sms_per_tile)
 
 
 def check() -> None:

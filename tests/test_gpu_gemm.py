@@ -6,14 +6,16 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("sms_per_tile", [1, 2])
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 256, 256), (256, 512, 128), (384, 768, 1024),
                                    (200, 312, 72), (8192, 4096, 1792), (1024, 1792, 4096)])
-def test_matmul_nt_matches_fp32_reference(m, n, k):
+def test_matmul_nt_matches_fp32_reference(m, n, k, sms_per_tile):
+    """Both forms: one SM per 128 x 256 tile, and pairs of SMs on 256 x 256 tiles (cta_group::2)."""
     from pccl_b200.ops import gemm
     g = torch.Generator(device="cuda").manual_seed(m + n + k)
     a = torch.randn(m, k, device="cuda", generator=g).to(torch.bfloat16)
     b = (torch.randn(n, k, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
-    c = gemm.matmul_nt(a, b)
+    c = gemm.matmul_nt(a, b, sms_per_tile=sms_per_tile)
     torch.cuda.synchronize()
     gemm.check()
     ref = a.float() @ b.float().t()
@@ -21,17 +23,18 @@ def test_matmul_nt_matches_fp32_reference(m, n, k):
     torch.testing.assert_close(c.float(), ref, atol=2e-2 * (k ** 0.5) * 0.05, rtol=2 ** -7)
 
 
-def test_distinct_tiles_land_in_their_own_places():
+@pytest.mark.parametrize("sms_per_tile", [1, 2])
+def test_distinct_tiles_land_in_their_own_places(sms_per_tile):
     """A structured input catches swizzle / descriptor mistakes that random data could hide."""
     from pccl_b200.ops import gemm
-    m, n, k = 256, 512, 128
+    m, n, k = 256 + 128 * (sms_per_tile - 1), 512, 128          # an odd number of row blocks for the paired form
     a = torch.zeros(m, k, device="cuda", dtype=torch.bfloat16)
     b = torch.zeros(n, k, device="cuda", dtype=torch.bfloat16)
     a[:, 0] = torch.arange(m, device="cuda").to(torch.bfloat16) % 64
     a[:, 77] = 1
     b[:, 0] = 1
     b[:, 77] = (torch.arange(n, device="cuda") % 32).to(torch.bfloat16)
-    c = gemm.matmul_nt(a, b)
+    c = gemm.matmul_nt(a, b, sms_per_tile=sms_per_tile)
     torch.cuda.synchronize()
     gemm.check()
     ref = a.float() @ b.float().t()
