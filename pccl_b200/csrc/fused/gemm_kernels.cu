@@ -121,19 +121,20 @@ int pick_tile_n(int, int, int) { return kBN; }
 // The two-SM kernel: clusters of two CTAs, each CTA loading 128-row boxes of A and of B.
 template <class Policy>
 void launch_pair(const MatrixDesc& a, const MatrixDesc& b, const typename Policy::Params& params, int ctas,
-                 uint64_t timeout_ms, cudaStream_t stream, bool cooperative) {
+                 uint64_t timeout_ms, cudaStream_t stream, bool cooperative, int aux_ctas = 0) {
   PCCL_CHECK(a.cols == b.cols, "GEMM: A and B disagree on K (" << a.cols << " vs " << b.cols << ")");
   PCCL_CHECK(a.cols % 8 == 0 && b.rows % 8 == 0, "GEMM: K and N must be multiples of 8");
   Problem g;
   g.M = a.rows; g.N = b.rows; g.K = a.cols;
   g.tiles_m = (g.M + kBM - 1) / kBM;
+  PCCL_CHECK(aux_ctas % 2 == 0, "paired GEMM: auxiliary CTAs come in whole clusters of two");
   int grid = ctas > 0 ? ctas : sm_count();
   if (grid > sm_count()) grid = sm_count();
   grid &= ~1;                                             // whole pairs only
-  if (grid < 2) grid = 2;
+  if (grid < aux_ctas + 2) grid = aux_ctas + 2;
   const int64_t forced_bn = Environs::get_int("PCCL_GEMM_TILE_N", 0);
   g.bn = forced_bn >= 32 && forced_bn <= kBN && forced_bn % 32 == 0 ? static_cast<int>(forced_bn)
-                                                                      : pick_tile_n(g.M, g.N, grid / 2);
+                                                                      : pick_tile_n(g.M, g.N, (grid - aux_ctas) / 2);
   g.tiles_n = (g.N + g.bn - 1) / g.bn;
   g.error = error_word();
   g.timeout_ns = timeout_ms * 1000000ull;
@@ -141,8 +142,7 @@ void launch_pair(const MatrixDesc& a, const MatrixDesc& b, const typename Policy
   auto kernel = umma_gemm2_kernel<Policy>;
   PCCL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2));
   const int pair_tiles = (g.tiles_m + 1) / 2 * g.tiles_n;
-  if (grid > 2 * pair_tiles) grid = 2 * pair_tiles;
-  if (grid < 2) grid = 2;
+  if (grid - aux_ctas > 2 * pair_tiles) grid = 2 * pair_tiles + aux_ctas;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kThreads);
@@ -215,7 +215,11 @@ void gemm_reduce_scatter(const PeerBases& peers, const MatrixDesc& x, const Matr
   p.rows_per_rank = rows_per_rank;
   p.blocks_per_rank = rows_per_rank / kBM;
   p.epoch = epoch;
-  launch<ReduceScatterPolicy>(x, w, p, ctas, timeout_ms, stream);
+  // Pairs of SMs on 256-row blocks when every rank's rows split into whole pairs of blocks.
+  if (Environs::get_int("PCCL_GEMM_SMS_PER_TILE", 2) == 2 && p.blocks_per_rank % 2 == 0)
+    launch_pair<ReduceScatterPolicy>(x, w, p, ctas, timeout_ms, stream, true);
+  else
+    launch<ReduceScatterPolicy>(x, w, p, ctas, timeout_ms, stream);
 }
 
 void all_gather_gemm(const PeerBases& peers, uint64_t gathered_off, int M, int K, const MatrixDesc& w,
@@ -258,7 +262,10 @@ void all_gather_gemm(const PeerBases& peers, uint64_t gathered_off, int M, int K
   p.epoch = epoch;
   MatrixDesc a{peers.base[peers.rank] + gathered_off, M, K, K};
   int grid = ctas > 0 ? ctas : sms;
-  launch<AllGatherPolicy>(a, w, p, grid, timeout_ms, stream, p.copy_ctas);
+  if (Environs::get_int("PCCL_GEMM_SMS_PER_TILE", 2) == 2 && p.blocks_per_rank % 2 == 0 && p.copy_ctas % 2 == 0)
+    launch_pair<AllGatherPolicy>(a, w, p, grid, timeout_ms, stream, true, p.copy_ctas);
+  else
+    launch<AllGatherPolicy>(a, w, p, grid, timeout_ms, stream, p.copy_ctas);
 }
 
 namespace {

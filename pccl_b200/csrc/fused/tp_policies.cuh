@@ -65,6 +65,15 @@ struct ReduceScatterPolicy : PolicyDefaults {
     *mb = owner * p.blocks_per_rank + block_seq / p.peers.world;
     *nb = tile % g.tiles_n;
   }
+  // The same order for the paired kernel, in units of two row blocks (rows per rank are then a
+  // multiple of 256, so a pair never straddles two owners).
+  __device__ static void pair_coords(const Params& p, const Problem& g, int tile, int* mb2, int* nb) {
+    const int pairs_per_rank = p.blocks_per_rank / 2;
+    const int block_seq = tile / g.tiles_n;
+    const int owner = (p.peers.rank + 1 + block_seq % p.peers.world) % p.peers.world;
+    *mb2 = owner * pairs_per_rank + block_seq / p.peers.world;
+    *nb = tile % g.tiles_n;
+  }
   __device__ static bool before_load(const Params&, const Problem&, int, uint64_t, const volatile uint32_t*) {
     return true;
   }
@@ -192,6 +201,14 @@ struct AllGatherPolicy : PolicyDefaults {
     const int within = tile % per_shard;
     *mb = shard * p.blocks_per_rank + within % p.blocks_per_rank;
     *nb = within / p.blocks_per_rank;
+  }
+  __device__ static void pair_coords(const Params& p, const Problem& g, int tile, int* mb2, int* nb) {
+    const int pairs_per_rank = p.blocks_per_rank / 2;
+    const int per_shard = pairs_per_rank * g.tiles_n;
+    const int shard = (p.peers.rank + tile / per_shard) % p.peers.world;
+    const int within = tile % per_shard;
+    *mb2 = shard * pairs_per_rank + within % pairs_per_rank;
+    *nb = within / pairs_per_rank;
   }
   __device__ static bool before_load(const Params& p, const Problem&, int mb, uint64_t deadline,
                                      const volatile uint32_t* abort_flag) {

@@ -333,6 +333,12 @@ struct StorePolicy : PolicyDefaults {
     *mb = tile % g.tiles_m;
     *nb = tile / g.tiles_m;
   }
+  // The paired kernel's order: pairs of row blocks, M-fastest.
+  __device__ static void pair_coords(const Params&, const Problem& g, int tile, int* mb2, int* nb) {
+    const int pairs_m = (g.tiles_m + 1) / 2;
+    *mb2 = tile % pairs_m;
+    *nb = tile / pairs_m;
+  }
   __device__ static bool before_load(const Params&, const Problem&, int, uint64_t, const volatile uint32_t*) {
     return true;
   }

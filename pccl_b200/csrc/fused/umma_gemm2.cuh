@@ -117,7 +117,15 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   const volatile uint32_t* abort_flag = g.error;
   const uint64_t deadline = ptx::globaltimer() + g.timeout_ns;
   const int half = static_cast<int>(ptx2::cluster_ctarank());      // 0 = even CTA (issues the MMAs)
-  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+  // Auxiliary CTAs (an even number: whole clusters) take no part in the GEMM pipeline or its
+  // cluster barriers.
+  const int aux = Policy::aux_ctas(p);
+  if (static_cast<int>(blockIdx.x) < aux) {
+    Policy::aux_main(p, g, blockIdx.x, aux, deadline, abort_flag, smem);
+    return;
+  }
+  const int pair = (blockIdx.x - aux) >> 1, num_pairs = (gridDim.x - aux) >> 1;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages2; ++s) { ptx::mbar_init(&pipe.full[s], 2); ptx::mbar_init(&pipe.empty[s], 1); }
@@ -139,11 +147,9 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = pipe.tmem_base;
 
-  // The pair walks the policy's tile order over 256-row blocks: block pair i = 128-row blocks 2i, 2i+1.
-  Problem g2 = g;
-  g2.tiles_m = (g.tiles_m + 1) / 2;
+  // The pair walks the policy's order of 256-row blocks: block pair i = 128-row blocks 2i, 2i+1.
   const int tiles_m = Policy::prepare(p, g, deadline, abort_flag);
-  const int num_tiles = tiles_m < 0 ? 0 : g2.tiles_m * g.tiles_n;
+  const int num_tiles = tiles_m < 0 ? 0 : (g.tiles_m + 1) / 2 * g.tiles_n;
   const int k_blocks = (g.K + kBK - 1) / kBK;
   bool failed = false;
 
@@ -153,7 +159,7 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       uint32_t stage = 0, phase = 0;
       for (int tile = pair; tile < num_tiles && !failed; tile += num_pairs) {
         int mb2, nb;
-        Policy::tile_coords(p, g2, tile, &mb2, &nb);
+        Policy::pair_coords(p, g, tile, &mb2, &nb);
         const int mb = 2 * mb2 + half;
         if (!Policy::before_load(p, g, mb, deadline, abort_flag)) { raise_error(g, kErrPolicyWait, 0); failed = true; break; }
         for (int kb = 0; kb < k_blocks; ++kb) {
@@ -217,7 +223,7 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         if (!ok) break;
         __threadfence_block();
         int mb2, nb;
-        Policy::tile_coords(p, g2, tile, &mb2, &nb);
+        Policy::pair_coords(p, g, tile, &mb2, &nb);
         if (2 * mb2 + half < g.tiles_m) Policy::tile_done(p, g, 2 * mb2 + half, nb);
       }
     }
@@ -228,7 +234,7 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     for (int tile = pair; tile < num_tiles; tile += num_pairs, ++local_tile) {
       const uint32_t acc = local_tile & 1u, acc_phase = (local_tile >> 1) & 1u;
       int mb2, nb;
-      Policy::tile_coords(p, g2, tile, &mb2, &nb);
+      Policy::pair_coords(p, g, tile, &mb2, &nb);
       const int mb = 2 * mb2 + half;
       uint32_t ok = 1;
       if (lane == 0) ok = ptx::mbar_wait(&pipe.acc_full[acc], acc_phase, deadline, abort_flag) ? 1u : 0u;
@@ -308,7 +314,7 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     ptx::tc_fence_after_sync();
     ptx2::tmem_dealloc_pair(tmem_base, kTmemCols);
   }
-  Policy::finish(p, g, blockIdx.x, gridDim.x, deadline, abort_flag);
+  Policy::finish(p, g, blockIdx.x - aux, gridDim.x - aux, deadline, abort_flag);
 }
 
 }  // namespace gemm

@@ -108,12 +108,13 @@ class GpuProfile:
 
 H100_PROFILE = GpuProfile(name="h100")
 
-# B200: per-executor figures are what ONE channel (a group of CTAs) sustains.
-# SM ld/st over NVSwitch reaches the measured peer-copy rate with ~16-32 CTAs;
-# "tma" plans execute on the SM path here (TMA never touches peer memory), so
-# they are priced identically.  multimem moves N ranks' worth of data per byte
-# that crosses this GPU's links.
-_B200_BW = {"sm": 700.0, "tma": 700.0, "ce": 740.0, "rdma": 50.0, "multimem": 1500.0, "host": 25.0}
+# B200, calibrated on 512 MB fp32 all-reduces (GB/s per NVLink direction actually sustained):
+# two-shot moves 2 (W-1)/W of the message per direction in 0.859 ms on 2 GPUs and 1.527 ms on 8,
+# i.e. 615-625 GB/s through SM peer loads ("tma" plans execute on the same SM path: TMA never
+# touches peer memory); the one-pass in-switch all-reduce moves (W+1)/W of it in 1.355 ms on
+# 2 GPUs, i.e. 594 GB/s through multimem.  `plan_cost` multiplies a multimem step's slice by the
+# number of slices that cross this GPU's links while every rank runs that step.
+_B200_BW = {"sm": 620.0, "tma": 620.0, "ce": 740.0, "rdma": 50.0, "multimem": 590.0, "host": 25.0}
 B200_PROFILE = GpuProfile(
     name="b200",
     launch_overhead_us=0.6,
@@ -299,7 +300,11 @@ def plan_cost(graph, profile: GpuProfile, topology: TopologyProfile, elem_bytes:
             rate = profile.bandwidth_gb_s.get(key, _DEFAULT_BW)
             extra = 0.0
             if key == "multimem":
-                amount *= max(1, world_size)
+                # Slices on this GPU's busier link direction while all ranks run the step: a reduce
+                # sends this rank's copy of all W slices, a store receives all W, the fused
+                # all-reduce does both at once plus its own slice each way.
+                amount *= max(1, world_size) + (1 if op == PrimitiveOpType.MULTIMEM_ALLREDUCE else 0)
+                rate = min(rate, link)
                 # A multimem access is answered by the switch after it has gathered (or delivered)
                 # every rank's copy: two more fabric hops than a peer load before the first byte.
                 extra = 2.0 * topology.latency_us if topology is not None else 0.0

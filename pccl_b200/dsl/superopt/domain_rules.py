@@ -2,10 +2,10 @@
 
 A. *Executor equivalences*: primitives that differ only in which engine moves
    the bytes are interchangeable; for every such e-node the alternatives are
-   added to its e-class up front.  On top of the reference's families
-   (reference: pccl/dsl/superopt/domain_rules.py:19-57) the B200 build lets the
-   copy family include ``multimem.store`` **only** when the fabric reduces
-   in-switch, because a pull copy of a slice every rank needs is a broadcast.
+   added to its e-class up front.  The families are the reference's
+   (reference: pccl/dsl/superopt/domain_rules.py:19-57): the multimem primitives stand alone here,
+   because turning pulls into an in-switch broadcast or a run of reduces into an in-switch
+   reduction changes several nodes at once; those rewrites live in ``fabric_rules.py``.
 B. *Structural rules*: ``op(op(x, P), P) -> op(x, P)`` for idempotent
    re-application of the same primitive with identical parameters.
 C. *Adapter for cached SMT-verified rules*: single-node rules become executor

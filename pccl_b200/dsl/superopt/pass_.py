@@ -8,6 +8,9 @@
    with structural + cached SMT rules, extract the cheapest DAG under the
    device/topology cost model, and replace the graph's nodes
    (reference: pccl/dsl/superopt/pass_.py:52-159).
+3. *Fabric rules* (switched fabrics only): runs of nodes are rewritten to multi-source
+   reduces and to in-switch (multimem) reduction / broadcast where the cost model says the
+   whole plan gets cheaper (`fabric_rules.py`).
 """
 
 from __future__ import annotations
@@ -43,6 +46,7 @@ class SuperoptPass:
                 "split the graph into OCS phases first")
         self._apply_executor_upgrades(graph)
         self._apply_egraph_optimization(graph)
+        self._apply_fabric_rules(graph)
         return graph
 
     # -- phase 1 ---------------------------------------------------------------
@@ -66,6 +70,14 @@ class SuperoptPass:
         twin.channel = node.channel
         twin.tensor_info = node.tensor_info
         return twin
+
+    # -- phase 3 ---------------------------------------------------------------
+    def _apply_fabric_rules(self, graph: PrimitiveIRGraph) -> bool:
+        """Structural retargeting to a switched fabric (multi-source reduces, in-switch reduction
+        and broadcast), each rewrite kept only if it lowers the plan's price."""
+        from .fabric_rules import apply_fabric_rules
+        self.fabric_rewrites = apply_fabric_rules(graph, self.profile, self.topology)
+        return bool(self.fabric_rewrites)
 
     # -- phase 2 ---------------------------------------------------------------
     def _apply_egraph_optimization(self, graph: PrimitiveIRGraph) -> bool:

@@ -1,6 +1,7 @@
 """Cost model, e-graph, rule model/cache, enumerator, verifier, the pass, selector."""
 
 import pytest
+import torch
 
 from pccl_b200.dsl import nodes as N
 from pccl_b200.dsl.algorithms import (NvlsAllreduce, OneShotAllreduce, RecursiveHalvingDoubling,
@@ -189,3 +190,87 @@ def test_cost_based_selector_prefers_few_steps_for_small_and_bandwidth_for_large
     assert small.name == "oneshot"
     assert large.name in ("nvls", "twoshot") and large.bandwidth_optimal
     assert select_algorithm_cost_based(0, 6, 600, 2400).name == "ring"
+
+
+# ---- structural rewrites for a switched fabric --------------------------------------------------
+
+def _compile_with(graph, topology, size_hint=0):
+    from pccl_b200 import Compiler
+    return Compiler(enable_superopt=True, gpu_profile="b200", topology=topology,
+                    data_size_hint=size_hint).compile_to_dict(graph)
+
+
+def test_chain_of_reduces_becomes_one_multi_source_reduce():
+    from pccl_b200.dsl.decorators import build_graph
+    from pccl_b200.runtime import simulate
+    world, n = 4, 256
+
+    def plans(topology):
+        out = []
+        for rank in range(world):
+            def build(op, rank=rank):
+                from pccl_b200.dsl.algorithms.base import all_pairs_barrier
+                op.tensor("float32", (n,))
+                piece = n // world
+                mine = rank * piece
+                all_pairs_barrier(op, rank, world, 200)
+                for i in range(1, world):
+                    op.sm_reduce(source_rank=(rank + i) % world, src_offset=mine, dst_offset=mine,
+                                 remote_offset=mine, count=piece)
+                all_pairs_barrier(op, rank, world, 300)
+            graph = build_graph(f"chain{rank}", build)
+            graph.collective_type = "reduce_scatter"
+            out.append(_compile_with(graph, topology))
+        return out
+
+    switched = TopologyProfile("nvlink5", 900.0, 0.7, uniform_all_to_all=True)
+    fused = plans(switched)
+    kinds = [op["primitive"] for op in fused[0]["operations"] if "reduce" in op["primitive"]]
+    assert kinds == ["sm.reduce_multi"]
+    assert sorted(next(op for op in fused[0]["operations"] if op["primitive"] == "sm.reduce_multi")
+                  ["params"]["source_ranks"]) == [0, 1, 2, 3]
+    xs = [torch.randn(n, generator=torch.Generator().manual_seed(r)) for r in range(world)]
+    total = sum(x.double() for x in xs)
+    for r, out in enumerate(simulate(fused, xs)):
+        torch.testing.assert_close(out.double(), total[r * n // world:(r + 1) * n // world], atol=1e-5, rtol=1e-5)
+    # A point-to-point fabric keeps the chain.
+    kept = plans(NVLINK_TOPOLOGY)
+    assert sum("reduce" in op["primitive"] for op in kept[0]["operations"]) == world - 1
+
+
+@pytest.mark.parametrize("world", [4, 8])
+def test_two_shot_becomes_in_switch_allreduce_when_the_fabric_reduces(world):
+    from pccl_b200.dsl.algorithms import TwoShotAllreduce
+    from pccl_b200.runtime import simulate
+    n = world * 64 * 1024
+    plans = [_compile_with(TwoShotAllreduce().build_allreduce(r, world, n, "float32", "sm", 2), NVLINK5_TOPOLOGY)
+             for r in range(world)]
+    kinds = {op["primitive"] for op in plans[0]["operations"]}
+    assert "multimem.allreduce" in kinds and not kinds & {"sm.reduce_multi", "sm.copy", "tma.copy", "ce.copy"}
+    # one barrier fewer per channel than the two-shot plan it came from
+    before = TwoShotAllreduce().build_allreduce(0, world, n, "float32", "sm", 2)
+    assert sum(op["primitive"] == "notify" for op in plans[0]["operations"]) == \
+        sum(1 for node in before.nodes.values() if node.op_type.value == "notify") - 2 * (world - 1)
+    xs = [torch.randn(n, generator=torch.Generator().manual_seed(r)) for r in range(world)]
+    outs, sim = simulate(plans, xs, return_world=True)
+    for out in outs:
+        torch.testing.assert_close(out.double(), sum(x.double() for x in xs), atol=1e-4, rtol=1e-5)
+    assert sim.leftover_signals() == {}
+
+
+def test_two_shot_stays_on_peer_loads_where_the_switch_does_not_pay():
+    from pccl_b200.dsl.algorithms import TwoShotAllreduce
+    no_nvls = TopologyProfile("nvlink5", 900.0, 0.7, uniform_all_to_all=True)
+    n = 8 * 64 * 1024
+    kinds = {op["primitive"] for op in _compile_with(TwoShotAllreduce().build_allreduce(0, 8, n, "float32", "sm", 1),
+                                                     no_nvls)["operations"]}
+    assert "sm.reduce_multi" in kinds and not any(k.startswith("multimem") for k in kinds)
+    # Two ranks: the in-switch path moves 1.5x the bytes of two-shot, so the price goes up and it is not taken.
+    n = 2 * 1024 * 1024
+    kinds = {op["primitive"] for op in _compile_with(TwoShotAllreduce().build_allreduce(0, 2, n, "float32", "sm", 1),
+                                                     NVLINK5_TOPOLOGY)["operations"]}
+    assert not any(k.startswith("multimem") for k in kinds)
+    # fp8 has no in-switch arithmetic: the reduction stays on the SMs (the broadcast half may still move).
+    kinds = {op["primitive"] for op in _compile_with(TwoShotAllreduce().build_allreduce(0, 8, n, "float8_e4m3", "sm", 1),
+                                                     NVLINK5_TOPOLOGY)["operations"]}
+    assert "sm.reduce_multi" in kinds and not kinds & {"multimem.reduce", "multimem.allreduce"}
