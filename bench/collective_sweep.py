@@ -13,7 +13,10 @@ Single GPU (N virtual ranks in one cooperative launch, peer traffic through HBM)
 Per (collective, dtype, size, algorithm, channels) one JSON line: device time (CUDA events around
 `--iters` back-to-back calls, max over ranks), algorithm and bus bandwidth
 (bus = alg * 2(N-1)/N for all-reduce, alg * (N-1)/N otherwise), the NCCL time for the same call
-(defaults, NVLS allowed, no clone in the timed region), and the ratio.  Messages smaller than
+(defaults, NVLS allowed, no clone in the timed region), and the ratio.  `--check` verifies every
+all-reduce configuration first (float64 host sum of randn(seed=rank) inputs up to --check-bytes,
+NCCL above), `--out` keeps all rows as JSON, `--write-tuning` merges the winners per size into the
+tuning file that `select_algorithm` and `pccl_b200.parallel` read.  Messages smaller than
 the 126 MB L2 are timed L2-warm (like NCCL's own tests); the JSON says so.
 The reference's sweep is tests/bench_algo_comparison.py (rank-0 timing, host sync per call).
 """
@@ -75,6 +78,31 @@ def run_multi(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t)
 
+    rows = []
+
+    def allreduce_error(call, full, numel, dtype):
+        """max |result - float64 host sum of every rank's randn(seed=rank)| for messages up to
+        --check-bytes (every rank regenerates all inputs on the host); larger ones are compared with
+        NCCL's all-reduce of the same input on the device.  Max over ranks."""
+        esize = torch.empty((), dtype=dtype).element_size()
+        if numel * esize <= args.check_bytes:
+            parts = [torch.randn(numel, generator=torch.Generator().manual_seed(r)).to(dtype) for r in range(world)]
+            full.copy_(parts[rank])
+            ref = sum(p.double() for p in parts)
+            call()
+            torch.cuda.synchronize()
+            err = float((full.double().cpu() - ref).abs().max() / ref.abs().max().clamp_min(1e-30))
+        else:
+            full.normal_()
+            ref = full.clone()
+            dist.all_reduce(ref)
+            call()
+            torch.cuda.synchronize()
+            err = float(((full.float() - ref.float()).abs().max() / ref.float().abs().max().clamp_min(1e-30)))
+        t = torch.tensor([err], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
     for kind in args.collectives:
         for dname in args.dtypes:
             dtype = DTYPES[dname]
@@ -101,7 +129,8 @@ def run_multi(args):
 
                 nccl_ms = reduce_max(timed_loop(nccl_call, iters, torch.cuda.synchronize, dist.barrier))
                 for algo in args.algos:
-                    allowed = {"allreduce": ("auto", "ll", "push", "ring", "rhd", "tree", "oneshot", "twoshot", "nvls"),
+                    allowed = {"allreduce": ("auto", "ll", "push", "ring", "rhd", "tree", "oneshot", "twoshot", "nvls",
+                                             "nvls_twopass", "hybrid"),
                                "allgather": ("auto", "push", "ring", "rhd", "twoshot", "nvls"),
                                "reduce_scatter": ("auto", "push", "ring", "rhd", "twoshot", "nvls"),
                                "alltoall": ("auto", "push", "ring", "twoshot")}[kind]
@@ -147,6 +176,9 @@ def run_multi(args):
                             if rank == 0:
                                 print(json.dumps({"collective": kind, "algo": algo, "bytes": nbytes, "skipped": str(err)[:120]}))
                             continue
+                        rel_err = None
+                        if kind == "allreduce" and args.check:
+                            rel_err = allreduce_error(call, full, numel, dtype)
                         ms = reduce_max(timed_loop(call, iters, lambda: pp.synchronize(name), dist.barrier))
                         if rank == 0:
                             _, real_algo, real_ch = pp.registered_plans()[name]
@@ -155,16 +187,67 @@ def run_multi(args):
                             elif uses_push:
                                 real_algo, real_ch = "push", 0
                             alg = numel * esize / (ms * 1e-3) / 1e9
-                            print(json.dumps({
+                            row = {
                                 "collective": kind, "dtype": dname, "bytes": numel * esize, "world": world,
                                 "algo": real_algo, "requested": algo, "channels": real_ch,
                                 "nvls": bool(engine.nvls_active()), "us": round(ms * 1e3, 2),
                                 "algbw_gbs": round(alg, 2), "busbw_gbs": round(alg * bus_factor(kind, world), 2),
                                 "nccl_us": round(nccl_ms * 1e3, 2), "vs_nccl": round(nccl_ms / ms, 3),
                                 "l2": "cold (message > L2)" if numel * esize > (126 << 20) else "warm",
-                                "in_place": kind != "alltoall"}), flush=True)
+                                "in_place": kind != "alltoall"}
+                            if rel_err is not None:
+                                row["max_rel_err"] = rel_err
+                                row["checked_against"] = "float64 host sum" if numel * esize <= args.check_bytes \
+                                    else "NCCL all-reduce of the same input"
+                            rows.append(row)
+                            print(json.dumps(row), flush=True)
+    if rank == 0:
+        if args.out:
+            with open(args.out, "w") as handle:
+                json.dump({"world": world, "iters": args.iters, "rows": rows}, handle, indent=1)
+        if args.write_tuning:
+            write_tuning(args.write_tuning, world, rows)
     dist.barrier()
     dist.destroy_process_group()
+
+
+def write_tuning(path, world, rows):
+    """Merge this sweep's winners into the tuning file: per collective, break points
+    [{"max_bytes", "algorithm", "channels", "us"}] where consecutive sizes with the same winner are
+    merged and the last entry is open-ended.  Only sizes that were measured with at least two
+    algorithms count (a lone "auto" row says nothing about the alternatives)."""
+    try:
+        with open(path) as handle:
+            doc = json.load(handle)
+    except (OSError, ValueError):
+        doc = {}
+    doc.setdefault("routes", {})
+    for kind in sorted({r["collective"] for r in rows}):
+        by_size = {}
+        for r in rows:
+            if r["collective"] != kind or r.get("requested") == "auto":
+                continue
+            by_size.setdefault(r["bytes"], []).append(r)
+        table = []
+        for nbytes in sorted(by_size):
+            cands = by_size[nbytes]
+            if len(cands) < 2:
+                continue
+            best = min(cands, key=lambda r: r["us"])
+            entry = {"max_bytes": nbytes, "algorithm": best["algo"], "us": best["us"]}
+            if best["channels"]:
+                entry["channels"] = best["channels"]
+            if table and table[-1]["algorithm"] == entry["algorithm"] and table[-1].get("channels") == entry.get("channels"):
+                table[-1].update(max_bytes=nbytes, us=best["us"])
+            else:
+                table.append(entry)
+        if table:
+            table[-1]["max_bytes"] = None
+            doc["routes"].setdefault(kind, {})[str(world)] = table
+    doc["source"] = "bench/collective_sweep.py --write-tuning"
+    os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+    with open(path, "w") as handle:
+        json.dump(doc, handle, indent=1)
 
 
 def run_virtual(args):
@@ -218,12 +301,19 @@ def main():
     ap.add_argument("--channels", default="auto")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--virtual-ranks", type=int, default=0)
+    ap.add_argument("--out", default=None, help="write every row to this JSON file (rank 0)")
+    ap.add_argument("--write-tuning", default=None,
+                    help="merge the fastest algorithm per size into this tuning file (the selector reads it)")
+    ap.add_argument("--check", action="store_true", help="verify every all-reduce configuration before timing it")
+    ap.add_argument("--check-bytes", default="16M",
+                    help="up to this size the check is against a float64 host sum, above it against NCCL")
     args = ap.parse_args()
     args.collectives = args.collectives.split(",")
     args.dtypes = args.dtypes.split(",")
     args.algos = args.algos.split(",")
     args.channels = args.channels.split(",")
     args.min_bytes, args.max_bytes = parse_size(args.min_bytes), parse_size(args.max_bytes)
+    args.check_bytes = parse_size(args.check_bytes)
     if args.virtual_ranks:
         run_virtual(args)
     else:

@@ -30,30 +30,74 @@ from .tree import TreeAllreduce
 
 _is_power_of_2 = is_power_of_two
 
-#: message-size crossovers (bytes) on a switched fabric, by world size:
-#: (one-shot up to, in-switch reduction from, in-switch reduction up to); two-shot elsewhere.
-#: Measured on B200 / NVLink 5: with two ranks NVLS moves 1.5x the bytes of two-shot and never wins;
-#: with four it wins between a few MB and a few tens of MB; eight is set from the byte counts
-#: (1.125 n against 1.75 n per direction).
+#: message-size crossovers (bytes) on a switched fabric, by world size, used when no tuning file
+#: covers the world size: (one-shot up to, in-switch reduction from, in-switch reduction up to);
+#: two-shot elsewhere.  With two ranks the in-switch all-reduce moves 1.5x the bytes of two-shot
+#: per link direction and never wins; from four ranks on it moves fewer ((W+1)/W against 2(W-1)/W
+#: of the message) and wins wherever bandwidth matters.
 _NEVER = 1 << 62
 SWITCHED_CROSSOVERS: Dict[int, tuple] = {
     2: (4 * 1024 * 1024, _NEVER, _NEVER),
-    4: (2 * 1024 * 1024, 2 * 1024 * 1024, 32 * 1024 * 1024),
+    4: (2 * 1024 * 1024, 2 * 1024 * 1024, _NEVER),
     8: (128 * 1024, 4 * 1024 * 1024, _NEVER),
 }
 
 
+_PACKAGED_TUNING = os.path.join(os.path.dirname(os.path.abspath(__file__)), "tuning_b200.json")
+_tuning_cache: Dict[str, dict] = {}
+
+
+def tuning_path(path: Optional[str] = None) -> str:
+    """Where measured choices are read from: the argument, ``PCCL_TUNING_FILE``,
+    ``~/.pccl/tuning_b200.json`` if it exists, else the table shipped with the package
+    (written by ``bench/collective_sweep.py --write-tuning`` on 8 x B200)."""
+    if path:
+        return path
+    env = os.environ.get("PCCL_TUNING_FILE")
+    if env:
+        return env
+    home = os.path.expanduser("~/.pccl/tuning_b200.json")
+    return home if os.path.exists(home) else _PACKAGED_TUNING
+
+
+def load_tuning(path: Optional[str] = None) -> dict:
+    """The tuning document (cached per path); ``{}`` when there is none or it is unreadable."""
+    path = tuning_path(path)
+    if path not in _tuning_cache:
+        try:
+            with open(path) as handle:
+                _tuning_cache[path] = json.load(handle)
+        except (OSError, ValueError):
+            _tuning_cache[path] = {}
+    return _tuning_cache[path]
+
+
+def clear_tuning_cache() -> None:
+    _tuning_cache.clear()
+
+
+def tuned_route(kind: str, world_size: int, data_bytes: int, path: Optional[str] = None) -> Optional[dict]:
+    """The measured best way to run ``kind`` at this world size and message size, or ``None``.
+
+    The tuning file holds, per collective and world size, break points sorted by size:
+    ``{"routes": {"allreduce": {"8": [{"max_bytes": 524288, "algorithm": "ll"}, {"max_bytes": 33554432,
+    "algorithm": "push"}, {"max_bytes": null, "algorithm": "nvls", "channels": 16}]}}}``; the first
+    entry whose ``max_bytes`` covers the message applies (``null`` = no upper bound)."""
+    table = load_tuning(path).get("routes", {}).get(kind, {}).get(str(world_size))
+    if not table:
+        return None
+    for entry in table:
+        limit = entry.get("max_bytes")
+        if limit is None or data_bytes <= limit:
+            return entry
+    return table[-1]
+
+
 def load_tuned_crossovers(path: Optional[str] = None) -> Dict[int, tuple]:
-    """Crossovers measured by the sweep benchmark, if a tuning file exists
-    (``PCCL_TUNING_FILE`` or ``~/.pccl/tuning_b200.json``), else the built-in table."""
-    path = path or os.environ.get("PCCL_TUNING_FILE") or os.path.expanduser("~/.pccl/tuning_b200.json")
-    try:
-        with open(path) as handle:
-            raw = json.load(handle)
-        return {int(k): tuple(v) for k, v in raw.get("allreduce_crossovers", {}).items()} \
-            or SWITCHED_CROSSOVERS
-    except (OSError, ValueError):
-        return SWITCHED_CROSSOVERS
+    """All-reduce crossovers ``{world: (one-shot up to, in-switch from, in-switch up to)}`` from the
+    tuning file's ``allreduce_crossovers``, else the built-in table."""
+    raw = load_tuning(path)
+    return {int(k): tuple(v) for k, v in raw.get("allreduce_crossovers", {}).items()} or SWITCHED_CROSSOVERS
 
 
 def select_algorithm(world_size: int, data_bytes: int,
@@ -66,6 +110,12 @@ def select_algorithm(world_size: int, data_bytes: int,
             return ALGORITHMS[forced]()
 
     if getattr(topology, "uniform_all_to_all", False):
+        from . import ALGORITHMS
+        route = tuned_route("allreduce", world_size, data_bytes)
+        if route is not None and route.get("plan_algorithm", route.get("algorithm")) in ALGORITHMS:
+            name = route.get("plan_algorithm", route["algorithm"])
+            if name not in ("nvls", "hybrid", "nvls_twopass") or topology.in_switch_reduction:
+                return ALGORITHMS[name]()
         table = load_tuned_crossovers()
         nearest = min(table, key=lambda w: abs(w - world_size))
         entry = tuple(table[nearest])

@@ -25,6 +25,7 @@ import torch.distributed as dist
 
 from .. import engine as _engine
 from ..dsl.algorithms import ALGORITHMS, select_algorithm
+from ..dsl.algorithms.selector import tuned_route
 from ..dsl.compiler import Compiler
 from ..dsl.superopt.cost_model import B200_PROFILE, NVLINK5_TOPOLOGY, TopologyProfile
 
@@ -266,6 +267,19 @@ def all_reduce(tensor: torch.Tensor, op: str = "sum", algorithm: Optional[str] =
     and sums of up to ``PUSH_MAX_BYTES`` through the fused push kernel (both: no plan, no staging copy,
     asynchronous on the current stream); everything else runs as a plan.
     """
+    if algorithm is None and op == "sum" and os.environ.get("PCCL_ALGO") is None:
+        # A measured table, when one covers this world size, says which path wins at this size
+        # (same file on every rank, so every rank takes the same path).
+        route = tuned_route("allreduce", _state["world"], tensor.numel() * tensor.element_size())
+        if route is not None:
+            choice = route["algorithm"]
+            if choice == "ll" and _ll_eligible(tensor, op, "ll"):
+                algorithm = "ll"
+            elif choice == "push" and _push_eligible(tensor, op, "push"):
+                algorithm = "push"
+            elif choice in ALGORITHMS:
+                algorithm = choice
+                channels = channels or route.get("channels")
     if _ll_eligible(tensor, op, algorithm):
         ll = _state["ll"]
         ll["epoch"] += 1

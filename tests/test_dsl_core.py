@@ -187,3 +187,43 @@ def test_trace_summary_reports_phase_rates():
     w = waits(trace)
     assert w["chains"] == 2 and abs(w["total_us"] - 103.5) < 1e-6
     assert "multimem.allreduce" in summarize(trace, 8)
+
+
+def test_selector_follows_a_tuning_file(tmp_path, monkeypatch):
+    """`collective_sweep --write-tuning` output drives select_algorithm and the route lookup."""
+    import importlib.util
+    import json
+    import os
+    from pccl_b200.dsl.algorithms import selector
+    from pccl_b200.dsl.superopt.cost_model import B200_PROFILE, NVLINK5_TOPOLOGY
+    spec = importlib.util.spec_from_file_location(
+        "collective_sweep", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench",
+                                         "collective_sweep.py"))
+    sweep = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(sweep)
+    rows = []
+    for size, (ll, two, nvls) in {4096: (5, 9, 12), 1 << 20: (30, 25, 28), 1 << 24: (200, 150, 120),
+                                  1 << 29: (3000, 1500, 1000)}.items():
+        for algo, us in (("ll", ll), ("twoshot", two), ("nvls", nvls)):
+            rows.append({"collective": "allreduce", "bytes": size, "algo": algo, "requested": algo,
+                         "channels": 0 if algo == "ll" else 16, "us": us})
+    path = tmp_path / "tuning.json"
+    sweep.write_tuning(str(path), 8, rows)
+    sweep.write_tuning(str(path), 4, [dict(r, us=r["us"] + (600 if r["algo"] == "nvls" else 0)) for r in rows])
+    doc = json.loads(path.read_text())
+    assert [e["algorithm"] for e in doc["routes"]["allreduce"]["8"]] == ["ll", "twoshot", "nvls"]
+    assert doc["routes"]["allreduce"]["8"][-1]["max_bytes"] is None and "4" in doc["routes"]["allreduce"]
+    monkeypatch.setenv("PCCL_TUNING_FILE", str(path))
+    monkeypatch.delenv("PCCL_ALGO", raising=False)
+    selector.clear_tuning_cache()
+    try:
+        assert selector.tuned_route("allreduce", 8, 1000)["algorithm"] == "ll"
+        assert selector.tuned_route("allreduce", 8, 1 << 30)["algorithm"] == "nvls"
+        assert selector.tuned_route("allreduce", 2, 1 << 20) is None
+        # every swept size: the selector's plan algorithm is the measured winner among the plan algorithms
+        for size in (1 << 20, 1 << 24, 1 << 29):
+            best = min((r for r in rows if r["bytes"] == size and r["algo"] != "ll"), key=lambda r: r["us"])["algo"]
+            assert selector.select_algorithm(8, size, NVLINK5_TOPOLOGY, B200_PROFILE).name == best
+        assert selector.select_algorithm(4, 1 << 29, NVLINK5_TOPOLOGY, B200_PROFILE).name == "twoshot"
+    finally:
+        selector.clear_tuning_cache()
