@@ -39,7 +39,9 @@ OPTIONS: Dict[str, tuple] = {
     "PCCL_WAIT_TIMEOUT_MS": ("wait_timeout_ms", int, 10000, "time budget of device-side waits per launch"),
     "PCCL_NVLS_ENABLE": ("nvls_enable", _flag, True, "use NVLS multicast when every rank supports it"),
     "PCCL_DISABLE_NVLS": ("disable_nvls", _flag, False, "turn NVLS off"),
-    "PCCL_ALGO": ("algo", str, None, "force ring|rhd|tree|oneshot|twoshot|nvls"),
+    "PCCL_ALGO": ("algo", str, None, "force ring|rhd|tree|oneshot|twoshot|nvls|nvls_twopass|hybrid"),
+    "PCCL_NVLS_FRACTION": ("nvls_fraction", float, 0.7,
+                           "hybrid all-reduce: share of the message reduced in the switch, the rest goes two-shot"),
     "PCCL_CHANNELS": ("channels", int, None, "force the channel count of generated plans"),
     "PCCL_EXECUTOR": ("executor", str, None, "sm (default) | ce (copy engine) | cpu (gloo replay)"),
     "PCCL_LL_MAX_BYTES": ("ll_max_bytes", _size, 256 << 10,
@@ -50,7 +52,20 @@ OPTIONS: Dict[str, tuple] = {
     "PCCL_CLOSING_BARRIER": ("closing_barrier", _flag, True,
                              "append an all-pairs barrier to pull-style plans (ring, rhd, tree, hand-built)"),
     "PCCL_RDMA": ("rdma", _flag, False, "build option: compile the verbs transport of the RDMA executor"),
-    "PCCL_TUNING_FILE": ("tuning_file", str, None, "JSON with measured algorithm crossovers"),
+    "PCCL_TUNING_FILE": ("tuning_file", str, None,
+                         "JSON of measured routes per collective, world size and message size "
+                         "(bench/collective_sweep.py --write-tuning)"),
+    "PCCL_PLAN_CACHE": ("plan_cache", str, "~/.pccl/plans", "directory of compiled plans (off = compile every time)"),
+    "PCCL_VALIDATE": ("validate", _flag, True,
+                      "check all ranks' plans together (deadlock, leftover signals) when a plan is first compiled"),
+    "PCCL_TRACE": ("trace", _flag, False, "stamp %globaltimer per plan step; read with Engine.trace(name)"),
+    "PCCL_COOPERATIVE": ("cooperative", _flag, True,
+                         "launch kernels whose CTAs wait on one another cooperatively (all CTAs resident)"),
+    "PCCL_PUSH_MAX_BYTES": ("push_max_bytes", _size, 32 << 20,
+                            "largest message taken by the fused push collectives (0 = never)"),
+    "PCCL_GEMM_SMS_PER_TILE": ("gemm_sms_per_tile", int, 2,
+                               "2 = pairs of SMs on 256x256 tiles (tcgen05.mma.cta_group::2), 1 = one SM per 128x256 tile"),
+    "PCCL_GEMM_TILE_N": ("gemm_tile_n", int, 0, "tile width of the paired GEMM (multiple of 32; 0 = 256)"),
     "PCCL_LOG_LEVEL": ("log_level", str, "WARN", "TRACE|DEBUG|INFO|WARN|ERROR|CRITICAL"),
     "PCCL_JOB_ID": ("job_id", str, None, "namespace of the fd-passing sockets"),
     "PCCL_DEBUG_ENDPOINT_INIT": ("debug_endpoint_init", _flag, False, "print bootstrap stages"),
@@ -70,6 +85,7 @@ class PcclConfig:
     nvls_enable: bool = True
     disable_nvls: bool = False
     algo: Optional[str] = None
+    nvls_fraction: float = 0.7
     channels: Optional[int] = None
     executor: Optional[str] = None
     ll_max_bytes: int = 256 << 10
@@ -78,6 +94,13 @@ class PcclConfig:
     closing_barrier: bool = True
     rdma: bool = False
     tuning_file: Optional[str] = None
+    plan_cache: str = "~/.pccl/plans"
+    validate: bool = True
+    trace: bool = False
+    cooperative: bool = True
+    push_max_bytes: int = 32 << 20
+    gemm_sms_per_tile: int = 2
+    gemm_tile_n: int = 0
     log_level: str = "WARN"
     job_id: Optional[str] = None
     debug_endpoint_init: bool = False

@@ -71,17 +71,19 @@ void bind_fused_ops(py::module_& m) {
   // Fused all-gather -> GEMM; the gathered activations live in the symmetric heap at gathered_off.
   f.def("all_gather_gemm",
         [](int64_t gathered_off, int64_t m, int64_t k, const torch::Tensor& w, torch::Tensor& out, int64_t flags_off,
-           torch::Tensor& ready, int64_t epoch, int copy_ctas, int ctas) {
+           torch::Tensor& ready, int64_t epoch, int copy_ctas, int ctas, bool swiglu) {
           const gemm::MatrixDesc dw = as_matrix(w, "w");
           TORCH_CHECK(out.scalar_type() == torch::kBFloat16 && out.stride(1) == 1, "out must be row-major bf16");
+          TORCH_CHECK(out.size(0) == m && out.size(1) == (swiglu ? w.size(0) / 2 : w.size(0)),
+                      "out must be [M, N_local] (or [M, N_local / 2] with swiglu)");
           gemm::all_gather_gemm(peer_bases(), static_cast<uint64_t>(gathered_off), static_cast<int>(m),
                                 static_cast<int>(k), dw, static_cast<uint64_t>(flags_off),
                                 as_u32(ready, (m + 127) / 128, "ready"), out.data_ptr(), out.stride(0),
                                 static_cast<uint32_t>(epoch), c10::cuda::getCurrentCUDAStream().stream(), copy_ctas,
-                                ctas);
+                                ctas, 2000, swiglu);
         },
         py::arg("gathered_off"), py::arg("m"), py::arg("k"), py::arg("w"), py::arg("out"), py::arg("flags_off"),
-        py::arg("ready"), py::arg("epoch"), py::arg("copy_ctas") = 0, py::arg("ctas") = 0);
+        py::arg("ready"), py::arg("epoch"), py::arg("copy_ctas") = 0, py::arg("ctas") = 0, py::arg("swiglu") = false);
   // Fused all-reduce + residual + RMSNorm over symmetric buffers.
   f.def("ar_residual_rmsnorm",
         [](int64_t x_off, int64_t y_off, int64_t res_off, int64_t flags_off, const torch::Tensor& gamma,
@@ -231,6 +233,25 @@ void bind_fused_ops(py::module_& m) {
         py::arg("cta_counter"), py::arg("offsets"), py::arg("cap"), py::arg("epoch"),
         py::arg("local_heap") = py::none(), py::arg("ctas") = 0, py::arg("phases") = 7,
         py::arg("topk_idx") = py::none(), py::arg("topk_gate") = py::none());
+  // Gather a list of contiguous tensors into `bucket` at the given byte offsets (unpack: scatter back).
+  f.def("bucket_pack",
+        [](const std::vector<torch::Tensor>& tensors, const std::vector<int64_t>& offsets, torch::Tensor& bucket,
+           bool unpack) {
+          TORCH_CHECK(tensors.size() == offsets.size(), "one offset per tensor");
+          TORCH_CHECK(bucket.is_cuda() && bucket.is_contiguous(), "bucket must be a contiguous CUDA tensor");
+          std::vector<gemm::PackEntry> entries;
+          entries.reserve(tensors.size());
+          for (size_t i = 0; i < tensors.size(); ++i) {
+            const torch::Tensor& t = tensors[i];
+            TORCH_CHECK(t.is_cuda() && t.is_contiguous(), "bucket_pack: tensors must be contiguous CUDA tensors");
+            TORCH_CHECK(offsets[i] >= 0 && offsets[i] + static_cast<int64_t>(t.nbytes()) <= static_cast<int64_t>(bucket.nbytes()),
+                        "bucket_pack: tensor ", i, " does not fit the bucket at offset ", offsets[i]);
+            entries.push_back({t.data_ptr(), static_cast<uint64_t>(offsets[i]), static_cast<uint64_t>(t.nbytes())});
+          }
+          gemm::bucket_pack(entries.data(), static_cast<int>(entries.size()), bucket.data_ptr(), unpack,
+                            c10::cuda::getCurrentCUDAStream().stream());
+        },
+        py::arg("tensors"), py::arg("offsets"), py::arg("bucket"), py::arg("unpack") = false);
   // Device-side error word of the GEMM family (0 = ok); synchronises.
   f.def("read_error", &gemm::read_error);
   f.def("clear_error", &gemm::clear_error);

@@ -45,9 +45,12 @@ void gemm_reduce_scatter(const PeerBases& peers, const MatrixDesc& x, const Matr
 // rank ([M, K] bf16, M = world * rows_per_rank); each rank has written its own row shard there
 // before the call.  w[N_local, K] local bf16, out[M, N_local] local bf16.  flags_off: symmetric
 // u32[2 * world]; ready: local zero-initialised u32[M / 128].
+// swiglu: w stacks gate and up rows interleaved in groups of 16 and out is [M, N_local / 2] =
+// silu(gate) * up, computed in the epilogue.
 void all_gather_gemm(const PeerBases& peers, uint64_t gathered_off, int M, int K, const MatrixDesc& w,
                      uint64_t flags_off, uint32_t* ready, void* out, int64_t ldc, uint32_t epoch,
-                     cudaStream_t stream, int copy_ctas = 0, int ctas = 0, uint64_t timeout_ms = 2000);
+                     cudaStream_t stream, int copy_ctas = 0, int ctas = 0, uint64_t timeout_ms = 2000,
+                     bool swiglu = false);
 
 // Fused all-reduce + residual add + RMSNorm.  x, y and the residual h are [tokens][hidden] bf16
 // at the given symmetric-heap offsets on every rank; flags_off: symmetric u32[2 * world] (zeroed
@@ -80,6 +83,18 @@ void collective_push(PushMode mode, const PeerBases& peers, uint64_t area_off, u
                      uint64_t flags_off, uint32_t* counters, const void* in, void* out, uint64_t bytes, int dtype,
                      uint32_t epoch, cudaStream_t stream, int ctas, uint64_t timeout_ms = 2000,
                      uint32_t* error = nullptr);
+
+// ---- gradient buckets ------------------------------------------------------------------------------
+// Gather `count` tensors into one bucket (or scatter them back, unpack = true) with one launch per
+// kPackBatch tensors: the table travels in the kernel's parameters, no host-to-device copy.
+struct PackEntry {
+  void* tensor;             // device address of the tensor's first byte (contiguous)
+  uint64_t bucket_offset;   // bytes from the bucket's start
+  uint64_t bytes;
+};
+constexpr int kPackBatch = 128;
+struct PackBatch { PackEntry entry[kPackBatch]; };
+void bucket_pack(const PackEntry* entries, int count, void* bucket, bool unpack, cudaStream_t stream);
 
 // ---- expert-parallel MoE feed-forward (top-2 routing) ------------------------------------------------
 // Symmetric-heap offsets (identical on every rank) of the buffers the three kernels share.

@@ -224,7 +224,8 @@ void gemm_reduce_scatter(const PeerBases& peers, const MatrixDesc& x, const Matr
 
 void all_gather_gemm(const PeerBases& peers, uint64_t gathered_off, int M, int K, const MatrixDesc& w,
                      uint64_t flags_off, uint32_t* ready, void* out, int64_t ldc, uint32_t epoch,
-                     cudaStream_t stream, int copy_ctas, int ctas, uint64_t timeout_ms) {
+                     cudaStream_t stream, int copy_ctas, int ctas, uint64_t timeout_ms, bool swiglu) {
+  PCCL_CHECK(!swiglu || w.rows % 32 == 0, "AG->GEMM with SwiGLU: gate and up rows come in groups of 16 each");
   PCCL_CHECK(M % peers.world == 0 && (M / peers.world) % kBM == 0,
              "AG->GEMM: rows per rank must be a multiple of " << kBM);
   PCCL_CHECK(epoch >= 1, "AG->GEMM: epoch counts calls from 1");
@@ -262,10 +263,15 @@ void all_gather_gemm(const PeerBases& peers, uint64_t gathered_off, int M, int K
   p.epoch = epoch;
   MatrixDesc a{peers.base[peers.rank] + gathered_off, M, K, K};
   int grid = ctas > 0 ? ctas : sms;
-  if (Environs::get_int("PCCL_GEMM_SMS_PER_TILE", 2) == 2 && p.blocks_per_rank % 2 == 0 && p.copy_ctas % 2 == 0)
-    launch_pair<AllGatherPolicy>(a, w, p, grid, timeout_ms, stream, true, p.copy_ctas);
-  else
-    launch<AllGatherPolicy>(a, w, p, grid, timeout_ms, stream, p.copy_ctas);
+  const bool pair = Environs::get_int("PCCL_GEMM_SMS_PER_TILE", 2) == 2 && p.blocks_per_rank % 2 == 0 &&
+                    p.copy_ctas % 2 == 0;
+  if (swiglu) {
+    if (pair) launch_pair<AllGatherSwigluPolicy>(a, w, p, grid, timeout_ms, stream, true, p.copy_ctas);
+    else launch<AllGatherSwigluPolicy>(a, w, p, grid, timeout_ms, stream, p.copy_ctas);
+  } else {
+    if (pair) launch_pair<AllGatherPolicy>(a, w, p, grid, timeout_ms, stream, true, p.copy_ctas);
+    else launch<AllGatherPolicy>(a, w, p, grid, timeout_ms, stream, p.copy_ctas);
+  }
 }
 
 namespace {

@@ -340,5 +340,21 @@ struct AllGatherPolicy : PolicyDefaults {
   __device__ static void finish(const Params&, const Problem&, int, int, uint64_t, const volatile uint32_t*) {}
 };
 
+// All-gather -> GEMM with the SwiGLU of a gated feed-forward in the epilogue: the weight stacks the
+// gate and up projections interleaved in groups of 16 rows (16 gate rows, then the 16 up rows of
+// the same hidden units), so every 32 accumulator columns hold both halves of 16 outputs and the
+// kernel writes act[M][N / 2] = silu(gate) * up directly.  The [M][N] pre-activation never
+// reaches memory and the element-wise kernel between the two GEMMs of the block disappears.
+struct AllGatherSwigluPolicy : AllGatherPolicy {
+  static constexpr int kOutPer32 = 16;
+  __device__ static void transform(const float* acc, float, float* out) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float gate = acc[i];
+      out[i] = gate / (1.f + __expf(-gate)) * acc[16 + i];
+    }
+  }
+};
+
 }  // namespace gemm
 }  // namespace pccl

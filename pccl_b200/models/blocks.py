@@ -1,8 +1,8 @@
 """Model blocks that exercise the fused operators end to end (inference forward).
 
 ``TensorParallelMLP``   Llama-style SwiGLU feed-forward under tensor + sequence parallelism:
-    x[T/W, H] -(all-gather fused into GEMM)-> [T, 2F/W] -SwiGLU-> [T, F/W]
-      -(GEMM with fused reduce-scatter)-> [T/W, H].
+    x[T/W, H] -(all-gather fused into the GEMM, SwiGLU in its epilogue)-> [T, F/W]
+      -(GEMM with fused reduce-scatter)-> [T/W, H]: two kernels per block, no element-wise pass.
 ``MixtralMoEBlock``     residual + RMSNorm + expert-parallel top-2 MoE feed-forward.
 
 Each block has a `reference()` in plain PyTorch (fp32) used by the tests.  The reference
@@ -26,15 +26,19 @@ def rms_norm(x: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-5) -> torch.T
 class TensorParallelMLP:
     def __init__(self, tokens: int, hidden: int, ffn_local: int, w_gate_up: torch.Tensor, w_down: torch.Tensor):
         """``w_gate_up [2 * ffn_local, hidden]`` (gate rows then up rows), ``w_down [hidden, ffn_local]``."""
+        from ..ops.moe import interleave_gate_up
         self.tokens, self.hidden, self.ffn_local = tokens, hidden, ffn_local
-        self.up = ColumnParallelLinear(tokens, hidden, 2 * ffn_local, w_gate_up)
+        if ffn_local % 16:
+            raise ValueError("ffn_local must be a multiple of 16")
+        # Gate and up rows interleaved in groups of 16: one 32-column slice of the accumulator then
+        # holds both halves of 16 outputs, which is what the fused epilogue combines.
+        stacked = interleave_gate_up(w_gate_up[:ffn_local].unsqueeze(0), w_gate_up[ffn_local:].unsqueeze(0))
+        self.up = ColumnParallelLinear(tokens, hidden, 2 * ffn_local, stacked, swiglu=True)
         self.down = RowParallelLinear(tokens, ffn_local, hidden, w_down)
         self.act = torch.empty(tokens, ffn_local, dtype=torch.bfloat16, device="cuda")
 
     def __call__(self, x_shard: torch.Tensor) -> torch.Tensor:
-        gate_up = self.up(x_shard)                                   # [T, 2F/W]
-        gate, up = gate_up[:, :self.ffn_local], gate_up[:, self.ffn_local:]
-        torch.mul(F.silu(gate), up, out=self.act)
+        self.up(x_shard, self.act)                                   # [T, F/W] = silu(gate) * up
         return self.down(self.act)                                   # [T/W, H]
 
     @staticmethod

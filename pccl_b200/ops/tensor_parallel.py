@@ -58,7 +58,11 @@ class GemmReduceScatter:
 
 
 class AllGatherGemm:
-    def __init__(self, m: int, n_local: int, k: int, group=None, copy_ctas: int = 0):
+    """``swiglu=True``: ``w`` stacks the gate and up projections interleaved in groups of 16 rows
+    (``pccl_b200.ops.moe.interleave_gate_up``) and the result is ``[M, n_local / 2] = silu(gate) * up``,
+    computed in the GEMM's epilogue."""
+
+    def __init__(self, m: int, n_local: int, k: int, group=None, copy_ctas: int = 0, swiglu: bool = False):
         self.engine = _engine.get_engine()
         self.world, self.rank = self.engine.world, self.engine.rank
         if m % (self.world * _BLOCK):
@@ -70,6 +74,9 @@ class AllGatherGemm:
         self.flags.zero_()
         self.ready = torch.zeros(m // _BLOCK, dtype=torch.int32, device="cuda")
         self.copy_ctas = copy_ctas
+        self.swiglu = bool(swiglu)
+        if self.swiglu and n_local % 32:
+            raise ValueError("with swiglu the stacked gate/up weight has a multiple of 32 rows")
         self.epoch = 0
         self.group = group
         _fence(group)
@@ -83,10 +90,10 @@ class AllGatherGemm:
         if x_shard.data_ptr() != self.local_shard.data_ptr():
             self.local_shard.copy_(x_shard)
         if out is None:
-            out = torch.empty(self.m, self.n, dtype=torch.bfloat16, device=w.device)
+            out = torch.empty(self.m, self.n // 2 if self.swiglu else self.n, dtype=torch.bfloat16, device=w.device)
         self.epoch += 1
         _native().all_gather_gemm(self.gathered.heap_offset, self.m, self.k, w, out, self.flags.heap_offset,
-                                  self.ready, self.epoch, self.copy_ctas, ctas)
+                                  self.ready, self.epoch, self.copy_ctas, ctas, self.swiglu)
         return out
 
 

@@ -233,14 +233,17 @@ def ensure_plan(kind: str, numel: int, dtype: torch.dtype, algorithm: Optional[s
         name += "_f" + os.environ.get("PCCL_NVLS_FRACTION", "0.7")
     if name in _state["registered"]:
         return name
-    template = ALGORITHMS[algorithm]()
-    plan_executor = executor or ("multimem" if algorithm == "nvls" else "sm")
-    graph = getattr(template, "build_" + kind)(rank, world, numel, dtype_name, plan_executor, channels)
-    if reduce_op != "sum":
-        for node in graph.nodes.values():
-            if hasattr(node, "reduce_op"):
-                node.reduce_op = reduce_op
-    text = Compiler().compile_to_json(graph)
+    plan_executor = executor or ("multimem" if algorithm in ("nvls", "nvls_twopass", "hybrid") else "sm")
+
+    def compile_for(r: int) -> str:
+        graph = getattr(ALGORITHMS[algorithm](), "build_" + kind)(r, world, numel, dtype_name, plan_executor, channels)
+        if reduce_op != "sum":
+            for node in graph.nodes.values():
+                if hasattr(node, "reduce_op"):
+                    node.reduce_op = reduce_op
+        return Compiler().compile_to_json(graph)
+
+    text = _plan_from_cache(name, rank, world, compile_for)
     engine = _engine.get_engine()
     if hasattr(engine, "register_operation_from_string"):
         ok = engine.register_operation_from_string(name, text)
@@ -257,6 +260,50 @@ def ensure_plan(kind: str, numel: int, dtype: torch.dtype, algorithm: Optional[s
         dist.barrier(group=_state["group"])      # nobody signals a rank that has not registered yet
     _state["registered"][name] = (kind, algorithm, channels)
     return name
+
+
+def _plan_cache_dir() -> Optional[str]:
+    where = os.environ.get("PCCL_PLAN_CACHE", os.path.expanduser("~/.pccl/plans"))
+    return None if where.lower() in ("", "0", "off", "none") else where
+
+
+def _plan_from_cache(name: str, rank: int, world: int, compile_for) -> str:
+    """This rank's compiled plan: from the on-disk cache when the same (collective, algorithm, dtype,
+    size, channels, world, rank, library version) was compiled before, else compiled now, and, before
+    it is stored, checked together with every other rank's plan: the engine's abstract replay of the
+    signal protocol (``PCCL_VALIDATE=0`` skips it) refuses a set that would deadlock or leave signals
+    behind.  Templates are deterministic, so every rank can build all ranks' plans without talking
+    to anyone; a cached plan was checked when it was first compiled."""
+    import hashlib
+    from .. import __version__
+    where = _plan_cache_dir()
+    extra = os.environ.get("PCCL_NVLS_FRACTION", "") if "hybrid" in name else ""
+    key = hashlib.sha1(f"{name}|rank{rank}|{__version__}|{extra}".encode()).hexdigest()
+    path = os.path.join(where, key + ".json") if where else None
+    if path and os.path.exists(path):
+        try:
+            with open(path) as handle:
+                text = handle.read()
+            if text.lstrip().startswith("{"):
+                return text
+        except OSError:
+            pass
+    text = compile_for(rank)
+    if os.environ.get("PCCL_VALIDATE", "1") != "0" and world > 1 and not isinstance(_engine.get_engine(), _engine.CpuEngine):
+        native = _engine.load_native()
+        report = native.check_world([text if r == rank else compile_for(r) for r in range(world)])
+        if report["deadlock"] or report["leftover_signals"]:
+            raise _engine.PCCLError(f"plan '{name}' fails the signal-protocol check: {report['detail']}")
+    if path:
+        try:
+            os.makedirs(where, exist_ok=True)
+            tmp = f"{path}.{os.getpid()}.tmp"
+            with open(tmp, "w") as handle:
+                handle.write(text)
+            os.replace(tmp, path)
+        except OSError:
+            pass
+    return text
 
 
 def all_reduce(tensor: torch.Tensor, op: str = "sum", algorithm: Optional[str] = None,

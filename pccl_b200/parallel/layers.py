@@ -26,8 +26,13 @@ from . import collectives as _c
 
 
 class ColumnParallelLinear:
-    def __init__(self, tokens: int, in_features: int, out_features_local: int, weight: torch.Tensor = None):
-        self.op = AllGatherGemm(tokens, out_features_local, in_features)
+    """``swiglu=True`` makes it the gated first half of a SwiGLU feed-forward: ``weight`` holds
+    the gate and up projections interleaved in groups of 16 rows and the output is
+    ``[T, out_features_local / 2] = silu(gate) * up`` straight from the GEMM's epilogue."""
+
+    def __init__(self, tokens: int, in_features: int, out_features_local: int, weight: torch.Tensor = None,
+                 swiglu: bool = False):
+        self.op = AllGatherGemm(tokens, out_features_local, in_features, swiglu=swiglu)
         self.weight = weight if weight is not None else torch.empty(
             out_features_local, in_features, dtype=torch.bfloat16, device="cuda")
 
@@ -81,10 +86,26 @@ def partition_buckets(sizes: Sequence[int], bucket_elems: int) -> List[List[int]
 class GradientBuckets:
     """Average gradients over the data-parallel ranks through the plan engine.
 
-    Parameters are packed, in order, into buckets of at most ``bucket_bytes``; each bucket is a slice
-    of the symmetric working buffer, so the all-reduce runs in place with no staging copy.  Buckets
-    are sized for launch latency and overlap (NVSwitch gives every pair full bandwidth, so there is
-    no per-link reason to split further).
+    Parameters are packed, in order, into buckets of at most ``bucket_bytes``.  A bucket is gathered
+    into the head of the symmetric working buffer, where its all-reduce runs in place with no staging
+    copy (buckets take turns there: they are reduced one after the other on one side stream);
+    packing and unpacking are one kernel launch per bucket (the table of gradient addresses travels
+    in the kernel's parameters).  Buckets are sized for launch latency and overlap (NVSwitch gives
+    every pair full bandwidth, so there is no per-link reason to split further).
+
+    Two ways to use it:
+
+    * ``reduce()`` after backward: every bucket is packed, reduced and unpacked on a side stream and
+      the current stream waits for the result.
+    * ``attach()`` once, then ``finish()`` after every backward: a hook on each parameter marks its
+      gradient ready; when the last gradient of a bucket arrives (buckets are filled in reverse
+      parameter order, the order backward produces them) the bucket is reduced on the side stream
+      while backward goes on computing.  ``finish()`` reduces what is left and makes the current
+      stream wait.  Every rank must produce its gradients for the same buckets, in any order.
+
+    The collectives' kernels run next to whatever backward has on the GPU; they are launched so that
+    all their CTAs are resident at once (see ``csrc/common/launch.h``), so a GEMM holding most of the
+    SMs delays them but cannot starve them.
     """
 
     def __init__(self, params: Iterable[torch.nn.Parameter], bucket_bytes: int = 64 << 20,
@@ -92,33 +113,108 @@ class GradientBuckets:
         self.params: List[torch.nn.Parameter] = [p for p in params if p.requires_grad]
         self.dtype = dtype
         esize = torch.empty((), dtype=dtype).element_size()
+        self.esize = esize
         world = int(_c._state["world"])          # the engine is already connected (pccl_b200.parallel.init)
+        self.world = world
         self.buckets: List[Sequence[int]] = partition_buckets([p.numel() for p in self.params], bucket_bytes // esize)
         # every bucket's element count is rounded up so that it divides over ranks and 16-byte vectors
         self.sizes = []
+        unit = world * 8
         for idxs in self.buckets:
             n = sum(self.params[i].numel() for i in idxs)
-            unit = world * 8
             self.sizes.append((n + unit - 1) // unit * unit)
         self.capacity = max(self.sizes)
         self.buffer = _c.working_tensor(self.capacity, dtype)
+        self.offsets: List[List[int]] = []           # byte offset of every parameter inside its bucket
+        for idxs in self.buckets:
+            at, row = 0, []
+            for i in idxs:
+                row.append(at * esize)
+                at += self.params[i].numel()
+            self.offsets.append(row)
+        self.bucket_of = {i: b for b, idxs in enumerate(self.buckets) for i in idxs}
+        self.stream = torch.cuda.Stream()
+        self._native = None
+        self._hooks: list = []
+        self._pending = [0] * len(self.buckets)
+        self._launched = [False] * len(self.buckets)
 
+    # -- one bucket ------------------------------------------------------------------------------
+    def _fused(self):
+        if self._native is None:
+            from .. import engine as _engine
+            self._native = _engine.load_native().fused
+        return self._native
+
+    def _grads(self, b: int) -> List[torch.Tensor]:
+        grads = []
+        for i in self.buckets[b]:
+            g = self.params[i].grad
+            if g is None:
+                raise RuntimeError(f"parameter {i} has no gradient")
+            if g.dtype != self.dtype or not g.is_contiguous():
+                raise RuntimeError("GradientBuckets reduces contiguous gradients of its own dtype "
+                                   f"({self.dtype}); parameter {i} has {g.dtype}")
+            grads.append(g)
+        return grads
+
+    def _reduce_bucket(self, b: int) -> None:
+        """Pack, all-reduce (average) and unpack bucket ``b`` on the side stream, after everything
+        the current stream has queued so far."""
+        flat = self.buffer[:self.sizes[b]]
+        grads = self._grads(b)
+        used = sum(g.numel() for g in grads)
+        self.stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.stream):
+            if used < self.sizes[b]:
+                flat[used:].zero_()
+            self._fused().bucket_pack(grads, self.offsets[b], flat, False)
+            _c.all_reduce(flat, op="avg", async_op=True)
+            self._fused().bucket_pack(grads, self.offsets[b], flat, True)
+        for g in grads:
+            g.record_stream(self.stream)
+        self._launched[b] = True
+
+    # -- after backward --------------------------------------------------------------------------
     def reduce(self) -> None:
         """Average every parameter's ``.grad`` in place (call after backward)."""
-        for idxs, size in zip(self.buckets, self.sizes):
-            flat = self.buffer[:size]
-            offset = 0
-            for i in idxs:
-                g = self.params[i].grad
-                n = g.numel()
-                flat[offset:offset + n].copy_(g.reshape(-1))
-                offset += n
-            if offset < size:
-                flat[offset:].zero_()
-            _c.all_reduce(flat, op="avg")
-            offset = 0
-            for i in idxs:
-                g = self.params[i].grad
-                n = g.numel()
-                g.copy_(flat[offset:offset + n].view_as(g))
-                offset += n
+        for b in range(len(self.buckets)):
+            self._reduce_bucket(b)
+        self._join()
+
+    def _join(self) -> None:
+        torch.cuda.current_stream().wait_stream(self.stream)
+        self._launched = [False] * len(self.buckets)
+        self._pending = [len(idxs) for idxs in self.buckets]
+
+    # -- during backward -------------------------------------------------------------------------
+    def attach(self) -> "GradientBuckets":
+        """Install the hooks that start a bucket's reduction as soon as its last gradient exists."""
+        if self._hooks:
+            return self
+        self._pending = [len(idxs) for idxs in self.buckets]
+
+        def make(i: int):
+            def ready(_param):
+                b = self.bucket_of[i]
+                self._pending[b] -= 1
+                if self._pending[b] == 0 and not self._launched[b]:
+                    self._reduce_bucket(b)
+            return ready
+
+        for i, p in enumerate(self.params):
+            self._hooks.append(p.register_post_accumulate_grad_hook(make(i)))
+        return self
+
+    def detach(self) -> None:
+        for h in self._hooks:
+            h.remove()
+        self._hooks = []
+
+    def finish(self) -> None:
+        """Reduce the buckets backward did not complete (unused parameters keep their old gradient
+        out of it only if every rank skips them alike) and make the current stream wait."""
+        for b in range(len(self.buckets)):
+            if not self._launched[b] and all(self.params[i].grad is not None for i in self.buckets[b]):
+                self._reduce_bucket(b)
+        self._join()

@@ -299,6 +299,38 @@ def main():
         torch.testing.assert_close(prm.grad.float(), want, atol=0.03, rtol=2e-2)
     report["checked"] += 1
 
+    # Hook-driven reduction during a real backward, next to GEMMs that keep the SMs busy: the buckets'
+    # collectives are launched while backward still computes (all their CTAs resident at once, so the
+    # matmuls delay them but cannot starve them).
+    torch.manual_seed(77)                                                 # identical weights on every rank
+    layers = torch.nn.Sequential(*[torch.nn.Linear(2048, 2048, bias=False) for _ in range(4)]).cuda().bfloat16()
+    buckets = GradientBuckets(layers.parameters(), bucket_bytes=2048 * 2048 * 2).attach()
+    for step in range(2):
+        layers.zero_grad(set_to_none=True)
+        xb = torch.randn(4096, 2048, device="cuda", generator=torch.Generator(device="cuda").manual_seed(40 + rank + step)
+                         ).bfloat16()
+        layers(xb).float().pow(2).mean().backward()
+        buckets.finish()
+        torch.cuda.synchronize()
+        pp.check_errors()
+    # reference: the same backward without hooks, averaged with NCCL
+    buckets.detach()
+    layers.zero_grad(set_to_none=True)
+    layers(xb).float().pow(2).mean().backward()
+    for prm in layers.parameters():
+        want = prm.grad.float().clone()
+        dist.all_reduce(want)
+        prm.expected = want / world
+    layers.zero_grad(set_to_none=True)
+    buckets.attach()
+    layers(xb).float().pow(2).mean().backward()
+    buckets.finish()
+    torch.cuda.synchronize()
+    for prm in layers.parameters():
+        torch.testing.assert_close(prm.grad.float(), prm.expected, atol=2e-3, rtol=5e-2)
+    buckets.detach()
+    report["checked"] += 1
+
     # ---- OCS layer over the real engine, the NVLink connector, rank-uniform path choice ----
     from pccl_b200 import selfcheck
     ocs = selfcheck.run(only=["misaligned_view_same_path", "ocs_barrier_nvlink_connector",

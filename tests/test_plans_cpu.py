@@ -156,18 +156,25 @@ def test_out_of_range_access_is_reported():
         simulate(plans, make_inputs("allreduce", 2, 64))
 
 
-def test_switched_fabric_selector_follows_measured_crossovers():
-    """Two ranks never take the in-switch path; four take it only in the middle sizes."""
-    from pccl_b200.dsl.algorithms.selector import select_algorithm
+def test_switched_fabric_selector_built_in_crossovers(tmp_path, monkeypatch):
+    """Without a tuning file: two ranks never take the in-switch path (it moves 1.5x the bytes of
+    two-shot there); from four ranks on it takes over once bandwidth matters."""
+    from pccl_b200.dsl.algorithms import selector
     from pccl_b200.dsl.superopt import B200_PROFILE, NVLINK5_TOPOLOGY
-    pick = lambda w, b: type(select_algorithm(w, b, NVLINK5_TOPOLOGY, B200_PROFILE)).__name__
-    assert pick(2, 64 << 10) == "OneShotAllreduce"
-    assert pick(2, 512 << 20) == "TwoShotAllreduce"
-    assert pick(4, 1 << 20) == "OneShotAllreduce"
-    assert pick(4, 8 << 20) == "NvlsAllreduce"
-    assert pick(4, 512 << 20) == "TwoShotAllreduce"
-    assert pick(8, 1 << 20) == "TwoShotAllreduce"
-    assert pick(8, 512 << 20) == "NvlsAllreduce"
+    monkeypatch.setenv("PCCL_TUNING_FILE", str(tmp_path / "none.json"))
+    monkeypatch.delenv("PCCL_ALGO", raising=False)
+    selector.clear_tuning_cache()
+    pick = lambda w, b: type(selector.select_algorithm(w, b, NVLINK5_TOPOLOGY, B200_PROFILE)).__name__
+    try:
+        assert pick(2, 64 << 10) == "OneShotAllreduce"
+        assert pick(2, 512 << 20) == "TwoShotAllreduce"
+        assert pick(4, 1 << 20) == "OneShotAllreduce"
+        assert pick(4, 8 << 20) == "NvlsAllreduce"
+        assert pick(4, 512 << 20) == "NvlsAllreduce"
+        assert pick(8, 1 << 20) == "TwoShotAllreduce"
+        assert pick(8, 512 << 20) == "NvlsAllreduce"
+    finally:
+        selector.clear_tuning_cache()
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
