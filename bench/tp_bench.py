@@ -5,6 +5,7 @@
 Llama-3-8B shapes at TP = N scaled from the TP = 8 configuration (tokens 1024 per rank):
   GEMM -> reduce-scatter   X[1024*N, 14336/8] x W[14336/8, 4096]   (row-parallel down projection)
   all-gather -> GEMM       X shard [1024, 4096] -> [1024*N, 4096] x W[4096, 14336/8]
+  all-reduce + residual + RMSNorm at 1 / 128 / 8192 tokens, and the whole SwiGLU feed-forward block
 Times are device times (CUDA events), max over ranks, median of the iterations; a 256 MB
 buffer is rewritten between iterations so operands leave the L2.  The roofline time is the
 slower of FLOPs / measured bf16 peak and NVLink bytes / 770 GB/s (measured peer-copy rate).
@@ -145,6 +146,39 @@ def main():
                             "unfused_nccl_torch_ms": round(t_unfused, 4),
                             "speedup_vs_unfused": round(t_unfused / t_fused, 3),
                             "roofline_ms": round(roof_ms, 5), "fraction_of_roofline": round(roof_ms / t_fused, 3)})
+    # The whole tensor + sequence parallel SwiGLU feed-forward: two fused kernels against the
+    # unfused block (NCCL all-gather, cuBLAS, silu * up, cuBLAS, NCCL reduce-scatter).
+    from pccl_b200.models import TensorParallelMLP
+    f_local = kl
+    w_gu = (torch.randn(2 * f_local, h, device="cuda") * 0.02).to(torch.bfloat16)
+    w_dn = (torch.randn(h, f_local, device="cuda") * 0.02).to(torch.bfloat16)
+    mlp = TensorParallelMLP(m, h, f_local, w_gu, w_dn)
+    x_shard = torch.randn(m // world, h, device="cuda").to(torch.bfloat16)
+    mlp.up.input_shard.copy_(x_shard)
+    full = torch.empty(m, h, device="cuda", dtype=torch.bfloat16)
+    gu = torch.empty(m, 2 * f_local, device="cuda", dtype=torch.bfloat16)
+    act = torch.empty(m, f_local, device="cuda", dtype=torch.bfloat16)
+    part_out = torch.empty(m, h, device="cuda", dtype=torch.bfloat16)
+    y_shard = torch.empty(m // world, h, device="cuda", dtype=torch.bfloat16)
+
+    def unfused_mlp():
+        dist.all_gather_into_tensor(full, x_shard)
+        torch.matmul(full, w_gu.t(), out=gu)
+        torch.mul(torch.nn.functional.silu(gu[:, :f_local]), gu[:, f_local:], out=act)
+        torch.matmul(act, w_dn.t(), out=part_out)
+        dist.reduce_scatter_tensor(y_shard, part_out)
+
+    t_fused = timed(lambda: mlp(mlp.up.input_shard), args.iters, flush)
+    gemm.check()
+    t_unfused = timed(unfused_mlp, args.iters, flush)
+    mlp_flops = 2.0 * m * h * 2 * f_local + 2.0 * m * f_local * h
+    mlp_link = 2 * (world - 1) / world * m * h * 2
+    roof_ms = max(mlp_flops / (peak_tflops * 1e12), mlp_link / 2 / (link_gbs * 1e9)) * 1e3
+    results.append({"op": "tp_swiglu_mlp_block", "tokens": m, "hidden": h, "ffn_local": f_local, "world": world,
+                    "fused_ms": round(t_fused, 4), "unfused_nccl_cublas_ms": round(t_unfused, 4),
+                    "speedup_vs_unfused": round(t_unfused / t_fused, 3), "kernels_fused": 2,
+                    "roofline_ms": round(roof_ms, 4), "fraction_of_roofline": round(roof_ms / t_fused, 3),
+                    "note": "all-gather + gate/up GEMM + SwiGLU in one kernel, down GEMM + reduce-scatter in one"})
     if rank == 0:
         for r in results:
             print(json.dumps(r), flush=True)
