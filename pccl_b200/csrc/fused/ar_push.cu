@@ -122,7 +122,10 @@ __device__ __forceinline__ void arrive_and_post(const PushParams& p, int phase) 
   __shared__ uint32_t is_last;
   __syncthreads();
   if (threadIdx.x == 0) {
-    ptx::fence_sys();
+    // GPU scope suffices here: the CTA that completes the count fences at system scope before it posts,
+    // and that fence is cumulative over every arrival it counted (a system fence per CTA is slow while
+    // other SMs stream stores over NVLink).
+    ptx::fence_gpu();
     const uint32_t seen = atomicAdd(p.counters + phase, 1u) + 1u;
     is_last = seen == p.epoch * gridDim.x ? 1u : 0u;
   }

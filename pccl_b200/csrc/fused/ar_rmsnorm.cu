@@ -179,7 +179,10 @@ __global__ void __launch_bounds__(kThreadsNorm) ar_residual_rmsnorm_kernel(const
   //    the last CTA then waits for every peer's, so that y and h are complete on return.
   __syncthreads();
   if (threadIdx.x == 0) {
-    ptx::fence_sys();
+    // GPU scope suffices here: the CTA that completes the count fences at system scope before it posts,
+    // and that fence is cumulative over every arrival it counted (a system fence per CTA is slow while
+    // other SMs stream stores over NVLink).
+    ptx::fence_gpu();
     const uint32_t done = atomicAdd(p.cta_counter, 1u) + 1u;
     s_ok = done == p.epoch * gridDim.x ? 2u : 1u;
   }

@@ -252,6 +252,9 @@ void bind_fused_ops(py::module_& m) {
                             c10::cuda::getCurrentCUDAStream().stream());
         },
         py::arg("tensors"), py::arg("offsets"), py::arg("bucket"), py::arg("unpack") = false);
+  // Per-CTA milestones of the most recent GEMM-family launch (see gemm_host.h).
+  f.def("gemm_trace_enable", &gemm::gemm_trace_enable);
+  f.def("gemm_trace_read", &gemm::gemm_trace_read);
   // Device-side error word of the GEMM family (0 = ok); synchronises.
   f.def("read_error", &gemm::read_error);
   f.def("clear_error", &gemm::clear_error);

@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <vector>
 
 namespace pccl {
 namespace gemm {
@@ -12,6 +13,12 @@ namespace gemm {
 uint32_t* error_word();
 uint32_t read_error();
 void clear_error();
+
+// Timeline of the GEMM family's kernels (off by default): while enabled every CTA of a launch
+// stamps %globaltimer at its milestones (see Problem::trace); gemm_trace_read returns the stamps
+// of the most recent launch, 8 per CTA for up to 256 CTAs (synchronises).
+void gemm_trace_enable(bool on);
+std::vector<uint64_t> gemm_trace_read();
 
 struct MatrixDesc {
   const void* ptr;       // bf16, row-major

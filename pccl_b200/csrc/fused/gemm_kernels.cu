@@ -3,6 +3,7 @@
 
 #include <algorithm>
 #include <mutex>
+#include <vector>
 
 #include "../common/launch.h"
 #include "../engine/cuda_driver.h"
@@ -19,6 +20,8 @@ namespace {
 
 uint32_t* g_error = nullptr;
 std::once_flag g_error_once;
+uint64_t* g_trace = nullptr;          // [kTraceCtas][kGemmTraceStamps], allocated by gemm_trace_enable
+constexpr int kTraceCtas = 256;
 
 // 2-D bf16 tensor map over a row-major matrix: inner dimension = columns, box = kBK x box_rows,
 // 128-byte swizzle (the layout tcgen05.mma's SWIZZLE_128B descriptor expects).
@@ -87,6 +90,7 @@ void launch(const MatrixDesc& a, const MatrixDesc& b, const typename Policy::Par
   g.tiles_m = (g.M + kBM - 1) / kBM;
   g.tiles_n = (g.N + kBN - 1) / kBN;
   g.bn = kBN;
+  g.trace = g_trace;
   g.error = error_word();
   g.timeout_ns = timeout_ms * 1000000ull;
   const CUtensorMap ta = make_map(a, kBM), tb = make_map(b, kBN);
@@ -106,7 +110,8 @@ void launch(const MatrixDesc& a, const MatrixDesc& b, const typename Policy::Par
   Problem g_arg = g;
   typename Policy::Params params_arg = params;
   void* args[] = {&ta_arg, &tb_arg, &g_arg, &params_arg};
-  launch_coresident_args(kernel, static_cast<uint32_t>(grid), kThreads, kSmemBytes, stream, args, true);
+  launch_coresident_args(kernel, static_cast<uint32_t>(grid), kThreads + 32 * Policy::kReducerWarps, kSmemBytes, stream,
+                         args, true);
   (void)attr_once;
 }
 
@@ -136,6 +141,7 @@ void launch_pair(const MatrixDesc& a, const MatrixDesc& b, const typename Policy
   g.bn = forced_bn >= 32 && forced_bn <= kBN && forced_bn % 32 == 0 ? static_cast<int>(forced_bn)
                                                                       : pick_tile_n(g.M, g.N, (grid - aux_ctas) / 2);
   g.tiles_n = (g.N + g.bn - 1) / g.bn;
+  g.trace = g_trace;
   g.error = error_word();
   g.timeout_ns = timeout_ms * 1000000ull;
   const CUtensorMap ta = make_map(a, kBM), tb = make_map(b, g.bn / 2);
@@ -145,7 +151,7 @@ void launch_pair(const MatrixDesc& a, const MatrixDesc& b, const typename Policy
   if (grid - aux_ctas > 2 * pair_tiles) grid = 2 * pair_tiles + aux_ctas;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(kThreads + 32 * Policy::kReducerWarps);
   cfg.dynamicSmemBytes = kSmemBytes2;
   cfg.stream = stream;
   cudaLaunchAttribute attrs[2];
@@ -166,6 +172,20 @@ uint32_t* error_word() {
     PCCL_CUDA(cudaMemset(g_error, 0, sizeof(uint32_t)));
   });
   return g_error;
+}
+
+void gemm_trace_enable(bool on) {
+  if (on && !g_trace) PCCL_CUDA(cudaMalloc(reinterpret_cast<void**>(&g_trace), kTraceCtas * kGemmTraceStamps * sizeof(uint64_t)));
+  if (on) PCCL_CUDA(cudaMemset(g_trace, 0, kTraceCtas * kGemmTraceStamps * sizeof(uint64_t)));
+  if (!on && g_trace) { cudaFree(g_trace); g_trace = nullptr; }
+}
+
+std::vector<uint64_t> gemm_trace_read() {
+  std::vector<uint64_t> out;
+  if (!g_trace) return out;
+  out.resize(kTraceCtas * kGemmTraceStamps);
+  PCCL_CUDA(cudaMemcpy(out.data(), g_trace, out.size() * sizeof(uint64_t), cudaMemcpyDeviceToHost));
+  return out;
 }
 
 uint32_t read_error() {

@@ -194,7 +194,10 @@ struct MoeDownPolicy : PolicyDefaults {
     const int me = p.peers.rank, world = p.peers.world;
     if (threadIdx.x == 0) {
       ok_flag = 1;
-      ptx::fence_sys();
+      // GPU scope suffices here: the CTA that completes the count fences at system scope before it posts,
+      // and that fence is cumulative over every arrival it counted (a system fence per CTA is slow while
+      // other SMs stream stores over NVLink).
+      ptx::fence_gpu();
       const uint32_t arrived = atomicAdd(p.cta_counter, 1u) + 1u;
       if (arrived == p.shape.epoch * static_cast<uint32_t>(num_ctas)) {
         ptx::fence_sys();

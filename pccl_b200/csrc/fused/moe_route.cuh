@@ -137,7 +137,10 @@ __global__ void __launch_bounds__(kMoeRouteWarps * 32) moe_route_kernel(const Mo
   // region at its expert rank followed by this rank's flag there.
   __syncthreads();
   if (threadIdx.x == 0) {
-    ptx::fence_sys();
+    // GPU scope suffices here: the CTA that completes the count fences at system scope before it posts,
+    // and that fence is cumulative over every arrival it counted (a system fence per CTA is slow while
+    // other SMs stream stores over NVLink).
+    ptx::fence_gpu();
     is_last = atomicAdd(p.scratch + kE, 1u) + 1u == gridDim.x ? 1u : 0u;
   }
   __syncthreads();

@@ -4,8 +4,10 @@
 //       its full partial product; the epilogue stores each bf16 row segment straight into the
 //       *owning* rank's receive slot for this source over NVLink (tiles ordered so the most
 //       remote owner comes first and the own rows last), and posts one flag per finished
-//       128-row block.  After its GEMM tiles a CTA turns reducer: it waits for the flags of all
-//       sources of a block and sums the W slots in rank order (fp32, deterministic).
+//       128-row block.  Four extra warps per CTA are reducers from the start: each takes 32-row
+//       strips of this rank's own row blocks in the order their partials arrive, waits for the
+//       flags of all sources of the block and sums the W slots in rank order (fp32,
+//       deterministic), so the reduction runs under the GEMM instead of after it.
 //   AllGatherPolicy       Y_r = gather(X) W_r^T.  A few auxiliary CTAs pull the peers' row shards
 //       into the *local* gathered matrix with SM loads and publish a ready flag per 128-row
 //       block; the GEMM CTAs start with the local shard and wait for a block's flag before
@@ -92,8 +94,14 @@ struct ReduceScatterPolicy : PolicyDefaults {
   // Called by the signal warp's lane 0 once all four epilogue warps have stored tile (mb, nb)
   // (it acquired their mbarrier arrivals, so the fence below covers their stores).  The call
   // that completes the row block posts the flag at the owner.
+  //
+  // Fences: a tile's stores only have to be ordered before the block counter at GPU scope; the one
+  // CTA that completes the block then fences at system scope before the flag, which by cumulativity
+  // covers every tile it counted.  (A system-scope fence per tile measured tens of microseconds
+  // each while the other SMs keep streaming stores over NVLink: the flags of the first blocks
+  // reached the owner 25-40 us after their data.)
   __device__ static void tile_done(const Params& p, const Problem& g, int mb, int) {
-    ptx::fence_sys();
+    ptx::fence_gpu();
     const uint32_t target = p.epoch * static_cast<uint32_t>(g.tiles_n);
     const uint32_t seen = atomicAdd(p.block_counter + mb, 1u) + 1u;
     if (seen == target) {
@@ -107,20 +115,22 @@ struct ReduceScatterPolicy : PolicyDefaults {
   __device__ static int aux_ctas(const Params&) { return 0; }
   __device__ static void aux_main(const Params&, const Problem&, int, int, uint64_t, const volatile uint32_t*, uint8_t*) {}
 
-  // out = sum over the sources' slots, rank order, fp32.  kRV vectors per thread and iteration and
-  // kW slots each are loaded before the first add.  Every load is unconditional (lanes past the
-  // end re-read the last vector, slots past the world re-read the own one): a conditionally
-  // assigned register makes the compiler wait for each load before it issues the next.
+  // out = sum over the sources' slots, rank order, fp32, for `total` 16-byte vectors of rows
+  // [row0, ...) x columns [col0, ...), done by `nthreads` threads of which this is number `tid`.
+  // kRV vectors per thread and iteration and kW slots each are loaded before the first add.  Every
+  // load is unconditional (lanes past the end re-read the last vector, slots past the world re-read
+  // the own one): a conditionally assigned register makes the compiler wait for each load before
+  // it issues the next.
   template <int kW>
   __device__ static void sum_slots(const Params& p, const Problem& g, int me, int world, int row0, int col0,
-                                   int vec_per_row, int total) {
-    constexpr int kRV = kW >= 8 ? 2 : 4;
-    for (int i = threadIdx.x; i < total; i += blockDim.x * kRV) {
+                                   int vec_per_row, int total, int tid, int nthreads) {
+    constexpr int kRV = 16 / kW;                  // sixteen 16-byte loads in flight per thread whatever the world size
+    for (int i = tid; i < total; i += nthreads * kRV) {
       uint4 raw[kRV][kW];
       int r[kRV], c[kRV];
 #pragma unroll
       for (int u = 0; u < kRV; ++u) {
-        const int idx = min(i + u * static_cast<int>(blockDim.x), total - 1);
+        const int idx = min(i + u * nthreads, total - 1);
         r[u] = row0 + idx / vec_per_row;
         c[u] = col0 + (idx % vec_per_row) * 8;
 #pragma unroll
@@ -129,7 +139,7 @@ struct ReduceScatterPolicy : PolicyDefaults {
       }
 #pragma unroll
       for (int u = 0; u < kRV; ++u) {
-        if (i + u * static_cast<int>(blockDim.x) >= total) continue;
+        if (i + u * nthreads >= total) continue;
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
         for (int s = 0; s < kW; ++s) {
@@ -146,34 +156,39 @@ struct ReduceScatterPolicy : PolicyDefaults {
     }
   }
 
-  // Reducer phase: item = (local row block, n tile); sum the world slots in rank order.
-  __device__ static void finish(const Params& p, const Problem& g, int cta, int num_ctas, uint64_t deadline,
-                                const volatile uint32_t* abort_flag) {
-    __shared__ uint32_t ok_flag;
+  // Reducer warps: item = (local row block, n tile, 32-row strip), one warp per item, items in the
+  // order the blocks complete (every source delivers this rank's blocks in ascending order).
+  static constexpr int kReducerWarps = 4;
+  __device__ static void reducer_main(const Params& p, const Problem& g, int cta, int num_ctas, int rwarp, int lane,
+                                      uint64_t deadline, const volatile uint32_t* abort_flag) {
     const int me = p.peers.rank, world = p.peers.world;
     const uint32_t* flags = reinterpret_cast<const uint32_t*>(p.peers.base[me] + p.flags_off);
-    const int items = p.blocks_per_rank * g.tiles_n;
-    for (int item = cta; item < items; item += num_ctas) {
-      const int block = item / g.tiles_n, nb = item % g.tiles_n;
-      if (threadIdx.x == 0) ok_flag = 1;
-      __syncthreads();
-      if (static_cast<int>(threadIdx.x) < world) {
-        if (!wait_flag_ge(flags + threadIdx.x * p.blocks_per_rank + block, p.epoch, deadline, abort_flag)) {
-          ok_flag = 0;
-          raise_error(g, kErrPolicyWait, 3);
-        }
+    const int strips = kBM / 32;
+    const int items = p.blocks_per_rank * g.tiles_n * strips;
+    for (int item = cta * kReducerWarps + rwarp; item < items; item += num_ctas * kReducerWarps) {
+      const int block = item / (g.tiles_n * strips), rest = item % (g.tiles_n * strips);
+      const int nb = rest / strips, strip = rest % strips;
+      bool ok = true;
+      if (lane < world) ok = wait_flag_ge(flags + lane * p.blocks_per_rank + block, p.epoch, deadline, abort_flag);
+      if (!__all_sync(0xffffffffu, ok)) {
+        if (lane == 0) raise_error(g, kErrPolicyWait, 3);
+        return;
       }
-      __syncthreads();
-      if (!ok_flag) return;
-      const int row0 = block * kBM, col0 = nb * g.bn;
-      const int rows = min(kBM, p.rows_per_rank - row0), cols = min(g.bn, g.N - col0);
+      if (rwarp == 0 && lane == 0) {              // timeline: first and latest item whose partials were all in
+        if (item < num_ctas * kReducerWarps) trace_stamp(g, 6);
+        trace_stamp(g, 7);
+      }
+      const int row0 = block * kBM + strip * 32, col0 = nb * g.bn;
+      const int rows = min(32, p.rows_per_rank - row0), cols = min(g.bn, g.N - col0);
+      if (rows <= 0 || cols <= 0) continue;
       const int vec_per_row = cols / 8;                    // 8 bf16 per 16 bytes (N % 8 == 0)
       const int total = rows * vec_per_row;
-      if (world <= 2) sum_slots<2>(p, g, me, world, row0, col0, vec_per_row, total);
-      else if (world <= 4) sum_slots<4>(p, g, me, world, row0, col0, vec_per_row, total);
-      else sum_slots<8>(p, g, me, world, row0, col0, vec_per_row, total);
+      if (world <= 2) sum_slots<2>(p, g, me, world, row0, col0, vec_per_row, total, lane, 32);
+      else if (world <= 4) sum_slots<4>(p, g, me, world, row0, col0, vec_per_row, total, lane, 32);
+      else sum_slots<8>(p, g, me, world, row0, col0, vec_per_row, total, lane, 32);
     }
   }
+  __device__ static void finish(const Params&, const Problem&, int, int, uint64_t, const volatile uint32_t*) {}
 };
 
 // ------------------------------------------------------------------------------------------------

@@ -33,6 +33,8 @@ namespace gemm {
 constexpr int kBM = 128, kBN = 256, kBK = 64, kStages = 4;
 constexpr int kUmmaK = 16;
 constexpr int kThreads = 224;                                  // 7 warps: TMA, MMA, 4 epilogue, signal
+constexpr int kReducerThreads = 128;                           // + 4 reducer warps for policies that ask for them
+constexpr int kMaxThreads = kThreads + kReducerThreads;
 constexpr uint32_t kBytesA = kBM * kBK * 2, kBytesB = kBN * kBK * 2;
 constexpr uint32_t kStageBytes = kBytesA + kBytesB;
 constexpr int kEpiCols = 128;                                   // columns staged per epilogue pass
@@ -46,7 +48,15 @@ struct Problem {
   int bn;                     // columns per tile: kBN, or what the paired kernel's launcher chose (a multiple of 32)
   uint32_t* error;            // device word: 0 ok, else (code << 8 | role)
   uint64_t timeout_ns;
+  // Optional timeline (null = off): kGemmTraceStamps %globaltimer values per CTA:
+  // [0] kernel entered, [1] MMA issuer done with its last tile, [2] epilogue warps done,
+  // [3] reducer warps done, [4] CTA leaves, [5] first accumulator complete.
+  uint64_t* trace;
 };
+constexpr int kGemmTraceStamps = 8;
+__device__ __forceinline__ void trace_stamp(const Problem& g, int slot) {
+  if (g.trace) g.trace[static_cast<uint64_t>(blockIdx.x) * kGemmTraceStamps + slot] = ptx::globaltimer();
+}
 
 enum ErrorCode : uint32_t { kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueWait = 3, kErrPolicyWait = 4 };
 
@@ -70,6 +80,12 @@ struct PolicyDefaults {
   // true: the destination, validity and scale of a row come from Policy::row_info (rows of one
   // tile may go to unrelated addresses); false: tile_base + row * row_pitch.
   static constexpr bool kRowScatter = false;
+  // 4: the CTA carries four more warps that run Policy::reducer_main next to the GEMM roles (work
+  // that consumes what peers' epilogues deliver, overlapped with this CTA's own tiles); 0: none.
+  static constexpr int kReducerWarps = 0;
+  template <class P>
+  __device__ static void reducer_main(const P&, const Problem&, int, int, int, int, uint64_t,
+                                      const volatile uint32_t*) {}
   // Row of B (and column of the accumulator grid) where n-tile nb starts.
   template <class P>
   __device__ static int b_row(const P&, const Problem&, int, int nb);
@@ -90,7 +106,7 @@ struct RowInfo {
 };
 
 template <class Policy>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kMaxThreads, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  const Problem g, const typename Policy::Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -108,6 +124,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     return;
   }
   const int cta = blockIdx.x - aux, num_ctas = gridDim.x - aux;
+  if (threadIdx.x == 0) trace_stamp(g, 0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { ptx::mbar_init(&pipe.full[s], 1); ptx::mbar_init(&pipe.empty[s], 1); }
@@ -204,6 +221,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         }
         if (ok) ptx::umma_commit(&pipe.acc_full[acc]);  // accumulator complete
       }
+      trace_stamp(g, 1);
     }
   } else if (warp == 6) {
     // ---------------------------------------------------------------- signal warp
@@ -225,6 +243,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         Policy::tile_done(p, g, mb, nb);
       }
     }
+  } else if (warp >= 7) {
+    // ---------------------------------------------------------------- reducer warps (policies that have them)
+    if constexpr (Policy::kReducerWarps > 0)
+      Policy::reducer_main(p, g, cta, num_ctas, warp - 7, lane, deadline, abort_flag);
+    if (warp == 7 && lane == 0) trace_stamp(g, 3);
   } else {
     // ---------------------------------------------------------------- epilogue (warps 2..5)
     const int quarter = warp & 3;                      // TMEM lanes [32*quarter, +32)
@@ -296,10 +319,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         }
       }
     }
+    if (warp == 2 && lane == 0) trace_stamp(g, 2);
   }
 
   ptx::tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) trace_stamp(g, 4);
   if (warp == 1) {
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc(tmem_base, kTmemCols);

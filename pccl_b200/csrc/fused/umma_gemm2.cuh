@@ -106,7 +106,7 @@ struct Pipe2 {
 };
 
 template <class Policy>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kMaxThreads, 1)
 umma_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                   const Problem g, const typename Policy::Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -126,6 +126,7 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     return;
   }
   const int pair = (blockIdx.x - aux) >> 1, num_pairs = (gridDim.x - aux) >> 1;
+  if (threadIdx.x == 0) trace_stamp(g, 0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages2; ++s) { ptx::mbar_init(&pipe.full[s], 2); ptx::mbar_init(&pipe.empty[s], 1); }
@@ -207,6 +208,7 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         }
         if (!failed) ptx2::umma_commit_pair(&pipe.acc_full[acc]);   // accumulator halves complete in both CTAs
       }
+      trace_stamp(g, 1);
     }
   } else if (warp == 6) {
     // ---------------------------------------------------------------- signal warp
@@ -227,6 +229,12 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         if (2 * mb2 + half < g.tiles_m) Policy::tile_done(p, g, 2 * mb2 + half, nb);
       }
     }
+  } else if (warp >= 7) {
+    // ---------------------------------------------------------------- reducer warps (policies that have them)
+    if constexpr (Policy::kReducerWarps > 0)
+      Policy::reducer_main(p, g, static_cast<int>(blockIdx.x) - aux, static_cast<int>(gridDim.x) - aux, warp - 7, lane,
+                           deadline, abort_flag);
+    if (warp == 7 && lane == 0) trace_stamp(g, 3);
   } else {
     // ---------------------------------------------------------------- epilogue (warps 2..5, both CTAs)
     const int quarter = warp & 3;
@@ -299,7 +307,9 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
           atomicAdd_block(&pipe.stored_count, 1u);
         }
       }
+      if (local_tile == 0 && warp == 2 && lane == 0) trace_stamp(g, 5);
     }
+    if (warp == 2 && lane == 0) trace_stamp(g, 2);
   }
 
   // A role that gave up may have left loads in flight or the partner mid-tile: give outstanding
@@ -310,6 +320,7 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   }
   ptx::tc_fence_before_sync();
   ptx2::cluster_sync();                      // the partner no longer reads this CTA's memory or barriers
+  if (threadIdx.x == 0) trace_stamp(g, 4);
   if (warp == 1) {
     ptx::tc_fence_after_sync();
     ptx2::tmem_dealloc_pair(tmem_base, kTmemCols);

@@ -262,6 +262,22 @@ def ensure_plan(kind: str, numel: int, dtype: torch.dtype, algorithm: Optional[s
     return name
 
 
+_route_cache: Dict[int, Tuple[Optional[str], Optional[int]]] = {}
+
+
+def _routed_allreduce(nbytes: int) -> Tuple[Optional[str], Optional[int]]:
+    """(algorithm, channels) the tuning file names for an all-reduce of this size, or (None, None)."""
+    if os.environ.get("PCCL_ALGO") is not None:
+        return None, None
+    route = tuned_route("allreduce", _state["world"], nbytes)
+    if route is None:
+        return None, None
+    choice = route["algorithm"]
+    if choice in ("ll", "push") or choice in ALGORITHMS:
+        return choice, route.get("channels")
+    return None, None
+
+
 def _plan_cache_dir() -> Optional[str]:
     where = os.environ.get("PCCL_PLAN_CACHE", os.path.expanduser("~/.pccl/plans"))
     return None if where.lower() in ("", "0", "off", "none") else where
@@ -314,19 +330,16 @@ def all_reduce(tensor: torch.Tensor, op: str = "sum", algorithm: Optional[str] =
     and sums of up to ``PUSH_MAX_BYTES`` through the fused push kernel (both: no plan, no staging copy,
     asynchronous on the current stream); everything else runs as a plan.
     """
-    if algorithm is None and op == "sum" and os.environ.get("PCCL_ALGO") is None:
+    if algorithm is None and op == "sum":
         # A measured table, when one covers this world size, says which path wins at this size
-        # (same file on every rank, so every rank takes the same path).
-        route = tuned_route("allreduce", _state["world"], tensor.numel() * tensor.element_size())
-        if route is not None:
-            choice = route["algorithm"]
-            if choice == "ll" and _ll_eligible(tensor, op, "ll"):
-                algorithm = "ll"
-            elif choice == "push" and _push_eligible(tensor, op, "push"):
-                algorithm = "push"
-            elif choice in ALGORITHMS:
-                algorithm = choice
-                channels = channels or route.get("channels")
+        # (same file on every rank, so every rank takes the same path).  Looked up once per size.
+        nbytes = tensor.numel() * tensor.element_size()
+        routed = _route_cache.get(nbytes)
+        if routed is None:
+            routed = _route_cache[nbytes] = _routed_allreduce(nbytes)
+        if routed[0] is not None and (routed[0] not in ("ll", "push") or
+                                      (_ll_eligible if routed[0] == "ll" else _push_eligible)(tensor, op, routed[0])):
+            algorithm, channels = routed[0], channels or routed[1]
     if _ll_eligible(tensor, op, algorithm):
         ll = _state["ll"]
         ll["epoch"] += 1
