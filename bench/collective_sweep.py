@@ -107,7 +107,7 @@ def run_multi(args):
         for dname in args.dtypes:
             dtype = DTYPES[dname]
             esize = torch.empty((), dtype=dtype).element_size()
-            for nbytes in sizes(args.min_bytes, args.max_bytes):
+            for nbytes in (args.sizes or sizes(args.min_bytes, args.max_bytes)):
                 numel = max(world * 8, nbytes // esize // (world * 8) * (world * 8))
                 full = pp.working_tensor(numel, dtype)
                 shard = numel // world
@@ -301,6 +301,7 @@ def main():
     ap.add_argument("--channels", default="auto")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--virtual-ranks", type=int, default=0)
+    ap.add_argument("--sizes", default=None, help="explicit list of sizes (e.g. 256K,16M,512M) instead of powers of two")
     ap.add_argument("--out", default=None, help="write every row to this JSON file (rank 0)")
     ap.add_argument("--write-tuning", default=None,
                     help="merge the fastest algorithm per size into this tuning file (the selector reads it)")
@@ -314,6 +315,9 @@ def main():
     args.channels = args.channels.split(",")
     args.min_bytes, args.max_bytes = parse_size(args.min_bytes), parse_size(args.max_bytes)
     args.check_bytes = parse_size(args.check_bytes)
+    args.sizes = [parse_size(x) for x in args.sizes.split(",")] if args.sizes else None
+    if args.sizes:
+        args.max_bytes = max(args.max_bytes, max(args.sizes))
     if args.virtual_ranks:
         run_virtual(args)
     else:

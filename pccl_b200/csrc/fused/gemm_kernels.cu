@@ -19,7 +19,9 @@ namespace gemm {
 namespace {
 
 uint32_t* g_error = nullptr;
-std::once_flag g_error_once;
+std::once_flag g_error_once, g_tail_once;
+float* g_tail_ws = nullptr;            // split-tail workspace and counters of the paired kernel (allocated on first use)
+uint32_t* g_tail_counters = nullptr;
 uint64_t* g_trace = nullptr;          // [kTraceCtas][kGemmTraceStamps], allocated by gemm_trace_enable
 constexpr int kTraceCtas = 256;
 
@@ -91,6 +93,8 @@ void launch(const MatrixDesc& a, const MatrixDesc& b, const typename Policy::Par
   g.tiles_n = (g.N + kBN - 1) / kBN;
   g.bn = kBN;
   g.trace = g_trace;
+  g.tail_first = g.num_items = g.tiles_m * g.tiles_n;         // the one-SM kernel never splits
+  g.tail_slices = 1; g.tail_kb = 0; g.tail_ws = nullptr; g.tail_counters = nullptr;
   g.error = error_word();
   g.timeout_ns = timeout_ms * 1000000ull;
   const CUtensorMap ta = make_map(a, kBM), tb = make_map(b, kBN);
@@ -149,6 +153,35 @@ void launch_pair(const MatrixDesc& a, const MatrixDesc& b, const typename Policy
   PCCL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2));
   const int pair_tiles = (g.tiles_m + 1) / 2 * g.tiles_n;
   if (grid - aux_ctas > 2 * pair_tiles) grid = 2 * pair_tiles + aux_ctas;
+  // Split tail: when the last round keeps at most half of the pairs busy, cut its tiles along K.
+  const int pairs = (grid - aux_ctas) / 2, k_blocks = (g.K + kBK - 1) / kBK;
+  g.tail_first = g.num_items = pair_tiles;
+  g.tail_slices = 1; g.tail_kb = k_blocks; g.tail_ws = nullptr; g.tail_counters = nullptr;
+  bool split = false;
+  if (Policy::kSplitTail && Environs::get_flag("PCCL_GEMM_SPLIT_TAIL", true) && pair_tiles > pairs && g.bn == kBN) {
+    const int tail = pair_tiles % pairs;
+    int slices = tail > 0 ? std::min(pairs / tail, k_blocks / 4) : 0;      // at least four k-blocks per slice
+    // Measured on B200: the workspace round trip costs about 8 us, half of a K=4096 tile, so two
+    // slices do not pay; from three slices on the shorter last round wins.
+    static const int min_slices = Environs::get_int("PCCL_GEMM_SPLIT_MIN_SLICES", 3);
+    if (tail > 0 && tail <= kTailMaxTiles && slices >= std::max(2, min_slices)) {
+      const int per = (k_blocks + slices - 1) / slices;
+      slices = (k_blocks + per - 1) / per;
+      std::call_once(g_tail_once, [] {
+        PCCL_CUDA(cudaMalloc(reinterpret_cast<void**>(&g_tail_ws),
+                             static_cast<size_t>(sm_count() / 2 + 1) * 2 * kBM * kBN * sizeof(float)));
+        PCCL_CUDA(cudaMalloc(reinterpret_cast<void**>(&g_tail_counters), 2 * kTailMaxTiles * sizeof(uint32_t)));
+        PCCL_CUDA(cudaMemset(g_tail_counters, 0, 2 * kTailMaxTiles * sizeof(uint32_t)));
+      });
+      g.tail_first = pair_tiles - tail;
+      g.tail_slices = slices;
+      g.tail_kb = per;
+      g.num_items = g.tail_first + tail * slices;
+      g.tail_ws = g_tail_ws;
+      g.tail_counters = g_tail_counters;
+      split = true;                                         // slices of a tile wait for one another: co-residency
+    }
+  }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kThreads + 32 * Policy::kReducerWarps);
@@ -160,7 +193,7 @@ void launch_pair(const MatrixDesc& a, const MatrixDesc& b, const typename Policy
   attrs[1].id = cudaLaunchAttributeCooperative;
   attrs[1].val.cooperative = 1;
   cfg.attrs = attrs;
-  cfg.numAttrs = cooperative && cooperative_launches() ? 2 : 1;
+  cfg.numAttrs = (cooperative || split) && cooperative_launches() ? 2 : 1;
   PCCL_CUDA(cudaLaunchKernelEx(&cfg, kernel, ta, tb, g, params));
 }
 
@@ -194,7 +227,11 @@ uint32_t read_error() {
   return v;
 }
 
-void clear_error() { PCCL_CUDA(cudaMemset(error_word(), 0, sizeof(uint32_t))); }
+void clear_error() {
+  PCCL_CUDA(cudaMemset(error_word(), 0, sizeof(uint32_t)));
+  // A launch that gave up may have left the split tail's counters mid-count.
+  if (g_tail_counters) PCCL_CUDA(cudaMemset(g_tail_counters, 0, 2 * kTailMaxTiles * sizeof(uint32_t)));
+}
 
 void gemm_bf16_nt(const MatrixDesc& a, const MatrixDesc& b, void* c, int64_t ldc, cudaStream_t stream, int ctas,
                   uint64_t timeout_ms, int sms_per_tile) {

@@ -193,6 +193,7 @@ struct ReduceScatterPolicy : PolicyDefaults {
 
 // ------------------------------------------------------------------------------------------------
 struct AllGatherPolicy : PolicyDefaults {
+  static constexpr bool kSplitTail = true;
   struct Params {
     PeerView peers;
     uint64_t gathered_off;      // heap offset of the gathered A [world * rows_per_rank][K] bf16 (per rank)
@@ -362,6 +363,7 @@ struct AllGatherPolicy : PolicyDefaults {
 // reaches memory and the element-wise kernel between the two GEMMs of the block disappears.
 struct AllGatherSwigluPolicy : AllGatherPolicy {
   static constexpr int kOutPer32 = 16;
+  static constexpr bool kSplitTail = false;        // the split tail sums plain accumulators only
   __device__ static void transform(const float* acc, float, float* out) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) {

@@ -52,8 +52,16 @@ struct Problem {
   // [0] kernel entered, [1] MMA issuer done with its last tile, [2] epilogue warps done,
   // [3] reducer warps done, [4] CTA leaves, [5] first accumulator complete.
   uint64_t* trace;
+  // Split tail of the paired kernel (tail_first >= the tile count: off).  Work items [0, tail_first)
+  // are whole tiles; each later tile is cut along K into tail_slices items of tail_kb k-blocks whose
+  // fp32 partial accumulators meet in tail_ws ([tile][slice][half][128][256] floats) and are summed
+  // by the warps that produced them (tail_counters: [0, 64) arrivals, [64, 128) finished, per tile).
+  int tail_first, tail_slices, tail_kb, num_items;
+  float* tail_ws;
+  uint32_t* tail_counters;
 };
 constexpr int kGemmTraceStamps = 8;
+constexpr int kTailMaxTiles = 64;
 __device__ __forceinline__ void trace_stamp(const Problem& g, int slot) {
   if (g.trace) g.trace[static_cast<uint64_t>(blockIdx.x) * kGemmTraceStamps + slot] = ptx::globaltimer();
 }
@@ -83,6 +91,9 @@ struct PolicyDefaults {
   // 4: the CTA carries four more warps that run Policy::reducer_main next to the GEMM roles (work
   // that consumes what peers' epilogues deliver, overlapped with this CTA's own tiles); 0: none.
   static constexpr int kReducerWarps = 0;
+  // true: the paired kernel may cut the tiles of its last, partly filled round along K (needs a
+  // static tile list, plain row addressing through tile_base / row_pitch and no per-tile signal).
+  static constexpr bool kSplitTail = false;
   template <class P>
   __device__ static void reducer_main(const P&, const Problem&, int, int, int, int, uint64_t,
                                       const volatile uint32_t*) {}
@@ -346,6 +357,7 @@ __device__ __forceinline__ uint4 pack8_bf16(const float* f) {
 }
 
 struct StorePolicy : PolicyDefaults {
+  static constexpr bool kSplitTail = true;
   struct Params {
     __nv_bfloat16* c;
     int64_t ldc;

@@ -22,6 +22,12 @@
 //     partner may still read its shared memory or signal its barriers).
 // Roles, policies, bounded waits and error reporting are those of umma_gemm_kernel.  Policies see
 // 128-row blocks as before: the pair processes blocks (2 i, 2 i + 1) of one n-tile together.
+// Split tail: tiles are handed out one per pair and round, so a tile count that is not a multiple of
+// the pair count leaves most pairs idle in the last round (8192 x 1792: 224 tiles on 74 pairs, two
+// tiles in round four).  When the launcher finds at most half the pairs busy in that round it cuts
+// each of those tiles along K into slices, one per idle pair; every slice writes its fp32 partial
+// accumulator to a workspace, counts itself in, waits (bounded) for the other slices of its tile,
+// and the warps of all slices then share the sum and the store of the tile.
 // The tile width is a launch parameter (Problem::bn, a multiple of 32 up to 256): the launcher
 // picks the width whose tile count divides best over the SM pairs, because with whole 256-column
 // tiles a shape like 8192 x 1792 leaves 3.03 rounds of work to be done in 4.
@@ -96,6 +102,26 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
 
 }  // namespace ptx2
 
+// One unit of a pair's work: a whole tile, or (in the split tail) k-blocks [kb_begin, kb_end) of one.
+struct WorkItem {
+  int tile, kb_begin, kb_end, slice;
+  bool partial;
+};
+__device__ __forceinline__ WorkItem decode_item(const Problem& g, int item, int k_blocks) {
+  WorkItem w;
+  if (item < g.tail_first) {
+    w.tile = item; w.kb_begin = 0; w.kb_end = k_blocks; w.slice = 0; w.partial = false;
+  } else {
+    const int j = item - g.tail_first;
+    w.tile = g.tail_first + j / g.tail_slices;
+    w.slice = j % g.tail_slices;
+    w.kb_begin = w.slice * g.tail_kb;
+    w.kb_end = min(k_blocks, w.kb_begin + g.tail_kb);
+    w.partial = true;
+  }
+  return w;
+}
+
 struct Pipe2 {
   uint64_t full[kStages2];      // used in the even CTA: 2 arrivals (one per CTA's producer) + 64 KB
   uint64_t empty[kStages2];     // one per CTA, released by the pair-wide commit
@@ -104,6 +130,116 @@ struct Pipe2 {
   uint32_t tmem_base;
   uint32_t stored_count;
 };
+
+// Epilogue of one K-slice of a split tile (one epilogue warp: TMEM lanes [32 quarter, +32) of this
+// CTA's half).  Both directions are coalesced: the partial accumulator goes through the warp's
+// staging buffer so that a store instruction writes whole 128-byte lines of the workspace, and in
+// the sum a load instruction reads 512 contiguous bytes of one row.  Returns false when a wait ran out.
+template <class Policy>
+__device__ __forceinline__ bool split_tail_epilogue(const typename Policy::Params& p, const Problem& g,
+                                                    const WorkItem& work, int mb2, int nb, int half, int quarter,
+                                                    int lane, uint32_t tmem_acc, uint64_t* acc_empty, uint8_t* stage_buf,
+                                                    uint64_t deadline, const volatile uint32_t* abort_flag) {
+  static_assert(Policy::kOutPer32 == 32, "the split tail sums plain accumulators");
+  const int t = work.tile - g.tail_first;                       // tail tile number
+  const int slices = g.tail_slices;
+  float* tile_ws = g.tail_ws + static_cast<size_t>(t) * slices * 2 * kBM * kBN;
+  // 1. this warp's 32 rows of the partial accumulator -> workspace (fp32, row-major, 256 floats per row)
+  float* rows = tile_ws + (static_cast<size_t>(work.slice * 2 + half) * kBM + quarter * 32) * kBN;
+  const uint32_t taddr = tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+  for (int c = 0; c < g.bn; c += 32) {
+    uint32_t v[32];
+    ptx::tmem_ld_32x32b_x32(taddr + c, v);
+    ptx::tmem_ld_wait();
+    // lane = row: 8 chunks of 16 bytes, chunk index XOR-swizzled by the row against bank conflicts
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      *reinterpret_cast<uint4*>(stage_buf + lane * 128 + ((i ^ (lane & 7)) * 16)) =
+          make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    __syncwarp();
+    // 8 lanes write one row's 128 bytes, 4 rows per instruction
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int r = it * 4 + lane / 8, j = lane % 8;
+      const uint4 val = *reinterpret_cast<const uint4*>(stage_buf + r * 128 + ((j ^ (r & 7)) * 16));
+      *reinterpret_cast<uint4*>(rows + static_cast<size_t>(r) * kBN + c + 4 * j) = val;
+    }
+    __syncwarp();
+  }
+  ptx::tc_fence_before_sync();
+  __syncwarp();
+  uint32_t* arrived = g.tail_counters + t;
+  uint32_t* finished = g.tail_counters + kTailMaxTiles + t;
+  const uint32_t everyone = 8u * static_cast<uint32_t>(slices);  // 4 warps x 2 CTAs x slices
+  uint32_t ok = 1;
+  if (lane == 0) {
+    ptx2::mbar_arrive_leader(acc_empty);                         // the accumulator is free again
+    ptx::fence_gpu();
+    ptx::red_release_gpu_add(arrived, 1u);
+    // 2. wait until every slice of this tile is in the workspace
+    uint32_t spins = 0;
+    while (ptx::ld_acquire_gpu(arrived) < everyone) {
+      if ((++spins & 63u) == 0u && (*abort_flag || ptx::globaltimer() > deadline)) { ok = 0; break; }
+      __nanosleep(40);
+    }
+  }
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  if (!ok) return false;
+  // 3. sum the slices.  Unit = 128 consecutive floats of one of the tile's 256 rows (a lane owns 4 of
+  //    them); the warps of all slices take units round-robin.
+  const int segments = g.bn / 128;
+  const int units = 2 * kBM * segments;
+  const int wid = (work.slice * 2 + half) * 4 + quarter, warps = static_cast<int>(everyone);
+  //    Eight units are in flight at a time so that the loop pays one L2 round trip per slice, not per unit.
+  constexpr int kBatch = 8;
+  const size_t slice_pitch = static_cast<size_t>(2) * kBM * kBN;
+  for (int u0 = wid; u0 < units; u0 += kBatch * warps) {
+    float acc[kBatch][4];
+    size_t at[kBatch];
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b) {
+      const int u = min(u0 + b * warps, units - 1);               // clamped: extra lanes re-read a valid unit
+      at[b] = static_cast<size_t>(u / segments) * kBN + (u % segments) * 128 + lane * 4;
+      acc[b][0] = acc[b][1] = acc[b][2] = acc[b][3] = 0.f;
+    }
+#pragma unroll 1
+    for (int s = 0; s < slices; ++s) {
+      uint4 raw[kBatch];
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b) raw[b] = ptx::ld_local_v4(tile_ws + s * slice_pitch + at[b]);
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b) {
+        acc[b][0] += __uint_as_float(raw[b].x); acc[b][1] += __uint_as_float(raw[b].y);
+        acc[b][2] += __uint_as_float(raw[b].z); acc[b][3] += __uint_as_float(raw[b].w);
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b) {
+      const int u = u0 + b * warps;
+      if (u >= units) break;
+      const int row256 = u / segments, seg = u % segments;
+      const int mb = 2 * mb2 + row256 / kBM, r = row256 % kBM;
+      const int col = nb * g.bn + seg * 128 + lane * 4;
+      if (mb >= g.tiles_m || mb * kBM + r >= g.M || col >= g.N) continue;
+      uint8_t* dst = Policy::tile_base(p, g, mb) + static_cast<int64_t>(r) * Policy::row_pitch(p, g);
+      __nv_bfloat162 lo = __floats2bfloat162_rn(acc[b][0], acc[b][1]), hi = __floats2bfloat162_rn(acc[b][2], acc[b][3]);
+      uint2 packed;
+      packed.x = *reinterpret_cast<uint32_t*>(&lo);
+      packed.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(dst + static_cast<int64_t>(col) * 2) = packed;   // N % 8 == 0: 4 columns never straddle N
+    }
+  }
+  // 4. the last warp to finish puts the tile's counters back to zero for the next launch
+  __syncwarp();
+  if (lane == 0) {
+    if (atomicAdd(finished, 1u) + 1u == everyone) {
+      atomicExch(arrived, 0u);
+      atomicExch(finished, 0u);
+    }
+  }
+  return true;
+}
 
 template <class Policy>
 __global__ void __launch_bounds__(kMaxThreads, 1)
@@ -150,20 +286,22 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
 
   // The pair walks the policy's order of 256-row blocks: block pair i = 128-row blocks 2i, 2i+1.
   const int tiles_m = Policy::prepare(p, g, deadline, abort_flag);
-  const int num_tiles = tiles_m < 0 ? 0 : (g.tiles_m + 1) / 2 * g.tiles_n;
   const int k_blocks = (g.K + kBK - 1) / kBK;
+  const bool split = Policy::kSplitTail && g.tail_first < (g.tiles_m + 1) / 2 * g.tiles_n;
+  const int num_tiles = tiles_m < 0 ? 0 : (split ? g.num_items : (g.tiles_m + 1) / 2 * g.tiles_n);
   bool failed = false;
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer (both CTAs)
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
-      for (int tile = pair; tile < num_tiles && !failed; tile += num_pairs) {
+      for (int item = pair; item < num_tiles && !failed; item += num_pairs) {
+        const WorkItem work = split ? decode_item(g, item, k_blocks) : WorkItem{item, 0, k_blocks, 0, false};
         int mb2, nb;
-        Policy::pair_coords(p, g, tile, &mb2, &nb);
+        Policy::pair_coords(p, g, work.tile, &mb2, &nb);
         const int mb = 2 * mb2 + half;
         if (!Policy::before_load(p, g, mb, deadline, abort_flag)) { raise_error(g, kErrPolicyWait, 0); failed = true; break; }
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = work.kb_begin; kb < work.kb_end; ++kb) {
           if (!ptx::mbar_wait(&pipe.empty[stage], phase ^ 1u, deadline, abort_flag)) {
             raise_error(g, kErrProducerWait, 0); failed = true; break;
           }
@@ -183,14 +321,15 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       const uint32_t idesc = ptx::umma_idesc_f32(2 * kBM, static_cast<uint32_t>(g.bn), true);
       uint32_t stage = 0, phase = 0;
       uint32_t local_tile = 0;
-      for (int tile = pair; tile < num_tiles && !failed; tile += num_pairs, ++local_tile) {
+      for (int item = pair; item < num_tiles && !failed; item += num_pairs, ++local_tile) {
+        const WorkItem work = split ? decode_item(g, item, k_blocks) : WorkItem{item, 0, k_blocks, 0, false};
         const uint32_t acc = local_tile & 1u, acc_phase = (local_tile >> 1) & 1u;
         if (!ptx::mbar_wait(&pipe.acc_empty[acc], acc_phase ^ 1u, deadline, abort_flag)) {
           raise_error(g, kErrMmaWait, 1); failed = true; break;
         }
         ptx::tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * kBN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = work.kb_begin; kb < work.kb_end; ++kb) {
           if (!ptx::mbar_wait(&pipe.full[stage], phase, deadline, abort_flag)) {
             raise_error(g, kErrMmaWait, 1); failed = true; break;
           }
@@ -201,7 +340,7 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
           for (int k = 0; k < kBK / kUmmaK; ++k) {
             const uint64_t da = ptx::umma_desc_k_sw128(a_addr + k * kUmmaK * 2);
             const uint64_t db = ptx::umma_desc_k_sw128(b_addr + k * kUmmaK * 2);
-            ptx2::umma_f16_pair(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            ptx2::umma_f16_pair(tmem_d, da, db, idesc, (kb != work.kb_begin || k != 0) ? 1u : 0u);
           }
           ptx2::umma_commit_pair(&pipe.empty[stage]);       // frees the stage in both CTAs
           if (++stage == kStages2) { stage = 0; phase ^= 1u; }
@@ -239,10 +378,11 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     // ---------------------------------------------------------------- epilogue (warps 2..5, both CTAs)
     const int quarter = warp & 3;
     uint32_t local_tile = 0;
-    for (int tile = pair; tile < num_tiles; tile += num_pairs, ++local_tile) {
+    for (int item = pair; item < num_tiles; item += num_pairs, ++local_tile) {
+      const WorkItem work = split ? decode_item(g, item, k_blocks) : WorkItem{item, 0, k_blocks, 0, false};
       const uint32_t acc = local_tile & 1u, acc_phase = (local_tile >> 1) & 1u;
       int mb2, nb;
-      Policy::pair_coords(p, g, tile, &mb2, &nb);
+      Policy::pair_coords(p, g, work.tile, &mb2, &nb);
       const int mb = 2 * mb2 + half;
       uint32_t ok = 1;
       if (lane == 0) ok = ptx::mbar_wait(&pipe.acc_full[acc], acc_phase, deadline, abort_flag) ? 1u : 0u;
@@ -250,6 +390,18 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       if (!ok) { if (lane == 0) raise_error(g, kErrEpilogueWait, 2); break; }
       ptx::tc_fence_after_sync();
       constexpr int kOut = Policy::kOutPer32;
+      if constexpr (Policy::kSplitTail) {
+        if (work.partial) {
+          if (!split_tail_epilogue<Policy>(p, g, work, mb2, nb, half, quarter, lane, tmem_base + acc * kBN,
+                                           &pipe.acc_empty[acc],
+                                           smem + kStages2 * kStageBytes2 + (warp - 2) * kEpiWarpBytes, deadline,
+                                           abort_flag)) {
+            if (lane == 0) raise_error(g, kErrEpilogueWait, 9);
+            break;
+          }
+          continue;
+        }
+      }
       constexpr int kRowBytes = kEpiCols / 32 * kOut * 2;
       constexpr int kChunks = kRowBytes / 16;
       constexpr int kRowsPerSt = 32 / kChunks;
