@@ -29,6 +29,10 @@ namespace gemm {
 namespace {
 
 constexpr int kThreadsNorm = 256;
+// Resident CTAs per SM.  A CTA alternates a load phase and a store phase around a block barrier, and a thread
+// has only two or three 16-byte loads in flight, so DRAM and NVLink stay busy only when several CTAs overlap
+// on an SM: two per SM reached 30 % of DRAM throughput in a profile, five are what 48 registers allow.
+constexpr int kNormCtasPerSm = 5;
 
 struct NormParams {
   PeerBases peers;
@@ -93,7 +97,7 @@ __device__ __forceinline__ void pull_sum(const NormParams& p, uint64_t offset, f
   }
 }
 
-__global__ void __launch_bounds__(kThreadsNorm) ar_residual_rmsnorm_kernel(const NormParams p) {
+__global__ void __launch_bounds__(kThreadsNorm, kNormCtasPerSm) ar_residual_rmsnorm_kernel(const NormParams p) {
   extern __shared__ float h_row[];            // hidden fp32 values of the current token
   __shared__ float warp_sums[kThreadsNorm / 32];
   __shared__ uint32_t s_ok;
@@ -219,7 +223,7 @@ void ar_residual_rmsnorm(const PeerBases& peers, uint8_t* mc_base, uint64_t x_of
   int sms = 0, dev = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  int grid = ctas > 0 ? ctas : (mine < 2 * sms ? mine : 2 * sms);
+  int grid = ctas > 0 ? ctas : (mine < kNormCtasPerSm * sms ? mine : kNormCtasPerSm * sms);
   if (grid < 1) grid = 1;
   // The grid size is part of the completion count: it must not change between calls of one
   // operator instance (the Python wrapper fixes tokens per instance).
