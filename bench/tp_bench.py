@@ -137,10 +137,12 @@ def main():
                 return torch.nn.functional.rms_norm(resid, (h,), gamma, 1e-5)
 
             t_unfused = timed(unfused_norm, args.iters, flush)
-            # bytes that must cross NVLink per GPU (two-shot: send and receive (W-1)/W of x, then of y and h)
-            link_bytes = (world - 1) / world * tokens * h * 2 * 3
-            local_bytes = tokens * h * 2 * 4 / world
-            roof_ms = max(link_bytes / (link_gbs * 1e9), local_bytes / (hbm_gbs * 1e9)) * 1e3
+            # bytes that must cross NVLink per GPU and direction: (W-1)/W of x for the reduction and (W-1)/W of
+            # h for the delivery (y is computed where it is used); the local pass reads x, the residual and
+            # h once and writes h and y
+            link_bytes = (world - 1) / world * tokens * h * 2 * 2
+            local_bytes = tokens * h * 2 * (3 / world + 3)
+            roof_ms = (link_bytes / (link_gbs * 1e9) + local_bytes / (hbm_gbs * 1e9)) * 1e3
             results.append({"op": "ar_residual_rmsnorm", "tokens": tokens, "hidden": h, "world": world,
                             "path": "nvls" if use_nvls else "peer", "fused_ms": round(t_fused, 4),
                             "unfused_nccl_torch_ms": round(t_unfused, 4),

@@ -7,9 +7,12 @@
 // x lives in symmetric memory.  Tokens are split over the ranks ("two-shot": a rank reduces
 // its T/W tokens and delivers y and h for them to every rank) unless T is too small to split,
 // in which case every rank reduces every token itself ("one-shot", nothing to deliver).
+// Only h crosses the fabric: a rank delivers the h rows of its tokens to every rank and, once all
+// ranks have delivered, every rank normalises the rows it received itself (one local read of h,
+// one local write of y), which halves the NVLink bytes against delivering y as well.
 // With NVLS the reduction is one multimem.ld_reduce per 16 bytes (the switch sums the ranks'
 // copies, fp32 accumulation) and the delivery one multimem.st; without it the kernel pulls the
-// peers' rows with 16-byte loads and pushes results with plain peer stores.
+// peers' rows with 16-byte loads and pushes h with plain peer stores.
 // Synchronisation: call-counting flags in symmetric memory ("my x is in place", "I have
 // delivered / finished reading"), bounded waits, error word on timeout.
 // The unfused baseline is NCCL all-reduce + torch add + RMSNorm; the reference has no such op.
@@ -127,6 +130,19 @@ __global__ void __launch_bounds__(kThreadsNorm, kNormCtasPerSm) ar_residual_rmsn
   const bool use_mc = p.mc_base != nullptr;
   uint8_t* self = p.peers.base[me];
 
+  // Sum of squares of the row now in h_row -> the row's scale; y = h * scale * gamma, stored locally.
+  auto row_scale = [&](float ss) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < kThreadsNorm / 32; ++w) total += warp_sums[w];
+    return rsqrtf(total / static_cast<float>(p.hidden) + p.eps);
+  };
+
+  // 2a. own tokens: h = residual + sum of the ranks' x; h goes to every rank, y stays here.
   for (int t = first + blockIdx.x; t < first + per_rank; t += gridDim.x) {
     const uint64_t row = static_cast<uint64_t>(t) * row_bytes;
     float ss = 0.f;
@@ -145,42 +161,35 @@ __global__ void __launch_bounds__(kThreadsNorm, kNormCtasPerSm) ar_residual_rmsn
       } else {
         pull_sum<8>(p, row + v * 16, acc);
       }
+      // The residual stream is bf16: the norm is taken of the rounded values, as every rank will read them.
+      const uint4 hp = pack8(acc);
+      unpack8(hp, acc);
 #pragma unroll
       for (int i = 0; i < 8; ++i) { h_row[v * 8 + i] = acc[i]; ss += acc[i] * acc[i]; }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = ss;
-    __syncthreads();
-    float total = 0.f;
-#pragma unroll
-    for (int w = 0; w < kThreadsNorm / 32; ++w) total += warp_sums[w];
-    const float scale = rsqrtf(total / static_cast<float>(p.hidden) + p.eps);
-    for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
-      float g[8], hv[8], yv[8];
-      unpack8(*reinterpret_cast<const uint4*>(p.gamma + v * 8), g);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) { hv[i] = h_row[v * 8 + i]; yv[i] = hv[i] * scale * g[i]; }
-      const uint4 hp = pack8(hv), yp = pack8(yv);
       if (p.one_shot) {
         ptx::st_v4(self + p.res_off + row + v * 16, hp);
-        ptx::st_v4(self + p.y_off + row + v * 16, yp);
       } else if (use_mc) {
         ptx::mm_st_v4(p.mc_base + p.res_off + row + v * 16, hp);
-        ptx::mm_st_v4(p.mc_base + p.y_off + row + v * 16, yp);
       } else {
         for (int i = 0; i < world; ++i) {
           const int r = (me + i) % world;
           ptx::st_v4(p.peers.base[r] + p.res_off + row + v * 16, hp);
-          ptx::st_v4(p.peers.base[r] + p.y_off + row + v * 16, yp);
         }
       }
+    }
+    const float scale = row_scale(ss);
+    for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+      float g[8], yv[8];
+      unpack8(*reinterpret_cast<const uint4*>(p.gamma + v * 8), g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) yv[i] = h_row[v * 8 + i] * scale * g[i];
+      ptx::st_v4(self + p.y_off + row + v * 16, pack8(yv));
     }
     __syncthreads();
   }
 
-  // 3. "delivered / done reading" -> every peer, once all CTAs of this rank are through;
-  //    the last CTA then waits for every peer's, so that y and h are complete on return.
+  // 3. "delivered / done reading" -> every peer, once all CTAs of this rank are through; every CTA
+  //    then waits for every peer's: the other ranks' h rows are in this rank's memory after that.
   __syncthreads();
   if (threadIdx.x == 0) {
     // GPU scope suffices here: the CTA that completes the count fences at system scope before it posts,
@@ -191,11 +200,39 @@ __global__ void __launch_bounds__(kThreadsNorm, kNormCtasPerSm) ar_residual_rmsn
     s_ok = done == p.epoch * gridDim.x ? 2u : 1u;
   }
   __syncthreads();
-  if (s_ok != 2u) return;
-  if (static_cast<int>(threadIdx.x) < world && static_cast<int>(threadIdx.x) != me) {
+  if (s_ok == 2u && static_cast<int>(threadIdx.x) < world && static_cast<int>(threadIdx.x) != me) {
     ptx::fence_sys();
     ptx::red_release_sys_add(reinterpret_cast<uint32_t*>(p.peers.base[threadIdx.x] + p.flags_off) + world + me, 1u);
-    if (!wait_ge(my_flags + world + threadIdx.x, p.epoch, deadline, abort_flag)) atomicCAS(p.error, 0u, 0x602u);
+  }
+  __syncthreads();
+  if (static_cast<int>(threadIdx.x) < world && static_cast<int>(threadIdx.x) != me) {
+    if (!wait_ge(my_flags + world + threadIdx.x, p.epoch, deadline, abort_flag)) { s_ok = 0; atomicCAS(p.error, 0u, 0x602u); }
+  }
+  __syncthreads();
+  if (!s_ok || p.one_shot) return;
+
+  // 2b. the other ranks' tokens: their h rows arrived above; the norm is local work (one read of h,
+  //     one write of y), so y never crosses NVLink.
+  const int others = p.tokens - per_rank;
+  for (int i = blockIdx.x; i < others; i += gridDim.x) {
+    const int t = i < first ? i : i + per_rank;
+    const uint64_t row = static_cast<uint64_t>(t) * row_bytes;
+    float ss = 0.f;
+    for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+      float acc[8];
+      unpack8(ptx::ld_peer_v4(self + p.res_off + row + v * 16), acc);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) { h_row[v * 8 + k] = acc[k]; ss += acc[k] * acc[k]; }
+    }
+    const float scale = row_scale(ss);
+    for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+      float g[8], yv[8];
+      unpack8(*reinterpret_cast<const uint4*>(p.gamma + v * 8), g);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) yv[k] = h_row[v * 8 + k] * scale * g[k];
+      ptx::st_v4(self + p.y_off + row + v * 16, pack8(yv));
+    }
+    __syncthreads();
   }
 }
 
