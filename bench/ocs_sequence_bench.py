@@ -3,14 +3,17 @@
     python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 bench/ocs_sequence_bench.py \
         [--elements 1048576] [--iterations 50] [--connectors tensor,nvlink]
 
-The sequence all-reduce -> all-to-all -> all-reduce is run four ways on the same input:
+The sequence all-reduce -> all-to-all -> all-reduce is run five ways on the same input:
   native            three `torch.distributed` (NCCL) calls, no boundaries;
   torch_plan        `OcsTorchPlanRunner`: the same calls with an OCS barrier-and-switch after the
                     first and the second (the comparison of the reference's
                     tests/bench_ocs_torch_overhead.py:105-200);
   engine_plan       `OcsCollectivePlanRunner` over this library's engine: every phase is a compiled
-                    ring plan, registered and executed through register_operation /
-                    execute_operation, with the same barriers and a signal reset after each;
+                    ring plan, registered (once; later executions reuse the registration) and
+                    executed through register_operation / execute_operation, with the same barriers
+                    and a signal reset after each;
+  engine_plan_switched  the same runner over two-shot all-reduce and direct all-to-all plans, the
+                    templates made for a switched fabric;
   engine_native     the three engine plans run back to back without barriers.
 Each iteration is timed on the host between two device synchronisations; per iteration the
 slowest rank counts; median and p95 over iterations.  Results of all four are checked against the
@@ -59,7 +62,8 @@ def main():
     import pccl_b200.parallel as pp
     from pccl_b200.ocs import (NvlinkSwitchConnector, OcsCollectivePlanRunner, OCSRuntime, OcsTorchPlanRunner,
                                TensorSwitchConnector, TorchDistributedSwitchConnector,
-                               build_ring_allreduce_alltoall_plan, build_torch_allreduce_alltoall_plan)
+                               build_ring_allreduce_alltoall_plan, build_switched_allreduce_alltoall_plan,
+                               build_torch_allreduce_alltoall_plan)
     pp.init()
     x = torch.full((args.elements,), float(rank + 1), device="cuda")
     # every element: sum of ranks' values, exchanged (unchanged: all equal), summed again
@@ -114,6 +118,15 @@ def main():
         barriers = [float(r["latency_us"]) for r in runtime.history[2 * args.warmup:]]
         results.append(("engine_plan", label, lat, slowest_rank(barriers)))
         engine_files = prepared[0]
+
+        # The same sequence with the templates made for a switched fabric (two-shot, direct all-to-all).
+        runtime = OCSRuntime(connector=connector)
+        switched_runner = OcsCollectivePlanRunner(engine=pccl.engine, runtime=runtime)
+        switched = switched_runner.prepare(
+            build_switched_allreduce_alltoall_plan(rank, world, args.elements, "float32", "sm"), f"sw{label}")
+        lat = timed(lambda i: switched_runner.execute(switched, x))
+        barriers = [float(r["latency_us"]) for r in runtime.history[2 * args.warmup:]]
+        results.append(("engine_plan_switched", label, lat, slowest_rank(barriers)))
 
     if engine_files is not None:
         names = list(engine_files.operation_names)

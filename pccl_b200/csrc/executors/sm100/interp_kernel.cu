@@ -319,8 +319,9 @@ __global__ void __launch_bounds__(kInterpThreads, 1) plan_interp_kernel(const La
         ptx::red_release_sys_add(P.signals[ref.rank] + ref.slot, 1u);
       }
       if (threadIdx.x == 0) {
-        ptx::fence_gpu();
-        ptx::st_release_sys(P.chain_progress + chain_id, progress_base + k + 1);
+        // Read by other chains of this GPU only: GPU scope.  (A system-scope release here waited for
+        // the acknowledgement of the notify just posted over NVLink: 3 us per step in a timeline.)
+        ptx::st_release_gpu(P.chain_progress + chain_id, progress_base + k + 1);
       }
     }
     if (trace) trace[k * kTraceStamps + 3] = ptx::globaltimer();

@@ -34,8 +34,9 @@ namespace {
 constexpr int kThreadsNorm = 256;
 // Resident CTAs per SM.  A CTA alternates a load phase and a store phase around a block barrier, and a thread
 // has only two or three 16-byte loads in flight, so DRAM and NVLink stay busy only when several CTAs overlap
-// on an SM: two per SM reached 30 % of DRAM throughput in a profile, five are what 48 registers allow.
-constexpr int kNormCtasPerSm = 5;
+// on an SM: two per SM reached 30 % of DRAM throughput in a profile; four leave 64 registers per thread,
+// enough to keep two 16-byte groups of a row in flight.
+constexpr int kNormCtasPerSm = 4;
 
 struct NormParams {
   PeerBases peers;
@@ -81,23 +82,63 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-// acc += sum over ranks of x_r[offset .. offset + 16).  All kW loads are issued unconditionally
-// before the first add (slots past the world re-read the own row and are not added): a
-// conditionally assigned register makes the compiler wait for each load in turn.
-template <int kW>
-__device__ __forceinline__ void pull_sum(const NormParams& p, uint64_t offset, float* acc) {
+// h = residual + sum over ranks of x for one token row: h (rounded to bf16, as every rank will read
+// it) goes to h_row and to every rank's residual buffer; returns this thread's share of sum(h^2).
+// kW: 0 = in-switch reduction (one multimem.ld_reduce per 16 bytes), else the number of peer loads
+// issued per 16 bytes (slots past the world re-read the own row and are not added).  kB 16-byte
+// groups are in flight per thread: every load is issued, unconditionally and from a clamped
+// address, before the first use, since a conditionally assigned register or a store between two
+// loads makes each load wait for the one before.
+template <int kW, int kB>
+__device__ __forceinline__ float sum_row(const NormParams& p, uint64_t row, int vecs, float* h_row) {
+  constexpr int kLoads = kW > 0 ? kW : 1;
   const int me = p.peers.rank, world = p.peers.world;
-  uint4 raw[kW];
+  uint8_t* self = p.peers.base[me];
+  float ss = 0.f;
+  for (int v0 = threadIdx.x; v0 < vecs; v0 += kB * kThreadsNorm) {
+    uint4 res[kB], x[kB][kLoads];
+    int v[kB];
 #pragma unroll
-  for (int r = 0; r < kW; ++r) raw[r] = ptx::ld_peer_v4(p.peers.base[r < world ? r : me] + p.x_off + offset);
+    for (int b = 0; b < kB; ++b) v[b] = v0 + b * kThreadsNorm < vecs ? v0 + b * kThreadsNorm : v0;
 #pragma unroll
-  for (int r = 0; r < kW; ++r) {
-    if (r >= world) break;
-    float f[8];
-    unpack8(raw[r], f);
+    for (int b = 0; b < kB; ++b) res[b] = ptx::ld_local_v4(self + p.res_off + row + v[b] * 16);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] += f[i];
+    for (int b = 0; b < kB; ++b) {
+      if constexpr (kW == 0) {
+        x[b][0] = ptx::mm_ld_reduce_add_bf16(p.mc_base + p.x_off + row + v[b] * 16);
+      } else {
+#pragma unroll
+        for (int r = 0; r < kW; ++r)
+          x[b][r] = ptx::ld_peer_v4(p.peers.base[r < world ? r : me] + p.x_off + row + v[b] * 16);
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < kB; ++b) {
+      if (b > 0 && v0 + b * kThreadsNorm >= vecs) break;
+      float acc[8], f[8];
+      unpack8(res[b], acc);
+#pragma unroll
+      for (int r = 0; r < kLoads; ++r) {
+        if (kW > 0 && r >= world) break;
+        unpack8(x[b][r], f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += f[i];
+      }
+      const uint4 hp = pack8(acc);
+      unpack8(hp, acc);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { h_row[v[b] * 8 + i] = acc[i]; ss += acc[i] * acc[i]; }
+      const uint64_t at = p.res_off + row + v[b] * 16;
+      if (p.one_shot) {
+        ptx::st_v4(self + at, hp);
+      } else if (kW == 0) {
+        ptx::mm_st_v4(p.mc_base + at, hp);
+      } else {
+        for (int i = 0; i < world; ++i) ptx::st_v4(p.peers.base[(me + i) % world] + at, hp);
+      }
+    }
   }
+  return ss;
 }
 
 __global__ void __launch_bounds__(kThreadsNorm, kNormCtasPerSm) ar_residual_rmsnorm_kernel(const NormParams p) {
@@ -145,38 +186,11 @@ __global__ void __launch_bounds__(kThreadsNorm, kNormCtasPerSm) ar_residual_rmsn
   // 2a. own tokens: h = residual + sum of the ranks' x; h goes to every rank, y stays here.
   for (int t = first + blockIdx.x; t < first + per_rank; t += gridDim.x) {
     const uint64_t row = static_cast<uint64_t>(t) * row_bytes;
-    float ss = 0.f;
-    for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
-      float acc[8];
-      unpack8(ptx::ld_local_v4(self + p.res_off + row + v * 16), acc);
-      if (use_mc) {
-        float f[8];
-        unpack8(ptx::mm_ld_reduce_add_bf16(p.mc_base + p.x_off + row + v * 16), f);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] += f[i];
-      } else if (world <= 2) {
-        pull_sum<2>(p, row + v * 16, acc);
-      } else if (world <= 4) {
-        pull_sum<4>(p, row + v * 16, acc);
-      } else {
-        pull_sum<8>(p, row + v * 16, acc);
-      }
-      // The residual stream is bf16: the norm is taken of the rounded values, as every rank will read them.
-      const uint4 hp = pack8(acc);
-      unpack8(hp, acc);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) { h_row[v * 8 + i] = acc[i]; ss += acc[i] * acc[i]; }
-      if (p.one_shot) {
-        ptx::st_v4(self + p.res_off + row + v * 16, hp);
-      } else if (use_mc) {
-        ptx::mm_st_v4(p.mc_base + p.res_off + row + v * 16, hp);
-      } else {
-        for (int i = 0; i < world; ++i) {
-          const int r = (me + i) % world;
-          ptx::st_v4(p.peers.base[r] + p.res_off + row + v * 16, hp);
-        }
-      }
-    }
+    float ss;
+    if (use_mc) ss = sum_row<0, 2>(p, row, vecs, h_row);
+    else if (world <= 2) ss = sum_row<2, 2>(p, row, vecs, h_row);
+    else if (world <= 4) ss = sum_row<4, 1>(p, row, vecs, h_row);
+    else ss = sum_row<8, 1>(p, row, vecs, h_row);
     const float scale = row_scale(ss);
     for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
       float g[8], yv[8];
@@ -218,11 +232,19 @@ __global__ void __launch_bounds__(kThreadsNorm, kNormCtasPerSm) ar_residual_rmsn
     const int t = i < first ? i : i + per_rank;
     const uint64_t row = static_cast<uint64_t>(t) * row_bytes;
     float ss = 0.f;
-    for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+    for (int v0 = threadIdx.x; v0 < vecs; v0 += 2 * kThreadsNorm) {
+      const int v1 = v0 + kThreadsNorm < vecs ? v0 + kThreadsNorm : v0;
+      const uint4 raw0 = ptx::ld_peer_v4(self + p.res_off + row + v0 * 16);
+      const uint4 raw1 = ptx::ld_peer_v4(self + p.res_off + row + v1 * 16);
       float acc[8];
-      unpack8(ptx::ld_peer_v4(self + p.res_off + row + v * 16), acc);
+      unpack8(raw0, acc);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) { h_row[v * 8 + k] = acc[k]; ss += acc[k] * acc[k]; }
+      for (int k = 0; k < 8; ++k) { h_row[v0 * 8 + k] = acc[k]; ss += acc[k] * acc[k]; }
+      if (v1 != v0) {
+        unpack8(raw1, acc);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { h_row[v1 * 8 + k] = acc[k]; ss += acc[k] * acc[k]; }
+      }
     }
     const float scale = row_scale(ss);
     for (int v = threadIdx.x; v < vecs; v += blockDim.x) {

@@ -130,11 +130,13 @@ int pick_tile_n(int, int, int) { return kBN; }
 // The two-SM kernel: clusters of two CTAs, each CTA loading 128-row boxes of A and of B.
 template <class Policy>
 void launch_pair(const MatrixDesc& a, const MatrixDesc& b, const typename Policy::Params& params, int ctas,
-                 uint64_t timeout_ms, cudaStream_t stream, bool cooperative, int aux_ctas = 0) {
+                 uint64_t timeout_ms, cudaStream_t stream, bool cooperative, int aux_ctas = 0, int groups = 1) {
+  // groups > 1: B stacks `groups` weight matrices of N rows each and the tile list is built on the
+  // device (ragged pairs), so the grid is not trimmed to a tile count known here.
   PCCL_CHECK(a.cols == b.cols, "GEMM: A and B disagree on K (" << a.cols << " vs " << b.cols << ")");
-  PCCL_CHECK(a.cols % 8 == 0 && b.rows % 8 == 0, "GEMM: K and N must be multiples of 8");
+  PCCL_CHECK(a.cols % 8 == 0 && b.rows % groups == 0 && b.rows / groups % 8 == 0, "GEMM: K and N must be multiples of 8");
   Problem g;
-  g.M = a.rows; g.N = b.rows; g.K = a.cols;
+  g.M = a.rows; g.N = b.rows / groups; g.K = a.cols;
   g.tiles_m = (g.M + kBM - 1) / kBM;
   PCCL_CHECK(aux_ctas % 2 == 0, "paired GEMM: auxiliary CTAs come in whole clusters of two");
   int grid = ctas > 0 ? ctas : sm_count();
@@ -152,7 +154,7 @@ void launch_pair(const MatrixDesc& a, const MatrixDesc& b, const typename Policy
   auto kernel = umma_gemm2_kernel<Policy>;
   PCCL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2));
   const int pair_tiles = (g.tiles_m + 1) / 2 * g.tiles_n;
-  if (grid - aux_ctas > 2 * pair_tiles) grid = 2 * pair_tiles + aux_ctas;
+  if (groups == 1 && grid - aux_ctas > 2 * pair_tiles) grid = 2 * pair_tiles + aux_ctas;
   // Split tail: when the last round keeps at most half of the pairs busy, cut its tiles along K.
   const int pairs = (grid - aux_ctas) / 2, k_blocks = (g.K + kBK - 1) / kBK;
   g.tail_first = g.num_items = pair_tiles;
@@ -332,6 +334,9 @@ void all_gather_gemm(const PeerBases& peers, uint64_t gathered_off, int M, int K
 }
 
 namespace {
+// SMs per tile of the expert GEMMs: 2 (SM pairs, the default) or 1; read per call so that tests can flip it.
+int moe_sms_per_tile() { return Environs::get_int("PCCL_GEMM_SMS_PER_TILE", 2) == 1 ? 1 : 2; }
+
 MoeShape moe_shape(const PeerBases& peers, const MoeBuffers& buf, int local_experts, bool wait_ready, uint32_t epoch) {
   PCCL_CHECK(buf.cap > 0 && buf.cap % kBM == 0, "MoE: region capacity must be a multiple of " << kBM);
   PCCL_CHECK(local_experts * peers.world <= kMoeMaxRegions,
@@ -360,7 +365,8 @@ void moe_expert_up(const PeerBases& peers, const MoeBuffers& buf, int hidden, in
   const int rows = local_experts * peers.world * buf.cap;
   MatrixDesc a{peers.base[peers.rank] + buf.recv_off, rows, hidden, hidden};
   MatrixDesc b{w13, local_experts * 2 * ffn, hidden, hidden};
-  launch<MoeUpPolicy>(a, b, p, ctas, timeout_ms, stream, 0, local_experts);
+  if (moe_sms_per_tile() == 2) launch_pair<MoeUpPolicy>(a, b, p, ctas, timeout_ms, stream, true, 0, local_experts);
+  else launch<MoeUpPolicy>(a, b, p, ctas, timeout_ms, stream, 0, local_experts);
 }
 
 void moe_expert_down(const PeerBases& peers, const MoeBuffers& buf, int tokens, int hidden, int ffn,
@@ -379,7 +385,8 @@ void moe_expert_down(const PeerBases& peers, const MoeBuffers& buf, int tokens, 
   const int rows = local_experts * peers.world * buf.cap;
   MatrixDesc a{h, rows, ffn, ffn};
   MatrixDesc b{w2, local_experts * hidden, ffn, ffn};
-  launch<MoeDownPolicy>(a, b, p, ctas, timeout_ms, stream, 0, local_experts);
+  if (moe_sms_per_tile() == 2) launch_pair<MoeDownPolicy>(a, b, p, ctas, timeout_ms, stream, true, 0, local_experts);
+  else launch<MoeDownPolicy>(a, b, p, ctas, timeout_ms, stream, 0, local_experts);
 }
 
 }  // namespace gemm

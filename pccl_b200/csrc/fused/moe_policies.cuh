@@ -1,4 +1,4 @@
-// Expert-parallel MoE feed-forward as two policies of umma_gemm_kernel.
+// Expert-parallel MoE feed-forward as two policies of the GEMM kernels (one SM per tile or SM pairs).
 //
 // Tokens arrive in "regions" of the receive buffer, one per (local expert, source rank):
 // region = local_expert * world + source, `cap` rows each, of which counts[region] are filled
@@ -40,6 +40,7 @@ struct MoeShape {
 struct MoeIndex {
   uint16_t prefix[kMoeMaxRegions + 1];
   uint32_t ok;
+  uint32_t pairs;             // sum over local experts of ceil(filled blocks / 2): tiles of the paired kernel per n-tile
 };
 __device__ __forceinline__ MoeIndex& moe_index() {
   __shared__ MoeIndex index;
@@ -70,6 +71,10 @@ __device__ __forceinline__ int moe_prepare(const MoeShape& s, const Problem& g, 
       total += (rows + kBM - 1) / kBM;
     }
     ix.prefix[regions] = static_cast<uint16_t>(total);
+    uint32_t pairs = 0;
+    for (int le = 0; le < s.local_experts; ++le)
+      pairs += (static_cast<uint32_t>(ix.prefix[(le + 1) * s.world] - ix.prefix[le * s.world]) + 1u) / 2u;
+    ix.pairs = pairs;
   }
   __syncthreads();
   // The rows were written by generic-proxy stores (of other GPUs); TMA reads through the async proxy.
@@ -95,6 +100,30 @@ __device__ __forceinline__ void moe_tile_coords(const MoeShape& s, const Problem
   *mb = region * s.cap_blocks + (b - ix.prefix[region]);
 }
 
+// Paired kernel: tile -> the 128-row block of CTA `half`.  A pair takes two consecutive filled blocks
+// of one expert (they share the expert's weight tile); an expert with an odd number of filled
+// blocks leaves the second half of its last pair absent.
+__device__ __forceinline__ void moe_ragged_pair(const MoeShape& s, const Problem& g, int tile, int half, int* mb,
+                                                bool* present, int* nb) {
+  const MoeIndex& ix = moe_index();
+  int le = 0, first = 0, blocks = 0, pairs = 1;
+  for (; le < s.local_experts; ++le) {
+    first = ix.prefix[le * s.world];
+    blocks = ix.prefix[(le + 1) * s.world] - first;
+    pairs = (blocks + 1) / 2;
+    if (tile < pairs * g.tiles_n) break;
+    tile -= pairs * g.tiles_n;
+  }
+  if (le == s.local_experts) { le = s.local_experts - 1; tile = 0; pairs = pairs > 0 ? pairs : 1; }   // not reached for tile < pair_tiles
+  *nb = tile / pairs;
+  const int in_expert = 2 * (tile % pairs) + half;
+  *present = in_expert < blocks;
+  const int b = first + (*present ? in_expert : in_expert - 1);
+  int region = le * s.world;
+  while (region + 1 < (le + 1) * s.world && ix.prefix[region + 1] <= b) ++region;
+  *mb = region * s.cap_blocks + (b - ix.prefix[region]);
+}
+
 // ------------------------------------------------------------------------------------------------
 struct MoeUpPolicy : PolicyDefaults {
   struct Params {
@@ -104,6 +133,13 @@ struct MoeUpPolicy : PolicyDefaults {
   };
   static constexpr int kOutPer32 = 16;
   static constexpr bool kSignalsTiles = false;
+  static constexpr bool kRaggedPairs = true;
+  __device__ static void ragged_pair(const Params& p, const Problem& g, int tile, int half, int* mb, bool* present,
+                                     int* nb) {
+    moe_ragged_pair(p.shape, g, tile, half, mb, present, nb);
+  }
+  __device__ static int pair_tiles(const Params&, const Problem& g) { return static_cast<int>(moe_index().pairs) * g.tiles_n; }
+  __device__ static void pair_coords(const Params&, const Problem&, int, int*, int*) {}
 
   __device__ static int prepare(const Params& p, const Problem& g, uint64_t deadline, const volatile uint32_t* abort_flag) {
     return moe_prepare(p.shape, g, deadline, abort_flag);
@@ -117,7 +153,7 @@ struct MoeUpPolicy : PolicyDefaults {
   // Weights of the local experts are stacked: expert le owns rows [le * N, (le + 1) * N).
   __device__ static int b_row(const Params& p, const Problem& g, int mb, int nb) {
     const int le = mb / p.shape.cap_blocks / p.shape.world;
-    return le * g.N + nb * kBN;
+    return le * g.N + nb * g.bn;
   }
   // acc[0..15] = gate pre-activations, acc[16..31] = up projections of the same 16 units.
   __device__ static void transform(const float* acc, float, float* out) {
@@ -151,6 +187,13 @@ struct MoeDownPolicy : PolicyDefaults {
   };
   static constexpr bool kRowScatter = true;
   static constexpr bool kSignalsTiles = false;
+  static constexpr bool kRaggedPairs = true;
+  __device__ static void ragged_pair(const Params& p, const Problem& g, int tile, int half, int* mb, bool* present,
+                                     int* nb) {
+    moe_ragged_pair(p.shape, g, tile, half, mb, present, nb);
+  }
+  __device__ static int pair_tiles(const Params&, const Problem& g) { return static_cast<int>(moe_index().pairs) * g.tiles_n; }
+  __device__ static void pair_coords(const Params&, const Problem&, int, int*, int*) {}
 
   __device__ static int prepare(const Params& p, const Problem& g, uint64_t deadline, const volatile uint32_t* abort_flag) {
     return moe_prepare(p.shape, g, deadline, abort_flag);
@@ -163,7 +206,7 @@ struct MoeDownPolicy : PolicyDefaults {
   }
   __device__ static int b_row(const Params& p, const Problem& g, int mb, int nb) {
     const int le = mb / p.shape.cap_blocks / p.shape.world;
-    return le * g.N + nb * kBN;
+    return le * g.N + nb * g.bn;
   }
   __device__ static RowInfo row_info(const Params& p, const Problem& g, int mb, int row_in_tile) {
     const int region = mb / p.shape.cap_blocks;

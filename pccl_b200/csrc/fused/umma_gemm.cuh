@@ -94,6 +94,10 @@ struct PolicyDefaults {
   // true: the paired kernel may cut the tiles of its last, partly filled round along K (needs a
   // static tile list, plain row addressing through tile_base / row_pitch and no per-tile signal).
   static constexpr bool kSplitTail = false;
+  // true: the paired kernel asks Policy::ragged_pair for the two 128-row blocks of a tile (they need
+  // not be neighbours and the second may be absent) and Policy::pair_tiles for the tile count;
+  // false: block pair i = blocks 2i, 2i + 1 through Policy::pair_coords.
+  static constexpr bool kRaggedPairs = false;
   template <class P>
   __device__ static void reducer_main(const P&, const Problem&, int, int, int, int, uint64_t,
                                       const volatile uint32_t*) {}

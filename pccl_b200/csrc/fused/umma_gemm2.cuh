@@ -131,6 +131,27 @@ struct Pipe2 {
   uint32_t stored_count;
 };
 
+// The 128-row block that CTA `half` of a pair owns in `tile`: its index, whether it exists (the
+// second block of the last pair of an odd count does not; the CTA then loads its partner's block so
+// that the MMA has defined operands, and stores nothing), the n-tile and the pair index.
+struct HalfBlock {
+  int mb, nb, mb2;
+  bool present;
+};
+template <class Policy>
+__device__ __forceinline__ HalfBlock half_block(const typename Policy::Params& p, const Problem& g, int tile, int half) {
+  HalfBlock hb;
+  if constexpr (Policy::kRaggedPairs) {
+    Policy::ragged_pair(p, g, tile, half, &hb.mb, &hb.present, &hb.nb);
+    hb.mb2 = 0;
+  } else {
+    Policy::pair_coords(p, g, tile, &hb.mb2, &hb.nb);
+    hb.mb = 2 * hb.mb2 + half;
+    hb.present = hb.mb < g.tiles_m;
+  }
+  return hb;
+}
+
 // Epilogue of one K-slice of a split tile (one epilogue warp: TMEM lanes [32 quarter, +32) of this
 // CTA's half).  Both directions are coalesced: the partial accumulator goes through the warp's
 // staging buffer so that a store instruction writes whole 128-byte lines of the workspace, and in
@@ -288,7 +309,11 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   const int tiles_m = Policy::prepare(p, g, deadline, abort_flag);
   const int k_blocks = (g.K + kBK - 1) / kBK;
   const bool split = Policy::kSplitTail && g.tail_first < (g.tiles_m + 1) / 2 * g.tiles_n;
-  const int num_tiles = tiles_m < 0 ? 0 : (split ? g.num_items : (g.tiles_m + 1) / 2 * g.tiles_n);
+  int num_tiles = 0;
+  if (tiles_m >= 0) {
+    if constexpr (Policy::kRaggedPairs) num_tiles = Policy::pair_tiles(p, g);
+    else num_tiles = split ? g.num_items : (g.tiles_m + 1) / 2 * g.tiles_n;
+  }
   bool failed = false;
 
   if (warp == 0) {
@@ -297,9 +322,8 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       uint32_t stage = 0, phase = 0;
       for (int item = pair; item < num_tiles && !failed; item += num_pairs) {
         const WorkItem work = split ? decode_item(g, item, k_blocks) : WorkItem{item, 0, k_blocks, 0, false};
-        int mb2, nb;
-        Policy::pair_coords(p, g, work.tile, &mb2, &nb);
-        const int mb = 2 * mb2 + half;
+        const HalfBlock hb = half_block<Policy>(p, g, work.tile, half);
+        const int mb = hb.mb, nb = hb.nb;
         if (!Policy::before_load(p, g, mb, deadline, abort_flag)) { raise_error(g, kErrPolicyWait, 0); failed = true; break; }
         for (int kb = work.kb_begin; kb < work.kb_end; ++kb) {
           if (!ptx::mbar_wait(&pipe.empty[stage], phase ^ 1u, deadline, abort_flag)) {
@@ -363,9 +387,8 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         }
         if (!ok) break;
         __threadfence_block();
-        int mb2, nb;
-        Policy::pair_coords(p, g, tile, &mb2, &nb);
-        if (2 * mb2 + half < g.tiles_m) Policy::tile_done(p, g, 2 * mb2 + half, nb);
+        const HalfBlock hb = half_block<Policy>(p, g, tile, half);
+        if (hb.present) Policy::tile_done(p, g, hb.mb, hb.nb);
       }
     }
   } else if (warp >= 7) {
@@ -381,9 +404,8 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     for (int item = pair; item < num_tiles; item += num_pairs, ++local_tile) {
       const WorkItem work = split ? decode_item(g, item, k_blocks) : WorkItem{item, 0, k_blocks, 0, false};
       const uint32_t acc = local_tile & 1u, acc_phase = (local_tile >> 1) & 1u;
-      int mb2, nb;
-      Policy::pair_coords(p, g, work.tile, &mb2, &nb);
-      const int mb = 2 * mb2 + half;
+      const HalfBlock hb = half_block<Policy>(p, g, work.tile, half);
+      const int mb = hb.mb, nb = hb.nb, mb2 = hb.mb2;
       uint32_t ok = 1;
       if (lane == 0) ok = ptx::mbar_wait(&pipe.acc_full[acc], acc_phase, deadline, abort_flag) ? 1u : 0u;
       ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -406,7 +428,7 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       constexpr int kChunks = kRowBytes / 16;
       constexpr int kRowsPerSt = 32 / kChunks;
       RowInfo info;
-      const bool block_ok = mb < g.tiles_m;              // an odd number of row blocks leaves the last pair half empty
+      const bool block_ok = hb.present;                  // an odd number of row blocks leaves the last pair half empty
       if constexpr (Policy::kRowScatter) {
         info = Policy::row_info(p, g, block_ok ? mb : 0, quarter * 32 + lane);
         if (!block_ok) info.valid = 0;

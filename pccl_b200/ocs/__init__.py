@@ -2,7 +2,8 @@
 
 from .controller import OCSPlanController, StaticPlanController
 from .collective_plan import (OCSCollectivePhase, OCSCollectivePlan, OcsCollectivePlanRunner,
-                              PreparedOcsCollectivePlan, build_ring_allreduce_alltoall_plan)
+                              PreparedOcsCollectivePlan, build_ring_allreduce_alltoall_plan,
+                              build_switched_allreduce_alltoall_plan)
 from .exceptions import (OCSBarrierTimeout, OCSError, OCSLinkNotReady, OCSPlanMismatchError,
                          OCSProtocolError)
 from .phase_runner import OcsPhaseRunner, PreparedOcsGraph
@@ -23,7 +24,7 @@ __all__ = [
     "OCSRuntime", "OCSBarrierState", "OCSLinkState", "OCSSwitchResult", "OcsPhaseRunner",
     "OcsCollectivePlanRunner", "PreparedOcsCollectivePlan", "PreparedOcsGraph",
     "StaticPlanController", "SwitchConnector", "TorchDistributedSwitchConnector",
-    "TensorSwitchConnector", "NvlinkSwitchConnector", "build_ring_allreduce_alltoall_plan", "OcsTorchPlanRunner",
+    "TensorSwitchConnector", "NvlinkSwitchConnector", "build_ring_allreduce_alltoall_plan", "build_switched_allreduce_alltoall_plan", "OcsTorchPlanRunner",
     "TorchCollectivePhase", "TorchCollectivePlan", "build_torch_allreduce_alltoall_plan",
     "OCS_CONTROL_MAGIC", "OCS_CONTROL_MAX_PAYLOAD_BYTES", "OCS_CONTROL_VERSION",
     "OCSControlMessage", "OCSControlMessageKey", "OCSControlMessageType", "OCSControlStatus",

@@ -35,6 +35,11 @@ class EngineBackedRunner:
         self.runtime = runtime if runtime is not None else OCSRuntime()
         self.compiler = compiler if compiler is not None else Compiler()
         self.json_dir = Path(json_dir) if json_dir is not None else None
+        #: a prepared plan that is executed again keeps its operations registered: the second and later
+        #: executions skip the registration and the host barrier that orders it (set False to register
+        #: at every execution)
+        self.reuse_registrations = True
+        self._live: dict = {}
 
     def _create_json_dir(self) -> Tuple[Path, bool]:
         """(directory, whether this runner owns and may delete it)."""
@@ -68,23 +73,42 @@ class EngineBackedRunner:
         data_phases = [i for i, name in enumerate(names) if name is not None]
         last = data_phases[-1] if data_phases else -1
         current = input_tensor
+        # A signal reset must never run while a peer may already post the next phase's signals.
+        # First execution (the reference's order): execute, barrier, reset, and the host barrier that
+        # follows the next registration orders the reset before any peer's next kernel.  Reused
+        # registrations have no such host barrier, so there the reset moves in front of the OCS
+        # barrier: execute_operation is blocking and plans are balanced, hence every signal posted to
+        # this rank in the phase has been consumed when it returns, and the OCS barrier then separates
+        # the reset from the peers' next phase.
+        reset_unfenced = False
         for i, (name, path) in enumerate(zip(names, files)):
+            reused = False
             if name is not None:
                 if path is None:
                     raise RuntimeError("data phase is missing its generated JSON")
                 target = output_tensor if (i == last and output_tensor is not None) \
                     else torch.empty_like(current)
-                if not self._engine().register_operation(name, str(path)):
-                    raise RuntimeError(f"failed to register {what} '{name}'")
-                self._synchronize_phase_registration(group)
+                reused = self.reuse_registrations and self._live.get(name) == str(path)
+                if not reused:
+                    self._live.pop(name, None)
+                    if not self._engine().register_operation(name, str(path)):
+                        raise RuntimeError(f"failed to register {what} '{name}'")
+                    self._synchronize_phase_registration(group)
+                    self._live[name] = str(path)
+                elif reset_unfenced:
+                    self._synchronize_phase_registration(group)
+                reset_unfenced = False
                 # execute_operation is blocking, so the host barrier below
                 # cannot overtake this phase's device work.
                 self._engine().execute_operation(name, current, target)
                 current = target
             if barriers[i] is not None:
-                self.runtime.barrier_switch(barriers[i], group=group, timeout=timeout)
-                if name is not None:
+                if name is not None and reused:
                     self._reset_signals(name)
+                self.runtime.barrier_switch(barriers[i], group=group, timeout=timeout)
+                if name is not None and not reused:
+                    self._reset_signals(name)
+                    reset_unfenced = True
         return current
 
 

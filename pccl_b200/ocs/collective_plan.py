@@ -154,3 +154,27 @@ def build_ring_allreduce_alltoall_plan(rank: int, world_size: int, tensor_size: 
         OCSCollectivePhase("alltoall_1", ring.build_alltoall(*args), barrier(1, 2)),
         OCSCollectivePhase("allreduce_2", ring.build_allreduce(*args)),
     ))
+
+
+def build_switched_allreduce_alltoall_plan(rank: int, world_size: int, tensor_size: int,
+                                           dtype: str = "float32", executor: str = "sm",
+                                           job_id: str = "ocs_collective_plan", group_id: int = 0,
+                                           first_barrier_id: int = 0,
+                                           first_epoch_id: int = 0) -> OCSCollectivePlan:
+    """The same three phases with the templates made for a switched fabric, where every peer is one
+    hop away: two-shot all-reduce (direct reduce-scatter, then direct all-gather) and a direct
+    all-to-all, instead of W - 1 ring steps each."""
+    from ..dsl.algorithms import TwoShotAllreduce
+    if world_size < 2:
+        raise ValueError("the fixed collective plan requires at least two ranks")
+    if tensor_size <= 0 or tensor_size % world_size:
+        raise ValueError("tensor_size must be positive and divisible by world_size")
+    direct = TwoShotAllreduce()
+    barrier = barrier_sequence(world_size, job_id, group_id, first_barrier_id, first_epoch_id,
+                               algorithm="auto", backend="pccl")
+    args = (rank, world_size, tensor_size, dtype, executor)
+    return OCSCollectivePlan(phases=(
+        OCSCollectivePhase("allreduce_0", direct.build_allreduce(*args), barrier(0, 1)),
+        OCSCollectivePhase("alltoall_1", direct.build_alltoall(*args), barrier(1, 2)),
+        OCSCollectivePhase("allreduce_2", direct.build_allreduce(*args)),
+    ))

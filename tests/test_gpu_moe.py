@@ -65,9 +65,14 @@ def test_router_with_non_finite_rows_stays_inside_its_outputs(experts):
     assert torch.equal(idx[finite][clear][:, 0].long(), ref_idx[clear][:, 0])
 
 
-@pytest.mark.parametrize("tokens,hidden,ffn,experts", [(512, 512, 1024, 8), (200, 256, 400, 4), (1024, 1024, 2048, 8)])
-def test_fused_moe_single_gpu(tokens, hidden, ffn, experts):
+@pytest.mark.parametrize("sms_per_tile", [1, 2])
+@pytest.mark.parametrize("tokens,hidden,ffn,experts", [(512, 512, 1024, 8), (200, 256, 400, 4), (1024, 1024, 2048, 8),
+                                                       (2048, 512, 768, 2)])
+def test_fused_moe_single_gpu(tokens, hidden, ffn, experts, sms_per_tile, monkeypatch):
+    """Expert GEMMs on one SM per tile and on SM pairs (two row blocks of one expert per tile; experts
+    with an odd number of filled blocks leave half of their last pair empty)."""
     from pccl_b200.ops import moe
+    monkeypatch.setenv("PCCL_GEMM_SMS_PER_TILE", str(sms_per_tile))
     native = __import__("pccl_b200.engine", fromlist=["load_native"]).load_native().fused
     native.clear_error()
     wg, w1, w3, w2 = _weights(experts, hidden, ffn)

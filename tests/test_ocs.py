@@ -198,6 +198,19 @@ def test_collective_plan_runner_and_builders():
     prepared = runner.prepare(plan)
     runner.execute(prepared, torch.zeros(64))
     assert [e[0] for e in log] == ["register", "execute", "barrier", "reset"] * 2 + ["register", "execute"]
+    # a second execution of the same prepared plan reuses the registrations ...
+    del log[:]
+    runner.execute(prepared, torch.zeros(64))
+    # (and resets before the barrier: no host barrier follows that could order a later reset)
+    assert [e[0] for e in log] == ["execute", "reset", "barrier"] * 2 + ["execute"]
+    # ... unless the runner is told to register every time
+    del log[:]
+    runner.reuse_registrations = False
+    runner.execute(prepared, torch.zeros(64))
+    assert [e[0] for e in log] == ["register", "execute", "barrier", "reset"] * 2 + ["register", "execute"]
+    switched = ocs.build_switched_allreduce_alltoall_plan(1, 4, 64)
+    assert [p.graph.collective_type for p in switched.phases] == ["allreduce", "alltoall", "allreduce"]
+    assert [p.barrier_after.algorithm if p.barrier_after else None for p in switched.phases] == ["auto", "auto", None]
     prepared.close()
     assert not prepared.json_dir.exists()
     with pytest.raises(RuntimeError, match="closed"):
