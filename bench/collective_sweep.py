@@ -214,7 +214,7 @@ def run_multi(args):
 def write_tuning(path, world, rows):
     """Merge this sweep's winners into the tuning file: per collective, break points
     [{"max_bytes", "algorithm", "channels", "us"}] where consecutive sizes with the same winner are
-    merged and the last entry is open-ended.  Only sizes that were measured with at least two
+    merged (a winner is kept while it stays within 3 % of the best) and the last entry is open-ended.  Only sizes that were measured with at least two
     algorithms count (a lone "auto" row says nothing about the alternatives)."""
     try:
         with open(path) as handle:
@@ -234,6 +234,13 @@ def write_tuning(path, world, rows):
             if len(cands) < 2:
                 continue
             best = min(cands, key=lambda r: r["us"])
+            # Hysteresis: the previous size's winner stays unless another one beats it by more than 3 %
+            # (timer noise otherwise flips the table between equals).
+            if table:
+                same = [r for r in cands if r["algo"] == table[-1]["algorithm"]
+                        and (r["channels"] or None) == table[-1].get("channels")]
+                if same and min(r["us"] for r in same) <= 1.03 * best["us"]:
+                    best = min(same, key=lambda r: r["us"])
             entry = {"max_bytes": nbytes, "algorithm": best["algo"], "us": best["us"]}
             if best["channels"]:
                 entry["channels"] = best["channels"]
@@ -305,10 +312,20 @@ def main():
     ap.add_argument("--out", default=None, help="write every row to this JSON file (rank 0)")
     ap.add_argument("--write-tuning", default=None,
                     help="merge the fastest algorithm per size into this tuning file (the selector reads it)")
+    ap.add_argument("--tuning-from", nargs="+", default=None, metavar="SWEEP_JSON",
+                    help="no measurement: rebuild --write-tuning from saved --out files (any worlds, any collectives)")
     ap.add_argument("--check", action="store_true", help="verify every all-reduce configuration before timing it")
     ap.add_argument("--check-bytes", default="16M",
                     help="up to this size the check is against a float64 host sum, above it against NCCL")
     args = ap.parse_args()
+    if args.tuning_from:
+        if not args.write_tuning:
+            ap.error("--tuning-from needs --write-tuning")
+        for path in args.tuning_from:
+            with open(path) as handle:
+                saved = json.load(handle)
+            write_tuning(args.write_tuning, saved["world"], saved["rows"])
+        return
     args.collectives = args.collectives.split(",")
     args.dtypes = args.dtypes.split(",")
     args.algos = args.algos.split(",")

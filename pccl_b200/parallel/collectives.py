@@ -213,8 +213,14 @@ def ensure_plan(kind: str, numel: int, dtype: torch.dtype, algorithm: Optional[s
         if kind == "allreduce":
             algorithm = select_algorithm(world, nbytes, _topology(), B200_PROFILE).name
         else:
-            algorithm = "nvls" if (_topology().in_switch_reduction and kind != "alltoall"
-                                   and nbytes >= (4 << 20) and world > 2) else "twoshot"
+            # The measured table first.  Without one: direct pulls.  In-switch multicast does not lower
+            # the busier direction of an all-gather or reduce-scatter (each rank still receives, or
+            # serves, (W-1)/W of the message), and peer loads moved 650 GB/s against 571 GB/s for
+            # multimem on 4 GPUs.
+            route = tuned_route(kind, world, nbytes) if kind in ("allgather", "reduce_scatter") else None
+            algorithm = route["algorithm"] if route and route["algorithm"] in ALGORITHMS else "twoshot"
+            if route and route["algorithm"] in ALGORITHMS and channels is None:
+                channels = route.get("channels")
     if channels is None:
         channels = default_channels(nbytes, world)
     if algorithm in ("ring", "rhd", "tree") and kind != "allreduce":

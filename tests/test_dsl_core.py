@@ -227,3 +227,38 @@ def test_selector_follows_a_tuning_file(tmp_path, monkeypatch):
         assert selector.select_algorithm(4, 1 << 29, NVLINK5_TOPOLOGY, B200_PROFILE).name == "twoshot"
     finally:
         selector.clear_tuning_cache()
+
+
+def test_packaged_tuning_matches_the_saved_sweeps():
+    """The table shipped with the package picks, at every swept size and world, a configuration whose
+    measured time is within 5 % of the best one measured (bench/results/sweep_*gpu_*.json)."""
+    import glob
+    import json
+    import os
+    from pccl_b200.dsl.algorithms import selector
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    packaged = os.path.join(root, "pccl_b200", "dsl", "algorithms", "tuning_b200.json")
+    files = sorted(glob.glob(os.path.join(root, "bench", "results", "sweep_*gpu_allreduce.json")) +
+                   glob.glob(os.path.join(root, "bench", "results", "sweep_*gpu_shards.json")))
+    assert files and os.path.exists(packaged)
+    selector.clear_tuning_cache()
+    checked = 0
+    for path in files:
+        saved = json.load(open(path))
+        world = saved["world"]
+        sizes = {}
+        for row in saved["rows"]:
+            if row.get("requested") != "auto":
+                sizes.setdefault((row["collective"], row["bytes"]), []).append(row)
+        for (kind, nbytes), rows in sizes.items():
+            if len(rows) < 2:
+                continue
+            route = selector.tuned_route(kind, world, nbytes, path=packaged)
+            assert route is not None, (kind, world, nbytes)
+            mine = [r["us"] for r in rows if r["algo"] == route["algorithm"]
+                    and (route.get("channels") is None or r["channels"] == route["channels"])]
+            assert mine, (kind, world, nbytes, route)
+            assert min(mine) <= 1.05 * min(r["us"] for r in rows), (kind, world, nbytes, route)
+            checked += 1
+    assert checked > 100
+    selector.clear_tuning_cache()
