@@ -297,10 +297,9 @@ void all_gather_gemm(const PeerBases& peers, uint64_t gathered_off, int M, int K
   p.ldc = ldc;
   p.rows_per_rank = M / peers.world;
   p.blocks_per_rank = p.rows_per_rank / kBM;
-  // Copier CTAs: by default the SMs that the GEMM tiles leave idle (at least 16, at most 48).  When
-  // there are fewer remote row blocks than copiers, a block is split into `copy_parts` pieces and
-  // the copier count is trimmed to a whole number of blocks' worth, so that one round of copying
-  // covers everything and no copier runs a second, lonely round.
+  // Copier CTAs: by default the SMs that the GEMM tiles leave idle (at least 16, at most 48).  A block
+  // is cut into copiers / 4 parts, so that about four row blocks are in flight at a time and blocks
+  // complete in the order the GEMM needs them.
   const int sms = sm_count();
   const int remote_blocks = (peers.world - 1) * p.blocks_per_rank;
   if (peers.world == 1) {
@@ -308,15 +307,13 @@ void all_gather_gemm(const PeerBases& peers, uint64_t gathered_off, int M, int K
     p.copy_parts = 1;
   } else {
     const int tiles = ((M + kBM - 1) / kBM) * ((w.rows + kBN - 1) / kBN);
-    // More tiles than SMs: the GEMM runs several waves and the copy must keep ahead of it; a
-    // copier pulls roughly 16 GB/s, so give it 32 SMs.
+    // More tiles than SMs: the GEMM runs several waves and the copy must keep ahead of it: 32 SMs with
+    // 128 KB in flight each cover the link's bandwidth-delay product twice over.
     int want = copy_ctas > 0 ? copy_ctas : (tiles >= sms ? 32 : std::min(48, std::max(16, sms - tiles)));
-    if (want >= remote_blocks) {
-      p.copy_parts = want / remote_blocks;
-      want = p.copy_parts * remote_blocks;
-    } else {
-      p.copy_parts = 1;
-    }
+    want &= ~1;                                           // whole clusters for the paired kernel
+    if (want < 2) want = 2;
+    p.copy_parts = std::max(1, want / 4);
+    if (remote_blocks * p.copy_parts < want) want = std::max(2, (remote_blocks * p.copy_parts + 1) & ~1);
     p.copy_ctas = want;
   }
   p.epoch = epoch;

@@ -156,30 +156,41 @@ struct ReduceScatterPolicy : PolicyDefaults {
     }
   }
 
-  // Reducer warps: item = (local row block, n tile, 32-row strip), one warp per item, items in the
-  // order the blocks complete (every source delivers this rank's blocks in ascending order).
+  // Reducer warps: item = (local row block, n tile, strip of a few rows), one warp per item, items in
+  // the order the blocks complete (every source delivers this rank's blocks in ascending order).
+  // A strip is what a warp sums in ONE round of loads (32 lanes x 16 loads in flight): the blocks
+  // that complete last are then spread over every reducer warp of the grid and cost one memory
+  // round trip.  With 32-row strips 64 warps were left with eight dependent rounds each, 14 us
+  // after the last block had arrived (per-CTA timeline, 4 GPUs).
   static constexpr int kReducerWarps = 4;
   __device__ static void reducer_main(const Params& p, const Problem& g, int cta, int num_ctas, int rwarp, int lane,
                                       uint64_t deadline, const volatile uint32_t* abort_flag) {
     const int me = p.peers.rank, world = p.peers.world;
     const uint32_t* flags = reinterpret_cast<const uint32_t*>(p.peers.base[me] + p.flags_off);
-    const int strips = kBM / 32;
+    const int loads_per_lane = world <= 2 ? 8 : world <= 4 ? 4 : 2;         // sum_slots' kRV for this world
+    int strip_rows = 32 * loads_per_lane * 8 / g.bn;                         // rows of a tile-wide strip in one round
+    strip_rows = strip_rows < 1 ? 1 : strip_rows > 32 ? 32 : strip_rows;
+    const int strips = (kBM + strip_rows - 1) / strip_rows;
     const int items = p.blocks_per_rank * g.tiles_n * strips;
+    int ready_block = -1;
     for (int item = cta * kReducerWarps + rwarp; item < items; item += num_ctas * kReducerWarps) {
       const int block = item / (g.tiles_n * strips), rest = item % (g.tiles_n * strips);
       const int nb = rest / strips, strip = rest % strips;
-      bool ok = true;
-      if (lane < world) ok = wait_flag_ge(flags + lane * p.blocks_per_rank + block, p.epoch, deadline, abort_flag);
-      if (!__all_sync(0xffffffffu, ok)) {
-        if (lane == 0) raise_error(g, kErrPolicyWait, 3);
-        return;
+      if (block != ready_block) {                 // a block this warp has seen complete stays complete
+        bool ok = true;
+        if (lane < world) ok = wait_flag_ge(flags + lane * p.blocks_per_rank + block, p.epoch, deadline, abort_flag);
+        if (!__all_sync(0xffffffffu, ok)) {
+          if (lane == 0) raise_error(g, kErrPolicyWait, 3);
+          return;
+        }
+        ready_block = block;
       }
       if (rwarp == 0 && lane == 0) {              // timeline: first and latest item whose partials were all in
         if (item < num_ctas * kReducerWarps) trace_stamp(g, 6);
         trace_stamp(g, 7);
       }
-      const int row0 = block * kBM + strip * 32, col0 = nb * g.bn;
-      const int rows = min(32, p.rows_per_rank - row0), cols = min(g.bn, g.N - col0);
+      const int row0 = block * kBM + strip * strip_rows, col0 = nb * g.bn;
+      const int rows = min(min(strip_rows, kBM - strip * strip_rows), p.rows_per_rank - row0), cols = min(g.bn, g.N - col0);
       if (rows <= 0 || cols <= 0) continue;
       const int vec_per_row = cols / 8;                    // 8 bf16 per 16 bytes (N % 8 == 0)
       const int total = rows * vec_per_row;
@@ -210,21 +221,33 @@ struct AllGatherPolicy : PolicyDefaults {
   __device__ static int prepare(const Params&, const Problem& g, uint64_t, const volatile uint32_t*) {
     return g.tiles_m;
   }
-  // Shards in the order own, rank+1, rank+2, ...; M-fastest inside a shard.
+  // Shards in the order own, rank+1, rank+2, ...  Inside the own shard M-fastest (consecutive CTAs
+  // share a weight tile); inside a remote shard N-fastest, rows in the order the copiers deliver
+  // them, so that a tile only waits for its own rows (consecutive CTAs then share the A rows).
   __device__ static void tile_coords(const Params& p, const Problem& g, int tile, int* mb, int* nb) {
     const int per_shard = p.blocks_per_rank * g.tiles_n;
-    const int shard = (p.peers.rank + tile / per_shard) % p.peers.world;
-    const int within = tile % per_shard;
-    *mb = shard * p.blocks_per_rank + within % p.blocks_per_rank;
-    *nb = within / p.blocks_per_rank;
+    const int step = tile / per_shard, within = tile % per_shard;
+    const int shard = (p.peers.rank + step) % p.peers.world;
+    if (step == 0) {
+      *mb = shard * p.blocks_per_rank + within % p.blocks_per_rank;
+      *nb = within / p.blocks_per_rank;
+    } else {
+      *mb = shard * p.blocks_per_rank + within / g.tiles_n;
+      *nb = within % g.tiles_n;
+    }
   }
   __device__ static void pair_coords(const Params& p, const Problem& g, int tile, int* mb2, int* nb) {
     const int pairs_per_rank = p.blocks_per_rank / 2;
     const int per_shard = pairs_per_rank * g.tiles_n;
-    const int shard = (p.peers.rank + tile / per_shard) % p.peers.world;
-    const int within = tile % per_shard;
-    *mb2 = shard * pairs_per_rank + within % pairs_per_rank;
-    *nb = within / pairs_per_rank;
+    const int step = tile / per_shard, within = tile % per_shard;
+    const int shard = (p.peers.rank + step) % p.peers.world;
+    if (step == 0) {
+      *mb2 = shard * pairs_per_rank + within % pairs_per_rank;
+      *nb = within / pairs_per_rank;
+    } else {
+      *mb2 = shard * pairs_per_rank + within / g.tiles_n;
+      *nb = within % g.tiles_n;
+    }
   }
   __device__ static bool before_load(const Params& p, const Problem&, int mb, uint64_t deadline,
                                      const volatile uint32_t* abort_flag) {
@@ -243,23 +266,59 @@ struct AllGatherPolicy : PolicyDefaults {
   __device__ static int aux_ctas(const Params& p) { return p.copy_ctas; }
 
   // Copier CTAs.  CTA 0 first announces "my shard is in place" to every peer.  Then the copiers
-  // walk the peers' shards (nearest successor first), block by block: pull 128 rows x K into the
-  // local gathered matrix, fence, publish ready[mb].  Finally each source is told that its shard
-  // has been read, and CTA 0 waits until every peer has read this rank's shard, so the caller
-  // may overwrite its input when the kernel is done.
+  // walk the peers' shards (nearest successor first) in row order: a 128-row block is cut into
+  // `copy_parts` parts, part i of the list goes to copier i mod (number of copiers), so at any
+  // time all copiers work on the same few blocks and the blocks complete one after another, in
+  // the order the GEMM needs them (one copier per block made all blocks complete together, at the
+  // end of the copy: most GEMM CTAs then waited 45 us for their first tile in a timeline).  A
+  // copier streams its parts through a ring of shared-memory stages without draining between
+  // parts: peer memory -> shared memory (bulk copy completing on an mbarrier) -> local gathered
+  // matrix (bulk copy in a group), kCopyLag loads in flight; a part is published (ready[mb], and
+  // a "read" count at its source) once kDoneLag newer store groups have been committed and the
+  // wait for all older groups has returned.  Never a multicast: each copier fetches only its own
+  // parts.  Finally CTA 0 waits until every peer has read this rank's shard, so the caller may
+  // overwrite its input when the kernel is done.
   static constexpr int kCopyStages = 12, kCopyLag = 8;     // 8 loads of 16 KB in flight, 4 stores pending
+  static constexpr int kDoneLag = 3, kDoneFifo = 16;
   static constexpr uint32_t kCopyChunk = 16 * 1024;
+
+  struct CopyPart {
+    const uint8_t* from;
+    uint8_t* to;
+    uint64_t bytes;
+    uint32_t chunks;
+    int mb, src;
+  };
+  __device__ static CopyPart copy_part(const Params& p, const Problem& g, int item) {
+    const int me = p.peers.rank, world = p.peers.world;
+    const uint64_t row_bytes = static_cast<uint64_t>(g.K) * 2;
+    const int block_item = item / p.copy_parts, part = item % p.copy_parts;
+    CopyPart d;
+    d.src = (me + 1 + block_item / p.blocks_per_rank) % world;
+    d.mb = d.src * p.blocks_per_rank + block_item % p.blocks_per_rank;
+    const uint64_t off = p.gathered_off + static_cast<uint64_t>(d.mb) * kBM * row_bytes;
+    const uint64_t rows_here = min(static_cast<int>(kBM), g.M - d.mb * kBM);
+    const uint64_t block_vecs = rows_here * row_bytes / 16;
+    const uint64_t per_part = (block_vecs + p.copy_parts - 1) / p.copy_parts;
+    const uint64_t first = static_cast<uint64_t>(part) * per_part;
+    const uint64_t vecs = first >= block_vecs ? 0 : min(per_part, block_vecs - first);
+    d.from = p.peers.base[d.src] + off + first * 16;
+    d.to = p.peers.base[me] + off + first * 16;
+    d.bytes = vecs * 16;
+    d.chunks = static_cast<uint32_t>((d.bytes + kCopyChunk - 1) / kCopyChunk);
+    return d;
+  }
 
   __device__ static void aux_main(const Params& p, const Problem& g, int cta, int num_ctas, uint64_t deadline,
                                   const volatile uint32_t* abort_flag, uint8_t* smem) {
-    __shared__ uint32_t ok_flag;
     __shared__ uint64_t bars[kCopyStages];
+    __shared__ int fifo_mb[kDoneFifo], fifo_src[kDoneFifo];
+    __shared__ uint32_t fifo_group[kDoneFifo];
     if (threadIdx.x == 0) {
       for (int s = 0; s < kCopyStages; ++s) ptx::mbar_init(&bars[s], 1);
       ptx::mbar_init_fence();
     }
     __syncthreads();
-    uint32_t chunk_base = 0;                                // chunks issued by this CTA so far (stage phases)
     const int me = p.peers.rank, world = p.peers.world;
     uint32_t* my_flags = reinterpret_cast<uint32_t*>(p.peers.base[me] + p.flags_off);
     if (cta == 0 && static_cast<int>(threadIdx.x) < world && static_cast<int>(threadIdx.x) != me) {
@@ -267,85 +326,108 @@ struct AllGatherPolicy : PolicyDefaults {
       ptx::fence_sys();
       ptx::red_release_sys_add(there, 1u);
     }
-    const uint64_t row_bytes = static_cast<uint64_t>(g.K) * 2;
-    const int remote_blocks = (world - 1) * p.blocks_per_rank;
-    const int items = remote_blocks * p.copy_parts;
-    for (int item = cta; item < items; item += num_ctas) {
-      const int block_item = item / p.copy_parts, part = item % p.copy_parts;
-      const int src = (me + 1 + block_item / p.blocks_per_rank) % world;
-      const int mb = src * p.blocks_per_rank + block_item % p.blocks_per_rank;
-      if (threadIdx.x == 0) {
-        ok_flag = wait_flag_ge(my_flags + src, p.epoch, deadline, abort_flag) ? 1u : 0u;
-        if (!ok_flag) raise_error(g, kErrPolicyWait, 4);
-      }
-      __syncthreads();
-      if (!ok_flag) return;
-      const uint64_t off = p.gathered_off + static_cast<uint64_t>(mb) * kBM * row_bytes;
-      const uint8_t* from = p.peers.base[src] + off;
-      uint8_t* to = p.peers.base[me] + off;
-      const uint64_t rows_here = min(static_cast<int>(kBM), g.M - mb * kBM);
-      const uint64_t block_vecs = rows_here * row_bytes / 16;
-      const uint64_t per_part = (block_vecs + p.copy_parts - 1) / p.copy_parts;
-      from += part * per_part * 16;
-      to += part * per_part * 16;
-      const uint64_t vecs = part * per_part >= block_vecs ? 0 : min(per_part, block_vecs - part * per_part);
-      // One thread moves the part with bulk copies: peer memory -> shared memory (completing on an
-      // mbarrier) -> local gathered matrix, kCopyLag loads in flight.  No SM load/store loop, and
-      // never a multicast: each copier fetches only its own part.
-      if (threadIdx.x == 0 && vecs > 0) {
-        const uint64_t bytes = vecs * 16;
-        const uint32_t chunks = static_cast<uint32_t>((bytes + kCopyChunk - 1) / kCopyChunk);
-        bool ok = true;
-        uint32_t loaded = 0;                               // chunks whose load has been issued
-        for (uint32_t i = 0; i < chunks + kCopyLag && ok; ++i) {
-          if (i >= static_cast<uint32_t>(kCopyLag)) {      // consume chunk c: wait for its load, store it
-            const uint32_t c = i - kCopyLag, seq = chunk_base + c;
-            const uint32_t len = static_cast<uint32_t>(min(static_cast<uint64_t>(kCopyChunk), bytes - static_cast<uint64_t>(c) * kCopyChunk));
-            if (!ptx::mbar_wait(&bars[seq % kCopyStages], (seq / kCopyStages) & 1u, deadline, abort_flag)) {
-              ok = false;
-              break;
-            }
-            ptx::bulk_store(to + static_cast<uint64_t>(c) * kCopyChunk, smem + (seq % kCopyStages) * kCopyChunk, len);
-            ptx::bulk_commit();
-          }
-          if (i < chunks) {                                // produce chunk i into its stage
-            const uint32_t seq = chunk_base + i;
-            const uint32_t len = static_cast<uint32_t>(min(static_cast<uint64_t>(kCopyChunk), bytes - static_cast<uint64_t>(i) * kCopyChunk));
-            // The store that last read this stage (kCopyStages chunks ago) must be done reading.
-            ptx::bulk_wait_read<kCopyStages - kCopyLag>();
-            ptx::mbar_expect_tx(&bars[seq % kCopyStages], len);
-            ptx::bulk_load(smem + (seq % kCopyStages) * kCopyChunk, from + static_cast<uint64_t>(i) * kCopyChunk, len,
-                           &bars[seq % kCopyStages]);
-            loaded = i + 1;
-          }
+    if (threadIdx.x == 0) {
+      const int items = (world - 1) * p.blocks_per_rank * p.copy_parts;
+      bool ok = true;
+      int waited_src = -1;
+      auto wait_src = [&](int src) {                       // "shard of rank src is in place"
+        if (src == waited_src) return true;
+        if (!wait_flag_ge(my_flags + src, p.epoch, deadline, abort_flag)) {
+          raise_error(g, kErrPolicyWait, 4);
+          return false;
         }
-        if (!ok) {
-          // Leaving early: wait (bounded) for the loads still writing this CTA's shared memory.
-          raise_error(g, kErrPolicyWait, 8);
-          const uint64_t drain = ptx::globaltimer() + 50000000ull;
-          uint32_t no_abort = 0;
-          for (uint32_t c = loaded > static_cast<uint32_t>(kCopyStages) ? loaded - kCopyStages : 0; c < loaded; ++c) {
-            const uint32_t seq = chunk_base + c;
-            ptx::mbar_wait(&bars[seq % kCopyStages], (seq / kCopyStages) & 1u, drain, &no_abort);
-          }
-        }
-        ptx::bulk_wait_all();
-        asm volatile("fence.proxy.async.global;" ::: "memory");
-        chunk_base += chunks;
-        if (!ok) ok_flag = 0;
-      }
-      __syncthreads();
-      if (!ok_flag) return;
-      if (threadIdx.x == 0) {
+        waited_src = src;
+        return true;
+      };
+      // A part's rows are published locally at once; the "read" counts for its source are added up
+      // and posted once, at the end (a system-scope release per part stalled the stream for
+      // microseconds each).
+      uint32_t parts_read[kMaxRanks] = {};
+      auto publish = [&](int mb, int src) {
         ptx::fence_gpu();
         ptx::red_release_gpu_add(p.ready + mb, 1u);
-        // One "done" count per part read, posted at the shard's owner.
-        uint32_t* done = reinterpret_cast<uint32_t*>(p.peers.base[src] + p.flags_off) + world + me;
-        ptx::red_release_sys_add(done, 1u);
+        ++parts_read[src];
+      };
+      int f_head = 0, f_count = 0;                          // parts stored, not yet known complete
+      uint32_t groups = 0;                                  // store groups committed
+      auto drain_fifo = [&]() {                             // every committed store has completed
+        ptx::bulk_wait_all();
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+        for (; f_count > 0; --f_count, f_head = (f_head + 1) % kDoneFifo) publish(fifo_mb[f_head], fifo_src[f_head]);
+      };
+      uint32_t seq_p = 0, seq_c = 0;                        // chunks loaded / stored so far (ring positions)
+      int p_item = cta, c_item = cta;
+      uint32_t p_chunk = 0, c_chunk = 0;
+      bool p_valid = p_item < items, c_valid = c_item < items;
+      CopyPart pd{}, cd{};
+      if (p_valid) { pd = copy_part(p, g, p_item); ok = wait_src(pd.src); }
+      if (c_valid) cd = copy_part(p, g, c_item);
+      while (ok) {
+        // parts whose last chunk has been stored (or that are empty) join the queue
+        while (c_valid && c_chunk == cd.chunks) {
+          if (f_count == kDoneFifo) drain_fifo();
+          const int slot = (f_head + f_count) % kDoneFifo;
+          fifo_mb[slot] = cd.mb; fifo_src[slot] = cd.src; fifo_group[slot] = groups;
+          ++f_count;
+          c_item += num_ctas; c_valid = c_item < items; c_chunk = 0;
+          if (c_valid) cd = copy_part(p, g, c_item);
+        }
+        while (ok && p_valid && p_chunk == pd.chunks) {
+          p_item += num_ctas; p_valid = p_item < items; p_chunk = 0;
+          if (p_valid) { pd = copy_part(p, g, p_item); ok = wait_src(pd.src); }
+        }
+        if (!ok) break;
+        // publish the oldest part once kDoneLag newer groups exist: waiting for "all but the newest
+        // kDoneLag groups" then covers its stores and does not stall the stream
+        if (f_count > 0 && groups - fifo_group[f_head] >= static_cast<uint32_t>(kDoneLag)) {
+          ptx::bulk_wait_group<kDoneLag>();
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+          while (f_count > 0 && groups - fifo_group[f_head] >= static_cast<uint32_t>(kDoneLag)) {
+            publish(fifo_mb[f_head], fifo_src[f_head]);
+            f_head = (f_head + 1) % kDoneFifo; --f_count;
+          }
+        }
+        if (p_valid && seq_p - seq_c < static_cast<uint32_t>(kCopyLag)) {
+          // produce: the store that last read this stage (kCopyStages chunks ago) must be done reading
+          const uint32_t len = static_cast<uint32_t>(min(static_cast<uint64_t>(kCopyChunk), pd.bytes - static_cast<uint64_t>(p_chunk) * kCopyChunk));
+          ptx::bulk_wait_read<kCopyStages - kCopyLag>();
+          ptx::mbar_expect_tx(&bars[seq_p % kCopyStages], len);
+          ptx::bulk_load(smem + (seq_p % kCopyStages) * kCopyChunk, pd.from + static_cast<uint64_t>(p_chunk) * kCopyChunk, len,
+                         &bars[seq_p % kCopyStages]);
+          ++seq_p; ++p_chunk;
+          continue;
+        }
+        if (seq_c < seq_p) {
+          // consume: wait for the oldest load, store it
+          const uint32_t len = static_cast<uint32_t>(min(static_cast<uint64_t>(kCopyChunk), cd.bytes - static_cast<uint64_t>(c_chunk) * kCopyChunk));
+          if (!ptx::mbar_wait(&bars[seq_c % kCopyStages], (seq_c / kCopyStages) & 1u, deadline, abort_flag)) {
+            raise_error(g, kErrPolicyWait, 8);
+            ok = false;
+            break;
+          }
+          ptx::bulk_store(cd.to + static_cast<uint64_t>(c_chunk) * kCopyChunk, smem + (seq_c % kCopyStages) * kCopyChunk, len);
+          ptx::bulk_commit();
+          ++groups; ++seq_c; ++c_chunk;
+          continue;
+        }
+        break;                                              // nothing left to load, nothing in flight
+      }
+      if (ok) {
+        drain_fifo();
+        for (int r = 0; r < world; ++r)
+          if (parts_read[r])
+            ptx::red_release_sys_add(reinterpret_cast<uint32_t*>(p.peers.base[r] + p.flags_off) + world + me, parts_read[r]);
+      } else {
+        // Leaving early: wait (bounded) for the loads still writing this CTA's shared memory.
+        const uint64_t drain = ptx::globaltimer() + 50000000ull;
+        uint32_t no_abort = 0;
+        for (uint32_t c = seq_c; c < seq_p; ++c) ptx::mbar_wait(&bars[c % kCopyStages], (c / kCopyStages) & 1u, drain, &no_abort);
+        ptx::bulk_wait_all();
       }
     }
-    if (cta == 0) {
-      // Every peer posts blocks_per_rank * copy_parts "done" counts per call.
+    __syncthreads();
+    if (cta == 0 && !*abort_flag) {
+      // Every peer posts blocks_per_rank * copy_parts "read" counts per call.
       if (static_cast<int>(threadIdx.x) < world && static_cast<int>(threadIdx.x) != me) {
         const uint32_t want = p.epoch * static_cast<uint32_t>(p.blocks_per_rank * p.copy_parts);
         if (!wait_flag_ge(my_flags + world + threadIdx.x, want, deadline, abort_flag))
