@@ -130,7 +130,7 @@ def run_multi(args):
                 nccl_ms = reduce_max(timed_loop(nccl_call, iters, torch.cuda.synchronize, dist.barrier))
                 for algo in args.algos:
                     allowed = {"allreduce": ("auto", "ll", "push", "ring", "rhd", "tree", "oneshot", "twoshot", "nvls",
-                                             "nvls_twopass", "hybrid"),
+                                             "nvls_twopass", "hybrid", "nvls_kernel"),
                                "allgather": ("auto", "push", "ring", "rhd", "twoshot", "nvls"),
                                "reduce_scatter": ("auto", "push", "ring", "rhd", "twoshot", "nvls"),
                                "alltoall": ("auto", "push", "ring", "twoshot")}[kind]
@@ -144,6 +144,8 @@ def run_multi(args):
                         continue
                     if algo in ("rhd", "tree") and world & (world - 1):
                         continue
+                    if algo == "nvls_kernel" and not pp.collectives._nvls_kernel_ok(full, "sum"):
+                        continue
                     for ch in args.channels:
                         forced_algo = None if algo == "auto" else algo
                         forced_ch = None if ch == "auto" else int(ch)
@@ -153,7 +155,10 @@ def run_multi(args):
                                 pp.collectives._ll_eligible(full, "sum", forced_algo)
                             uses_push = kind == "allreduce" and not uses_ll and algo in ("auto", "push") and \
                                 pp.collectives._push_eligible(full, "sum", forced_algo)
-                            if kind == "allreduce":
+                            if kind == "allreduce" and algo == "nvls_kernel":
+                                name = ""                       # a kernel, not a plan
+                                call = lambda: pp.all_reduce(full, algorithm="nvls_kernel", async_op=True)
+                            elif kind == "allreduce":
                                 name = pp.ensure_plan(kind, numel, dtype, None if (uses_ll or uses_push) else plan_algo,
                                                       forced_ch)
                                 call = lambda: pp.all_reduce(full, algorithm=forced_algo, channels=forced_ch, async_op=True)
@@ -181,7 +186,7 @@ def run_multi(args):
                             rel_err = allreduce_error(call, full, numel, dtype)
                         ms = reduce_max(timed_loop(call, iters, lambda: pp.synchronize(name), dist.barrier))
                         if rank == 0:
-                            _, real_algo, real_ch = pp.registered_plans()[name]
+                            _, real_algo, real_ch = pp.registered_plans()[name] if name else (kind, algo, 0)
                             if uses_ll:
                                 real_algo, real_ch = "ll", 0
                             elif uses_push:

@@ -19,7 +19,7 @@ mkdir -p "$OUT"
 RUN="python -m torch.distributed.run --nnodes=1 --nproc-per-node $N --master-addr 127.0.0.1"
 export PCCL_VALIDATE=${PCCL_VALIDATE:-0}          # templates are validated by the test-suite; saves W compilations per plan
 export PCCL_TUNING_FILE=/nonexistent              # "auto" rows must not follow an older table while a new one is measured
-ALGOS=auto,ll,push,ring,rhd,tree,oneshot,twoshot,nvls,hybrid
+ALGOS=auto,ll,push,ring,rhd,tree,oneshot,twoshot,nvls,nvls_kernel,hybrid
 SIZES=""; ITERS=20; SHARD_DTYPES=fp32,bf16
 if [ "${SWEEP_QUICK:-0}" = "1" ]; then
   SIZES="--sizes 1K,4K,16K,64K,256K,1M,4M,16M,64M,256M,1G"; ITERS=10; SHARD_DTYPES=fp32

@@ -66,6 +66,10 @@ OPTIONS: Dict[str, tuple] = {
     "PCCL_GEMM_SMS_PER_TILE": ("gemm_sms_per_tile", int, 2,
                                "2 = pairs of SMs on 256x256 tiles (tcgen05.mma.cta_group::2), 1 = one SM per 128x256 tile"),
     "PCCL_GEMM_TILE_N": ("gemm_tile_n", int, 0, "tile width of the paired GEMM (multiple of 32; 0 = 256)"),
+    "PCCL_GEMM_SPLIT_TAIL": ("gemm_split_tail", _flag, True,
+                             "paired GEMM: cut the tiles of a sparsely filled last round along K"),
+    "PCCL_GEMM_SPLIT_MIN_SLICES": ("gemm_split_min_slices", int, 3, "fewest K slices for which that split is used"),
+    "PCCL_NVLS_CTAS": ("nvls_ctas", int, 128, "grid of the in-switch all-reduce kernel (algorithm \"nvls_kernel\")"),
     "PCCL_LOG_LEVEL": ("log_level", str, "WARN", "TRACE|DEBUG|INFO|WARN|ERROR|CRITICAL"),
     "PCCL_JOB_ID": ("job_id", str, None, "namespace of the fd-passing sockets"),
     "PCCL_DEBUG_ENDPOINT_INIT": ("debug_endpoint_init", _flag, False, "print bootstrap stages"),
@@ -101,6 +105,9 @@ class PcclConfig:
     push_max_bytes: int = 32 << 20
     gemm_sms_per_tile: int = 2
     gemm_tile_n: int = 0
+    gemm_split_tail: bool = True
+    gemm_split_min_slices: int = 3
+    nvls_ctas: int = 128
     log_level: str = "WARN"
     job_id: Optional[str] = None
     debug_endpoint_init: bool = False

@@ -148,6 +148,20 @@ void bind_fused_ops(py::module_& m) {
         },
         py::arg("mode"), py::arg("input"), py::arg("output"), py::arg("area_off"), py::arg("capacity_bytes"),
         py::arg("flags_off"), py::arg("counters"), py::arg("epoch"), py::arg("ctas"), py::arg("error") = py::none());
+  // In-switch all-reduce (sum) of `bytes` at a symmetric-heap offset, in place.
+  f.def("allreduce_nvls",
+        [](int64_t data_off, int64_t bytes, int dtype, int64_t flags_off, torch::Tensor& cta_counter, int64_t epoch,
+           int ctas, c10::optional<torch::Tensor> error) {
+          Engine& e = Engine::instance();
+          TORCH_CHECK(e.nvlsActive(), "allreduce_nvls: the engine has no multicast mapping");
+          gemm::allreduce_nvls(peer_bases(), e.context().heap().mc_base(), static_cast<uint64_t>(data_off),
+                               static_cast<uint64_t>(bytes), dtype, static_cast<uint64_t>(flags_off),
+                               as_u32(cta_counter, 1, "cta_counter"), static_cast<uint32_t>(epoch),
+                               c10::cuda::getCurrentCUDAStream().stream(), ctas, 2000,
+                               error.has_value() ? as_u32(*error, 1, "error") : nullptr);
+        },
+        py::arg("data_off"), py::arg("bytes"), py::arg("dtype"), py::arg("flags_off"), py::arg("cta_counter"),
+        py::arg("epoch"), py::arg("ctas"), py::arg("error") = py::none());
   // MoE router on its own: top-2 expert indices, renormalised gates, the row each choice claims
   // in its expert's batch, and the per-expert token counts.  scratch: int32[experts + 1].
   f.def("moe_route",

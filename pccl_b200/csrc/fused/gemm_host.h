@@ -91,6 +91,14 @@ void collective_push(PushMode mode, const PeerBases& peers, uint64_t area_off, u
                      uint32_t epoch, cudaStream_t stream, int ctas, uint64_t timeout_ms = 2000,
                      uint32_t* error = nullptr);
 
+// Large-message all-reduce (sum) through the switch, in place on `bytes` at symmetric offset data_off
+// (16-byte aligned; bytes a multiple of 16 * world).  mc_base: multicast alias of the heap (required).
+// flags_off: symmetric u32[2 * world], zeroed once; cta_counter: local zero-initialised u32; `ctas` must be
+// the same for every call that shares them.  dtype: 0 f32, 1 f16, 2 bf16.  epoch = 1, 2, 3, ... per call.
+void allreduce_nvls(const PeerBases& peers, uint8_t* mc_base, uint64_t data_off, uint64_t bytes, int dtype,
+                    uint64_t flags_off, uint32_t* cta_counter, uint32_t epoch, cudaStream_t stream, int ctas,
+                    uint64_t timeout_ms = 2000, uint32_t* error = nullptr);
+
 // ---- gradient buckets ------------------------------------------------------------------------------
 // Gather `count` tensors into one bucket (or scatter them back, unpack = true) with one launch per
 // kPackBatch tensors: the table travels in the kernel's parameters, no host-to-device copy.

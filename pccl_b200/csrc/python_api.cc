@@ -121,6 +121,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              return py::make_tuple(heap_tensor(c.heap().data(c.rank()) + off, shape, dtype, c.heap().device()),
                                    static_cast<int64_t>(off));
            })
+      // Offset of a tensor inside this rank's symmetric data region, or -1 when it lives elsewhere.
+      .def("heapOffset",
+           [](Engine& e, const torch::Tensor& t) -> int64_t {
+             RankContext& c = e.context();
+             if (!t.is_cuda()) return -1;
+             const auto* first = static_cast<const uint8_t*>(t.data_ptr());
+             const uint8_t* base = c.heap().data(c.rank());
+             const size_t span = c.heap().layout().data_bytes;
+             if (first < base || first + t.nbytes() > base + span) return -1;
+             return static_cast<int64_t>(first - base);
+           })
       .def("arenaReset", [](Engine& e) { e.context().arena_reset(); })
       .def("peerTensor",
            [](Engine& e, int rank, int64_t heap_offset, const std::vector<int64_t>& shape, torch::ScalarType dtype) {

@@ -57,8 +57,10 @@ def init(group: Optional[dist.ProcessGroup] = None):
         and os.environ.get("PCCL_EXECUTOR") != "cpu" else None
     _state["err_ll"] = _state["errors"][0:1] if _state["errors"] is not None else None
     _state["err_push"] = _state["errors"][1:2] if _state["errors"] is not None else None
+    _state["err_nvls"] = _state["errors"][2:3] if _state["errors"] is not None else None
     _setup_ll(group)
     _setup_push(group)
+    _setup_nvls(group)
     _state["connected"] = True
     return _engine.get_engine()
 
@@ -120,6 +122,52 @@ def _setup_push(group) -> None:
     dist.barrier(group=group)
     _state["push"] = {"areas": areas, "flags": flags, "epoch": 0, "native": _engine.load_native().fused,
                       "counters": torch.zeros(2, dtype=torch.int32, device="cuda")}
+
+
+_NVLS_DTYPE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+
+
+def _setup_nvls(group) -> None:
+    """Flags and counter of the in-switch all-reduce kernel (algorithm "nvls_kernel")."""
+    _state["nvls"] = None
+    eng = _engine.get_engine()
+    if _state["world"] < 2 or not torch.cuda.is_available() or not hasattr(eng, "empty_symmetric") \
+            or os.environ.get("PCCL_EXECUTOR") == "cpu" or not eng.nvls_active():
+        return
+    flags = eng.empty_symmetric((2 * _state["world"],), torch.int32)
+    flags.zero_()
+    torch.cuda.synchronize()
+    dist.barrier(group=group)
+    _state["nvls"] = {"flags": flags, "epoch": 0, "native": _engine.load_native().fused,
+                      "counter": torch.zeros(1, dtype=torch.int32, device="cuda"),
+                      "ctas": max(1, int(os.environ.get("PCCL_NVLS_CTAS", "128")))}
+
+
+def _nvls_kernel_ok(tensor: torch.Tensor, op: str) -> bool:
+    """Sizes, dtype and arguments only (the same answer on every rank); where the tensor lives decides
+    staging, never the path."""
+    nbytes = tensor.numel() * tensor.element_size()
+    return (_state.get("nvls") is not None and op == "sum" and tensor.is_cuda and tensor.dtype in _NVLS_DTYPE
+            and nbytes > 0 and nbytes % (16 * _state["world"]) == 0)
+
+
+def _nvls_kernel(tensor: torch.Tensor) -> None:
+    """In-switch all-reduce of `tensor`, in place when it lies in symmetric memory, else through the
+    working buffer (two device copies more)."""
+    nv = _state["nvls"]
+    eng = _engine.get_engine()
+    nbytes = tensor.numel() * tensor.element_size()
+    offset = eng.native.heapOffset(tensor) if tensor.is_contiguous() else -1
+    staged = None
+    if offset < 0 or offset % 16:
+        staged = eng.working_buffer(tensor.numel(), tensor.dtype)
+        staged.copy_(tensor.reshape(-1))
+        offset = 0
+    nv["epoch"] += 1
+    nv["native"].allreduce_nvls(offset, nbytes, _NVLS_DTYPE[tensor.dtype], nv["flags"].heap_offset, nv["counter"],
+                                nv["epoch"], nv["ctas"], _state["err_nvls"])
+    if staged is not None:
+        tensor.copy_(staged.view_as(tensor) if tensor.is_contiguous() else staged.reshape(tensor.shape))
 
 
 def _push_eligible(tensor: torch.Tensor, op: str, algorithm: Optional[str]) -> bool:
@@ -279,7 +327,7 @@ def _routed_allreduce(nbytes: int) -> Tuple[Optional[str], Optional[int]]:
     if route is None:
         return None, None
     choice = route["algorithm"]
-    if choice in ("ll", "push") or choice in ALGORITHMS:
+    if choice in ("ll", "push", "nvls_kernel") or choice in ALGORITHMS:
         return choice, route.get("channels")
     return None, None
 
@@ -343,9 +391,18 @@ def all_reduce(tensor: torch.Tensor, op: str = "sum", algorithm: Optional[str] =
         routed = _route_cache.get(nbytes)
         if routed is None:
             routed = _route_cache[nbytes] = _routed_allreduce(nbytes)
-        if routed[0] is not None and (routed[0] not in ("ll", "push") or
-                                      (_ll_eligible if routed[0] == "ll" else _push_eligible)(tensor, op, routed[0])):
+        if routed[0] == "nvls_kernel":
+            if _nvls_kernel_ok(tensor, op):
+                algorithm = "nvls_kernel"
+        elif routed[0] is not None and (routed[0] not in ("ll", "push") or
+                                        (_ll_eligible if routed[0] == "ll" else _push_eligible)(tensor, op, routed[0])):
             algorithm, channels = routed[0], channels or routed[1]
+    if algorithm == "nvls_kernel":
+        if not _nvls_kernel_ok(tensor, op):
+            raise ValueError("the in-switch all-reduce kernel takes f32/f16/bf16 sums of a multiple of 16 * world "
+                             "bytes on an engine with NVLS")
+        _nvls_kernel(tensor)
+        return tensor
     if _ll_eligible(tensor, op, algorithm):
         ll = _state["ll"]
         ll["epoch"] += 1
@@ -416,7 +473,9 @@ def all_to_all(output: torch.Tensor, input: torch.Tensor, algorithm: Optional[st
 
 _FUSED_CODES = {0x701: "packet all-reduce: a peer's packets did not arrive",
                 0x801: "push collective: a peer's first flag did not arrive",
-                0x802: "push collective: a peer's second flag did not arrive"}
+                0x802: "push collective: a peer's second flag did not arrive",
+                0x901: "in-switch all-reduce: a peer's input flag did not arrive",
+                0x902: "in-switch all-reduce: a peer's delivery flag did not arrive"}
 
 
 def check_errors() -> None:
@@ -456,6 +515,11 @@ def reset() -> None:
         push["flags"].zero_()
         push["counters"].zero_()
         push["epoch"] = 0
+    nvls = _state.get("nvls")
+    if nvls is not None:
+        nvls["flags"].zero_()
+        nvls["counter"].zero_()
+        nvls["epoch"] = 0
     if errors is not None:
         errors.zero_()
     engine = _engine.get_engine()

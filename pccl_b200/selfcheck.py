@@ -57,6 +57,25 @@ def _allreduce_plan(algorithm: str, dtype=torch.float32, numel_per_rank: int = 6
     return case
 
 
+def _switch_kernel_allreduce(c: _Ctx):
+    """The in-switch all-reduce kernel: in place on a symmetric tensor and staged on an ordinary one,
+    twice each (call counting)."""
+    for dtype in (torch.float32, torch.bfloat16):
+        n = c.world * 98304
+        x = _randn(n, 300 + c.rank, dtype)
+        ref = x.float().clone()
+        dist.all_reduce(ref)
+        sym = c.pp.working_tensor(n, dtype)
+        for _ in range(2):
+            sym.copy_(x)
+            c.pp.all_reduce(sym, algorithm="nvls_kernel")
+            c.pp.synchronize()
+            torch.testing.assert_close(sym.float(), ref, **_tol(dtype))
+            y = c.pp.all_reduce(x.clone(), algorithm="nvls_kernel")
+            c.pp.synchronize()
+            torch.testing.assert_close(y.float(), ref, **_tol(dtype))
+
+
 def _packet_allreduce(c: _Ctx):
     for dtype in (torch.float32, torch.bfloat16):
         x = _randn(16384, 7 + c.rank, dtype)
@@ -349,6 +368,7 @@ def cases(nvls: bool) -> List[Tuple[str, Callable[[_Ctx], None]]]:
             ("plan_nvls_allreduce", _allreduce_plan("nvls")),
             ("plan_nvls_allreduce_bf16", _allreduce_plan("nvls", torch.bfloat16)),
             ("plan_hybrid_allreduce", _allreduce_plan("hybrid", channels=4)),
+            ("switch_kernel_allreduce", _switch_kernel_allreduce),
             ("plan_nvls_rs_ag", _plan_shards("nvls")),
             ("ar_residual_rmsnorm_nvls", _ar_rmsnorm("force")),
         ]
