@@ -265,7 +265,7 @@ def run_ours(args):
             "dtype": "fp32", "data": "synthetic randn(seed=rank)",
             "config": {"model": "allreduce_sum", "global_batch": args.bytes, "seq_len": numel,
                        "parallelism": f"dp{world}", "algorithm": algorithm, "channels": channels,
-                       "nvls": nvls, "ctas": stats.get("ctas") if name else int(os.environ.get("PCCL_NVLS_CTAS", "128")),
+                       "nvls": nvls, "ctas": stats.get("ctas") if name else int(os.environ.get("PCCL_NVLS_CTAS", "64")),
                        "in_place": True, "l2": "message (512 MB) exceeds the 126 MB L2; no flush needed",
                        "max_abs_err_all_elements_vs_nccl": final_err,
                        "candidates_ms": tried, "candidates_max_abs_err": errors,

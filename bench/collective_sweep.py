@@ -216,6 +216,9 @@ def run_multi(args):
     dist.destroy_process_group()
 
 
+_KERNEL_ROUTES = ("ll", "push", "nvls_kernel")
+
+
 def write_tuning(path, world, rows):
     """Merge this sweep's winners into the tuning file: per collective, break points
     [{"max_bytes", "algorithm", "channels", "us"}] where consecutive sizes with the same winner are
@@ -249,7 +252,16 @@ def write_tuning(path, world, rows):
             entry = {"max_bytes": nbytes, "algorithm": best["algo"], "us": best["us"]}
             if best["channels"]:
                 entry["channels"] = best["channels"]
-            if table and table[-1]["algorithm"] == entry["algorithm"] and table[-1].get("channels") == entry.get("channels"):
+            if best["algo"] in _KERNEL_ROUTES:
+                # a kernel won: also name the best plan, for callers the kernel does not take
+                plans = [r for r in cands if r["algo"] not in _KERNEL_ROUTES]
+                if plans:
+                    best_plan = min(plans, key=lambda r: r["us"])
+                    kept = [r for r in plans if table and r["algo"] == table[-1].get("plan_algorithm")]
+                    if kept and min(r["us"] for r in kept) <= 1.05 * best_plan["us"]:
+                        best_plan = kept[0]
+                    entry["plan_algorithm"] = best_plan["algo"]
+            if table and all(table[-1].get(k) == entry.get(k) for k in ("algorithm", "channels", "plan_algorithm")):
                 table[-1].update(max_bytes=nbytes, us=best["us"])
             else:
                 table.append(entry)

@@ -69,7 +69,7 @@ OPTIONS: Dict[str, tuple] = {
     "PCCL_GEMM_SPLIT_TAIL": ("gemm_split_tail", _flag, True,
                              "paired GEMM: cut the tiles of a sparsely filled last round along K"),
     "PCCL_GEMM_SPLIT_MIN_SLICES": ("gemm_split_min_slices", int, 3, "fewest K slices for which that split is used"),
-    "PCCL_NVLS_CTAS": ("nvls_ctas", int, 128, "grid of the in-switch all-reduce kernel (algorithm \"nvls_kernel\")"),
+    "PCCL_NVLS_CTAS": ("nvls_ctas", int, 64, "grid of the in-switch all-reduce kernel (algorithm \"nvls_kernel\")"),
     "PCCL_LOG_LEVEL": ("log_level", str, "WARN", "TRACE|DEBUG|INFO|WARN|ERROR|CRITICAL"),
     "PCCL_JOB_ID": ("job_id", str, None, "namespace of the fd-passing sockets"),
     "PCCL_DEBUG_ENDPOINT_INIT": ("debug_endpoint_init", _flag, False, "print bootstrap stages"),
@@ -107,7 +107,7 @@ class PcclConfig:
     gemm_tile_n: int = 0
     gemm_split_tail: bool = True
     gemm_split_min_slices: int = 3
-    nvls_ctas: int = 128
+    nvls_ctas: int = 64
     log_level: str = "WARN"
     job_id: Optional[str] = None
     debug_endpoint_init: bool = False

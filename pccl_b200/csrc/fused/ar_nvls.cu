@@ -79,24 +79,22 @@ __global__ void __launch_bounds__(kNvlsThreads) allreduce_nvls_kernel(const Nvls
   __syncthreads();
   if (!s_ok) return;
 
-  // 2. this rank's part: sum in the switch, deliver to everyone.  All loads of a round are issued
-  //    before the first store; the tail re-reads the part's last vector and skips its store.
+  // 2. this rank's part: sum in the switch, deliver to everyone.  Full rounds issue all their loads,
+  //    unconditionally, before the first store; what is left goes one vector per thread.  (No lane
+  //    re-reads a clamped address to stay unconditional here: a redundant multimem load is a
+  //    redundant reduction in the switch.)
   const uint64_t per = p.vecs / world, first = per * me;
-  uint8_t* mc = p.mc_base + p.data_off;
+  uint8_t* mc = p.mc_base + p.data_off + first * 16;
   const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kNvlsThreads;
-  for (uint64_t v0 = static_cast<uint64_t>(blockIdx.x) * kNvlsThreads + threadIdx.x; v0 < per; v0 += stride * kNvlsUnroll) {
+  uint64_t v0 = static_cast<uint64_t>(blockIdx.x) * kNvlsThreads + threadIdx.x;
+  for (; v0 + (kNvlsUnroll - 1) * stride < per; v0 += stride * kNvlsUnroll) {
     uint4 x[kNvlsUnroll];
 #pragma unroll
-    for (int u = 0; u < kNvlsUnroll; ++u) {
-      const uint64_t v = v0 + u * stride;
-      x[u] = switch_sum<DT>(mc + (first + (v < per ? v : per - 1)) * 16);
-    }
+    for (int u = 0; u < kNvlsUnroll; ++u) x[u] = switch_sum<DT>(mc + (v0 + u * stride) * 16);
 #pragma unroll
-    for (int u = 0; u < kNvlsUnroll; ++u) {
-      const uint64_t v = v0 + u * stride;
-      if (v < per) ptx::mm_st_v4(mc + (first + v) * 16, x[u]);
-    }
+    for (int u = 0; u < kNvlsUnroll; ++u) ptx::mm_st_v4(mc + (v0 + u * stride) * 16, x[u]);
   }
+  for (; v0 < per; v0 += stride) ptx::mm_st_v4(mc + v0 * 16, switch_sum<DT>(mc + v0 * 16));
 
   // 3. "delivered" -> every peer once all CTAs of this rank are through (the CTA that completes the
   //    count fences at system scope: cumulative over the arrivals it counted); that CTA then waits

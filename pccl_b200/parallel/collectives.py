@@ -140,7 +140,7 @@ def _setup_nvls(group) -> None:
     dist.barrier(group=group)
     _state["nvls"] = {"flags": flags, "epoch": 0, "native": _engine.load_native().fused,
                       "counter": torch.zeros(1, dtype=torch.int32, device="cuda"),
-                      "ctas": max(1, int(os.environ.get("PCCL_NVLS_CTAS", "128")))}
+                      "ctas": max(1, int(os.environ.get("PCCL_NVLS_CTAS", "64")))}
 
 
 def _nvls_kernel_ok(tensor: torch.Tensor, op: str) -> bool:
@@ -149,6 +149,13 @@ def _nvls_kernel_ok(tensor: torch.Tensor, op: str) -> bool:
     nbytes = tensor.numel() * tensor.element_size()
     return (_state.get("nvls") is not None and op == "sum" and tensor.is_cuda and tensor.dtype in _NVLS_DTYPE
             and nbytes > 0 and nbytes % (16 * _state["world"]) == 0)
+
+
+def _is_symmetric(tensor: torch.Tensor) -> bool:
+    eng = _engine.get_engine()
+    native = getattr(eng, "native", None)
+    return bool(tensor.is_cuda and tensor.is_contiguous() and native is not None
+                and native.heapOffset(tensor) >= 0 and native.heapOffset(tensor) % 16 == 0)
 
 
 def _nvls_kernel(tensor: torch.Tensor) -> None:
@@ -392,7 +399,11 @@ def all_reduce(tensor: torch.Tensor, op: str = "sum", algorithm: Optional[str] =
         if routed is None:
             routed = _route_cache[nbytes] = _routed_allreduce(nbytes)
         if routed[0] == "nvls_kernel":
-            if _nvls_kernel_ok(tensor, op):
+            # The table is measured in place on symmetric tensors.  An ordinary tensor would be staged
+            # through the working buffer (two copies more), which only pays above the push kernel's
+            # range.  Where a tensor lives is the same on every rank by construction: symmetric
+            # allocations are collective calls.
+            if _nvls_kernel_ok(tensor, op) and (nbytes > PUSH_MAX_BYTES or _is_symmetric(tensor)):
                 algorithm = "nvls_kernel"
         elif routed[0] is not None and (routed[0] not in ("ll", "push") or
                                         (_ll_eligible if routed[0] == "ll" else _push_eligible)(tensor, op, routed[0])):
