@@ -131,14 +131,14 @@ def run_multi(args):
                 for algo in args.algos:
                     allowed = {"allreduce": ("auto", "ll", "push", "ring", "rhd", "tree", "oneshot", "twoshot", "nvls",
                                              "nvls_twopass", "hybrid", "nvls_kernel"),
-                               "allgather": ("auto", "push", "ring", "rhd", "twoshot", "nvls"),
-                               "reduce_scatter": ("auto", "push", "ring", "rhd", "twoshot", "nvls"),
-                               "alltoall": ("auto", "push", "ring", "twoshot")}[kind]
+                               "allgather": ("auto", "ll", "push", "ring", "rhd", "twoshot", "nvls"),
+                               "reduce_scatter": ("auto", "ll", "push", "ring", "rhd", "twoshot", "nvls"),
+                               "alltoall": ("auto", "ll", "push", "ring", "twoshot")}[kind]
                     if algo not in allowed:
                         continue
                     if algo == "oneshot" and nbytes > (4 << 20):
                         continue
-                    if algo == "ll" and (kind != "allreduce" or nbytes > pp.collectives.LL_MAX_BYTES):
+                    if algo == "ll" and (nbytes if kind == "allreduce" else nbytes // world) > pp.collectives.LL_MAX_BYTES:
                         continue
                     if algo == "push" and nbytes > pp.collectives.PUSH_MAX_BYTES:
                         continue
@@ -149,7 +149,7 @@ def run_multi(args):
                     for ch in args.channels:
                         forced_algo = None if algo == "auto" else algo
                         forced_ch = None if ch == "auto" else int(ch)
-                        plan_algo = None if forced_algo == "push" else forced_algo      # plan registered for reporting
+                        plan_algo = None if forced_algo in ("push", "ll") else forced_algo   # plan registered for reporting
                         try:
                             uses_ll = kind == "allreduce" and algo in ("auto", "ll") and \
                                 pp.collectives._ll_eligible(full, "sum", forced_algo)
@@ -165,16 +165,19 @@ def run_multi(args):
                             elif kind == "allgather":
                                 name = pp.ensure_plan(kind, numel, dtype, plan_algo, forced_ch)
                                 mine = full[rank * shard:(rank + 1) * shard]
-                                uses_push = pp.collectives._push_ok(full, mine, forced_algo)
+                                uses_ll = pp.collectives._ll_part_ok(mine, full, forced_algo)
+                                uses_push = not uses_ll and pp.collectives._push_ok(full, mine, forced_algo)
                                 call = lambda: pp.all_gather(full, mine, algorithm=forced_algo, channels=forced_ch, async_op=True)
                             elif kind == "reduce_scatter":
                                 name = pp.ensure_plan(kind, numel, dtype, plan_algo, forced_ch)
                                 mine = full[rank * shard:(rank + 1) * shard]
-                                uses_push = pp.collectives._push_ok(full, mine, forced_algo)
+                                uses_ll = pp.collectives._ll_part_ok(mine, full, forced_algo)
+                                uses_push = not uses_ll and pp.collectives._push_ok(full, mine, forced_algo)
                                 call = lambda: pp.reduce_scatter(mine, full, algorithm=forced_algo, channels=forced_ch, async_op=True)
                             else:
                                 name = pp.ensure_plan(kind, numel, dtype, plan_algo or "twoshot", forced_ch)
-                                uses_push = pp.collectives._push_ok(full, nccl_out, forced_algo)
+                                uses_ll = pp.collectives._ll_part_ok(full[:shard], nccl_out, forced_algo)
+                                uses_push = not uses_ll and pp.collectives._push_ok(full, nccl_out, forced_algo)
                                 call = lambda: pp.all_to_all(nccl_out, full, algorithm=forced_algo, channels=forced_ch,
                                                             async_op=True)
                         except Exception as err:  # noqa: BLE001

@@ -31,6 +31,6 @@ $RUN --master-port 29602 "$HERE/bench/collective_sweep.py" --collectives allredu
     --min-bytes 256K --max-bytes 512M --sizes 256K,16M,512M --algos ring,twoshot,nvls --channels 1,2,4,8,16,32 --iters 10 \
     --out "$OUT/sweep_${N}gpu_channels.json" > "$OUT/sweep_${N}gpu_channels.log" 2>&1
 $RUN --master-port 29603 "$HERE/bench/collective_sweep.py" --collectives allgather,reduce_scatter --dtypes $SHARD_DTYPES \
-    --min-bytes 1K --max-bytes 1G $SIZES --algos auto,push,ring,twoshot,nvls --channels auto --iters $ITERS \
+    --min-bytes 1K --max-bytes 1G $SIZES --algos auto,ll,push,ring,twoshot,nvls --channels auto --iters $ITERS \
     --out "$OUT/sweep_${N}gpu_shards.json" --write-tuning "$TUNING" > "$OUT/sweep_${N}gpu_shards.log" 2>&1
 grep -c '^{' "$OUT"/sweep_${N}gpu_*.log

@@ -37,6 +37,8 @@ struct LLParams {
   uint2* out;
   uint64_t units;
   int dtype;                 // 0 f32, 1 f16, 2 bf16
+  int mode;                  // 0 all-reduce (units = whole message); 1 reduce-scatter, 2 all-gather,
+                             // 3 all-to-all (units = one rank's part)
   uint32_t flag;             // call number, never 0
   uint32_t* error;
   uint64_t timeout_ns;
@@ -92,42 +94,72 @@ __global__ void __launch_bounds__(kLLThreads) allreduce_ll_kernel(const LLParams
   const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
   const uint64_t first = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
 
-  // 1. push my units to every peer's slot for this source
-  for (uint64_t i = first; i < p.units; i += stride) {
-    const uint2 d = p.in[i];
-    for (int k = 1; k < world; ++k) {
-      const int peer = (me + k) % world;
-      uint4* slot = reinterpret_cast<uint4*>(p.peers.base[peer] + p.buf_off) +
-                    (parity * world + me) * p.capacity_units + i;
-      st_packet(slot, d, p.flag);
-    }
-  }
-  // 2. poll the peers' packets and reduce in rank order
   const uint64_t deadline = ptx::globaltimer() + p.timeout_ns;
   const uint4* mine = reinterpret_cast<const uint4*>(p.peers.base[me] + p.buf_off) + parity * world * p.capacity_units;
-  for (uint64_t i = first; i < p.units; i += stride) {
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int s = 0; s < world; ++s) {
-      uint2 d;
-      if (s == me) {
-        d = p.in[i];
-      } else {
-        const uint4* slot = mine + s * p.capacity_units + i;
-        uint4 v = ld_packet(slot);
-        uint32_t spins = 0;
-        while (v.y != p.flag || v.w != p.flag) {
-          if ((++spins & 255u) == 0u && (*reinterpret_cast<volatile uint32_t*>(p.error) ||
-                                          ptx::globaltimer() > deadline)) {
-            atomicCAS(p.error, 0u, 0x701u);
-            return;
-          }
-          v = ld_packet(slot);
-        }
-        d = make_uint2(v.x, v.z);
+  // Packet `i` of source `s` in this rank's buffer; null (with the error word set) when it never arrived.
+  auto receive = [&](int s, uint64_t i, uint2* d) {
+    const uint4* slot = mine + s * p.capacity_units + i;
+    uint4 v = ld_packet(slot);
+    uint32_t spins = 0;
+    while (v.y != p.flag || v.w != p.flag) {
+      if ((++spins & 255u) == 0u && (*reinterpret_cast<volatile uint32_t*>(p.error) || ptx::globaltimer() > deadline)) {
+        atomicCAS(p.error, 0u, 0x701u);
+        return false;
       }
-      accumulate<DT>(acc, d);
+      v = ld_packet(slot);
     }
-    p.out[i] = finish<DT>(acc);
+    *d = make_uint2(v.x, v.z);
+    return true;
+  };
+  auto slot_at = [&](int peer, uint64_t i) {
+    return reinterpret_cast<uint4*>(p.peers.base[peer] + p.buf_off) + (parity * world + me) * p.capacity_units + i;
+  };
+
+  if (p.mode == 0) {
+    // all-reduce.  1. push my units to every peer's slot for this source
+    for (uint64_t i = first; i < p.units; i += stride) {
+      const uint2 d = p.in[i];
+      for (int k = 1; k < world; ++k) st_packet(slot_at((me + k) % world, i), d, p.flag);
+    }
+    // 2. poll the peers' packets and reduce in rank order
+    for (uint64_t i = first; i < p.units; i += stride) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int s = 0; s < world; ++s) {
+        uint2 d;
+        if (s == me) d = p.in[i];
+        else if (!receive(s, i, &d)) return;
+        accumulate<DT>(acc, d);
+      }
+      p.out[i] = finish<DT>(acc);
+    }
+    return;
+  }
+  // The other three move one part per peer: part `peer` of the input for reduce-scatter and
+  // all-to-all, the whole (one-part) input for all-gather.
+  for (uint64_t i = first; i < p.units; i += stride) {
+    for (int k = 1; k < world; ++k) {
+      const int peer = (me + k) % world;
+      st_packet(slot_at(peer, i), p.in[p.mode == 2 ? i : peer * p.units + i], p.flag);
+    }
+  }
+  for (uint64_t i = first; i < p.units; i += stride) {
+    if (p.mode == 1) {                                   // reduce-scatter: rank-ordered fp32 sum of my part
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int s = 0; s < world; ++s) {
+        uint2 d;
+        if (s == me) d = p.in[me * p.units + i];
+        else if (!receive(s, i, &d)) return;
+        accumulate<DT>(acc, d);
+      }
+      p.out[i] = finish<DT>(acc);
+    } else {                                             // all-gather / all-to-all: part s of the output came from s
+      for (int s = 0; s < world; ++s) {
+        uint2 d;
+        if (s == me) d = p.in[p.mode == 2 ? i : me * p.units + i];
+        else if (!receive(s, i, &d)) return;
+        p.out[s * p.units + i] = d;
+      }
+    }
   }
 }
 
@@ -136,6 +168,13 @@ __global__ void __launch_bounds__(kLLThreads) allreduce_ll_kernel(const LLParams
 void allreduce_ll(const PeerBases& peers, uint64_t buf_off, uint64_t capacity_bytes, const void* in, void* out,
                   uint64_t bytes, int dtype, uint32_t epoch, cudaStream_t stream, uint64_t timeout_ms,
                   uint32_t* error) {
+  collective_ll(0, peers, buf_off, capacity_bytes, in, out, bytes, dtype, epoch, stream, timeout_ms, error);
+}
+
+void collective_ll(int mode, const PeerBases& peers, uint64_t buf_off, uint64_t capacity_bytes, const void* in,
+                   void* out, uint64_t bytes, int dtype, uint32_t epoch, cudaStream_t stream, uint64_t timeout_ms,
+                   uint32_t* error) {
+  PCCL_CHECK(mode >= 0 && mode <= 3, "LL collective: mode 0..3");
   PCCL_CHECK(bytes % 8 == 0 && bytes > 0, "LL all-reduce: size must be a positive multiple of 8 bytes");
   PCCL_CHECK(bytes <= capacity_bytes, "LL all-reduce: " << bytes << " bytes exceed the buffer's " << capacity_bytes);
   PCCL_CHECK(reinterpret_cast<uintptr_t>(in) % 8 == 0 && reinterpret_cast<uintptr_t>(out) % 8 == 0,
@@ -150,6 +189,7 @@ void allreduce_ll(const PeerBases& peers, uint64_t buf_off, uint64_t capacity_by
   p.out = static_cast<uint2*>(out);
   p.units = bytes / 8;
   p.dtype = dtype;
+  p.mode = mode;
   p.flag = epoch;
   p.error = error ? error : error_word();
   p.timeout_ns = timeout_ms * 1000000ull;

@@ -121,6 +121,31 @@ void bind_fused_ops(py::module_& m) {
         },
         py::arg("input"), py::arg("output"), py::arg("buf_off"), py::arg("capacity_bytes"), py::arg("epoch"),
         py::arg("error") = py::none());
+  // Packet-protocol reduce-scatter (1), all-gather (2), all-to-all (3); sizes follow the collective.
+  f.def("collective_ll",
+        [](int mode, const torch::Tensor& in, torch::Tensor& out, int64_t buf_off, int64_t capacity_bytes, int64_t epoch,
+           c10::optional<torch::Tensor> error) {
+          TORCH_CHECK(in.is_cuda() && out.is_cuda() && in.is_contiguous() && out.is_contiguous() &&
+                          in.scalar_type() == out.scalar_type(), "collective_ll: contiguous CUDA tensors of one dtype");
+          TORCH_CHECK(mode >= 1 && mode <= 3, "collective_ll: mode 1..3");
+          int dtype = -1;
+          if (in.scalar_type() == torch::kFloat32) dtype = 0;
+          else if (in.scalar_type() == torch::kFloat16) dtype = 1;
+          else if (in.scalar_type() == torch::kBFloat16) dtype = 2;
+          TORCH_CHECK(dtype >= 0, "collective_ll: float32, float16 or bfloat16");
+          const gemm::PeerBases peers = peer_bases();
+          const int64_t part = mode == 2 ? in.nbytes() : out.nbytes() / (mode == 3 ? peers.world : 1);
+          const int64_t want_in = mode == 2 ? part : part * peers.world;
+          const int64_t want_out = mode == 1 ? part : part * peers.world;
+          TORCH_CHECK(static_cast<int64_t>(in.nbytes()) == want_in && static_cast<int64_t>(out.nbytes()) == want_out,
+                      "collective_ll: tensor sizes do not match the collective");
+          gemm::collective_ll(mode, peers, static_cast<uint64_t>(buf_off), static_cast<uint64_t>(capacity_bytes),
+                              in.data_ptr(), out.data_ptr(), static_cast<uint64_t>(part), dtype,
+                              static_cast<uint32_t>(epoch), c10::cuda::getCurrentCUDAStream().stream(), 2000,
+                              error.has_value() ? as_u32(*error, 1, "error") : nullptr);
+        },
+        py::arg("mode"), py::arg("input"), py::arg("output"), py::arg("buf_off"), py::arg("capacity_bytes"),
+        py::arg("epoch"), py::arg("error") = py::none());
   // Fused push collectives (mode: 0 all-reduce, 1 reduce-scatter, 2 all-gather, 3 all-to-all).
   f.def("collective_push",
         [](int mode, const torch::Tensor& in, torch::Tensor& out, int64_t area_off, int64_t capacity_bytes,

@@ -74,6 +74,16 @@ void allreduce_ll(const PeerBases& peers, uint64_t buf_off, uint64_t capacity_by
                   uint64_t bytes, int dtype, uint32_t epoch, cudaStream_t stream, uint64_t timeout_ms = 2000,
                   uint32_t* error = nullptr);
 
+// The same packet protocol for the other collectives (sum where one is taken).  `bytes` is ONE RANK'S PART:
+//   mode 1 reduce-scatter  in [world * bytes], out [bytes] = the sum of every rank's part `rank`
+//   mode 2 all-gather      in [bytes],         out [world * bytes]
+//   mode 3 all-to-all      in [world * bytes] (part p goes to rank p), out [world * bytes] (part s came from s)
+//   mode 0 all-reduce      in, out [bytes] (allreduce_ll)
+// All modes share buf_off and the call counter `epoch`: consecutive calls of any mode alternate the parity.
+void collective_ll(int mode, const PeerBases& peers, uint64_t buf_off, uint64_t capacity_bytes, const void* in,
+                   void* out, uint64_t bytes, int dtype, uint32_t epoch, cudaStream_t stream,
+                   uint64_t timeout_ms = 2000, uint32_t* error = nullptr);
+
 // Fused push collectives for small and medium messages; in / out are ordinary device tensors.
 //   kPushAllReduce      sum; push reduce-scatter, reduce, push all-gather; out may alias in
 //   kPushReduceScatter  sum; in [bytes], out [bytes / world] = this rank's slice

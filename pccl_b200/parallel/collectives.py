@@ -234,6 +234,29 @@ def _ll_eligible(tensor: torch.Tensor, op: str, algorithm: Optional[str]) -> boo
             and tensor.dtype in (torch.float32, torch.float16, torch.bfloat16))
 
 
+def _ll_part_ok(part: torch.Tensor, full: torch.Tensor, algorithm: Optional[str], executor: Optional[str] = None,
+                op: str = "sum") -> bool:
+    """Reduce-scatter / all-gather / all-to-all through the packet kernel: `part` is what one rank sends
+    to (or receives from) one peer.  Sizes, dtype and arguments only.  Unforced, the packet kernel
+    takes parts of up to half its buffer; ``algorithm="ll"`` takes what fits."""
+    ll = _state.get("ll")
+    if ll is None or op != "sum" or algorithm not in (None, "ll") or executor is not None:
+        return False
+    nbytes = part.numel() * part.element_size()
+    limit = LL_MAX_BYTES if algorithm == "ll" else LL_MAX_BYTES // 2
+    return (part.is_cuda and full.is_cuda and part.dtype == full.dtype and nbytes % 8 == 0 and 0 < nbytes <= limit
+            and part.dtype in (torch.float32, torch.float16, torch.bfloat16))
+
+
+def _ll_collective(mode: int, input: torch.Tensor, output: torch.Tensor) -> None:
+    ll = _state["ll"]
+    ll["epoch"] += 1
+    src, dst = _aligned(input, 8), _aligned(output, 8)
+    ll["native"].collective_ll(mode, src, dst, ll["buf"].heap_offset, LL_MAX_BYTES, ll["epoch"], _state["err_ll"])
+    if dst is not output:
+        output.copy_(dst)
+
+
 def working_tensor(shape, dtype=torch.float32) -> torch.Tensor:
     """Tensor that aliases the engine's working buffer (offset 0)."""
     return _engine.working_buffer(shape, dtype)
@@ -447,9 +470,15 @@ def reduce_scatter(output: torch.Tensor, input: torch.Tensor, op: str = "sum",
     """``async_op``: enqueue on the current stream and return (``synchronize`` checks the status later).
 
     Sums of up to ``PUSH_MAX_BYTES`` run in the fused push kernel unless an algorithm is forced."""
-    if output.numel() * _state["world"] == input.numel() and _push_ok(input, output, algorithm, op=op):
-        _push(1, input, output)
-        return output
+    if output.numel() * _state["world"] == input.numel():
+        if _ll_part_ok(output, input, algorithm, op=op):
+            _ll_collective(1, input, output)
+            return output
+        if _push_ok(input, output, algorithm, op=op):
+            _push(1, input, output)
+            return output
+    if algorithm in ("ll", "push"):
+        raise ValueError(f"the {algorithm} reduce-scatter takes f32/f16/bf16 sums within its size limit")
     name = ensure_plan("reduce_scatter", input.numel(), input.dtype, algorithm, channels, op)
     _run(name, input, output, async_op)
     return output
@@ -459,9 +488,15 @@ def all_gather(output: torch.Tensor, input: torch.Tensor, algorithm: Optional[st
                channels: Optional[int] = None, executor: Optional[str] = None,
                async_op: bool = False) -> torch.Tensor:
     """``executor="ce"`` moves the shards with the copy engines (``algorithm`` twoshot)."""
-    if input.numel() * _state["world"] == output.numel() and _push_ok(output, input, algorithm, executor):
-        _push(2, input, output)
-        return output
+    if input.numel() * _state["world"] == output.numel():
+        if _ll_part_ok(input, output, algorithm, executor):
+            _ll_collective(2, input, output)
+            return output
+        if _push_ok(output, input, algorithm, executor):
+            _push(2, input, output)
+            return output
+    if algorithm in ("ll", "push"):
+        raise ValueError(f"the {algorithm} all-gather takes f32/f16/bf16 tensors within its size limit")
     if executor == "ce":
         algorithm = "twoshot"
     name = ensure_plan("allgather", output.numel(), output.dtype, algorithm, channels, executor=executor)
@@ -472,9 +507,15 @@ def all_gather(output: torch.Tensor, input: torch.Tensor, algorithm: Optional[st
 def all_to_all(output: torch.Tensor, input: torch.Tensor, algorithm: Optional[str] = None,
                channels: Optional[int] = None, executor: Optional[str] = None,
                async_op: bool = False) -> torch.Tensor:
-    if input.numel() == output.numel() and _push_ok(input, output, algorithm, executor):
-        _push(3, input, output)
-        return output
+    if input.numel() == output.numel() and input.numel() % _state["world"] == 0:
+        if _ll_part_ok(input[:input.numel() // _state["world"]], output, algorithm, executor):
+            _ll_collective(3, input, output)
+            return output
+        if _push_ok(input, output, algorithm, executor):
+            _push(3, input, output)
+            return output
+    if algorithm in ("ll", "push"):
+        raise ValueError(f"the {algorithm} all-to-all takes f32/f16/bf16 tensors within its size limit")
     if executor == "ce":
         algorithm = "twoshot"
     name = ensure_plan("alltoall", input.numel(), input.dtype, algorithm or "twoshot", channels, executor=executor)

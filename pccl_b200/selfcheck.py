@@ -120,6 +120,38 @@ def _push_mode(mode: str):
     return case
 
 
+def _packet_shard_collectives(c: _Ctx):
+    """Reduce-scatter, all-gather (also with the input inside the output) and all-to-all through the packet
+    kernel, interleaved with packet all-reduces (they share the buffer and the call counter)."""
+    pp, world, rank = c.pp, c.world, c.rank
+    for dtype, shard in ((torch.float32, 4096), (torch.bfloat16, 10240)):
+        n = shard * world
+        full = _randn(n, 41 + rank, dtype)
+        mine = _randn(shard, 67 + rank, dtype)
+        tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=0.06, rtol=2e-2)
+        ref = torch.empty(shard, device="cuda")
+        dist.reduce_scatter_tensor(ref, full.float())
+        got = pp.reduce_scatter(torch.empty(shard, device="cuda", dtype=dtype), full, algorithm="ll")
+        torch.testing.assert_close(got.float(), ref, **tol)
+        ref = torch.empty(n, device="cuda", dtype=dtype)
+        dist.all_gather_into_tensor(ref, mine)
+        got = pp.all_gather(torch.empty(n, device="cuda", dtype=dtype), mine, algorithm="ll")
+        assert torch.equal(got, ref), "packet all_gather differs from NCCL"
+        inplace = torch.zeros(n, device="cuda", dtype=dtype)
+        inplace[rank * shard:(rank + 1) * shard] = mine
+        pp.all_gather(inplace, inplace[rank * shard:(rank + 1) * shard])     # unforced: small parts take this path
+        assert torch.equal(inplace, ref), "in-place packet all_gather differs from NCCL"
+        x = _randn(2048, 5 + rank, dtype)
+        want = x.float().clone()
+        dist.all_reduce(want)
+        torch.testing.assert_close(pp.all_reduce(x.clone(), algorithm="ll").float(), want, **tol)
+        ref = torch.empty(n, device="cuda", dtype=dtype)
+        dist.all_to_all_single(ref, full)
+        got = pp.all_to_all(torch.empty(n, device="cuda", dtype=dtype), full, algorithm="ll")
+        assert torch.equal(got, ref), "packet all_to_all differs from NCCL"
+    pp.synchronize()
+
+
 def _misaligned_views_take_the_same_path(c: _Ctx):
     """One rank passes a view that is not 16-byte (nor 8-byte) aligned: every rank must still run the
     same kernel, and the reduction must land in that view."""
@@ -356,6 +388,7 @@ def cases(nvls: bool) -> List[Tuple[str, Callable[[_Ctx], None]]]:
         ("plan_twoshot_rs_ag", _plan_shards("twoshot")),
         ("copy_engine_all_gather", _copy_engine_all_gather),
         ("ar_residual_rmsnorm_peer", _ar_rmsnorm(False)),
+        ("packet_shard_collectives", _packet_shard_collectives),
         ("gemm_reduce_scatter", _gemm_reduce_scatter),
         ("all_gather_gemm", _all_gather_gemm),
         ("expert_parallel_moe", _expert_parallel_moe),
