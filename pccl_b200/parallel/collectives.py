@@ -414,6 +414,15 @@ def all_reduce(tensor: torch.Tensor, op: str = "sum", algorithm: Optional[str] =
     and sums of up to ``PUSH_MAX_BYTES`` through the fused push kernel (both: no plan, no staging copy,
     asynchronous on the current stream); everything else runs as a plan.
     """
+    if op == "avg" and algorithm in (None, "ll", "push", "nvls_kernel") and tensor.dtype in _NVLS_DTYPE \
+            and (_state.get("ll") or _state.get("push") or _state.get("nvls")):
+        # The fused kernels sum; the average is the sum times 1 / world (one element-wise pass, as the
+        # plans' own avg does).  Which kernel runs is decided exactly as for a sum.
+        all_reduce(tensor, "sum", algorithm, channels, async_op=True)
+        tensor.mul_(1.0 / _state["world"])
+        if not async_op:
+            synchronize()
+        return tensor
     if algorithm is None and op == "sum":
         # A measured table, when one covers this world size, says which path wins at this size
         # (same file on every rank, so every rank takes the same path).  Looked up once per size.

@@ -213,6 +213,8 @@ def test_selector_follows_a_tuning_file(tmp_path, monkeypatch):
     doc = json.loads(path.read_text())
     assert [e["algorithm"] for e in doc["routes"]["allreduce"]["8"]] == ["ll", "twoshot", "nvls"]
     assert doc["routes"]["allreduce"]["8"][-1]["max_bytes"] is None and "4" in doc["routes"]["allreduce"]
+    # where a kernel wins, the best plan is named beside it (for callers the kernel does not take)
+    assert doc["routes"]["allreduce"]["8"][0]["plan_algorithm"] == "twoshot"
     monkeypatch.setenv("PCCL_TUNING_FILE", str(path))
     monkeypatch.delenv("PCCL_ALGO", raising=False)
     selector.clear_tuning_cache()
