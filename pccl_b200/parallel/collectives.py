@@ -234,16 +234,35 @@ def _ll_eligible(tensor: torch.Tensor, op: str, algorithm: Optional[str]) -> boo
             and tensor.dtype in (torch.float32, torch.float16, torch.bfloat16))
 
 
+_shard_route_cache: Dict[Tuple[str, int], Optional[str]] = {}
+
+
+def _routed_shard_kernel(kind: str, full_bytes: int) -> Optional[str]:
+    """"ll" / "push" when the measured table names that kernel for this collective and size, else None."""
+    key = (kind, full_bytes)
+    if key not in _shard_route_cache:
+        route = None if os.environ.get("PCCL_ALGO") else tuned_route(kind, _state["world"], full_bytes)
+        _shard_route_cache[key] = route["algorithm"] if route and route["algorithm"] in ("ll", "push") else None
+    return _shard_route_cache[key]
+
+
 def _ll_part_ok(part: torch.Tensor, full: torch.Tensor, algorithm: Optional[str], executor: Optional[str] = None,
-                op: str = "sum") -> bool:
+                op: str = "sum", kind: Optional[str] = None) -> bool:
     """Reduce-scatter / all-gather / all-to-all through the packet kernel: `part` is what one rank sends
-    to (or receives from) one peer.  Sizes, dtype and arguments only.  Unforced, the packet kernel
-    takes parts of up to half its buffer; ``algorithm="ll"`` takes what fits."""
+    to (or receives from) one peer.  Sizes, dtype and arguments only.  Unforced, the measured table
+    decides where it names a kernel for this size; without one the packet kernel takes parts of up to
+    half its buffer.  ``algorithm="ll"`` takes what fits."""
     ll = _state.get("ll")
     if ll is None or op != "sum" or algorithm not in (None, "ll") or executor is not None:
         return False
     nbytes = part.numel() * part.element_size()
     limit = LL_MAX_BYTES if algorithm == "ll" else LL_MAX_BYTES // 2
+    if algorithm is None and kind is not None:
+        routed = _routed_shard_kernel(kind, full.numel() * full.element_size())
+        if routed == "push":
+            return False
+        if routed == "ll":
+            limit = LL_MAX_BYTES
     return (part.is_cuda and full.is_cuda and part.dtype == full.dtype and nbytes % 8 == 0 and 0 < nbytes <= limit
             and part.dtype in (torch.float32, torch.float16, torch.bfloat16))
 
@@ -480,7 +499,7 @@ def reduce_scatter(output: torch.Tensor, input: torch.Tensor, op: str = "sum",
 
     Sums of up to ``PUSH_MAX_BYTES`` run in the fused push kernel unless an algorithm is forced."""
     if output.numel() * _state["world"] == input.numel():
-        if _ll_part_ok(output, input, algorithm, op=op):
+        if _ll_part_ok(output, input, algorithm, op=op, kind="reduce_scatter"):
             _ll_collective(1, input, output)
             return output
         if _push_ok(input, output, algorithm, op=op):
@@ -498,7 +517,7 @@ def all_gather(output: torch.Tensor, input: torch.Tensor, algorithm: Optional[st
                async_op: bool = False) -> torch.Tensor:
     """``executor="ce"`` moves the shards with the copy engines (``algorithm`` twoshot)."""
     if input.numel() * _state["world"] == output.numel():
-        if _ll_part_ok(input, output, algorithm, executor):
+        if _ll_part_ok(input, output, algorithm, executor, kind="allgather"):
             _ll_collective(2, input, output)
             return output
         if _push_ok(output, input, algorithm, executor):
