@@ -165,8 +165,12 @@ def test_channelize_only_when_it_pays():
     assert max(n.channel for n in g32.nodes.values()) == 31
 
 
-def test_selector_reference_rule_and_switched_fabric(monkeypatch):
+def test_selector_reference_rule_and_switched_fabric(monkeypatch, tmp_path):
+    """The built-in rules (what applies when no measured table covers the world size)."""
+    from pccl_b200.dsl.algorithms import selector
     monkeypatch.delenv("PCCL_ALGO", raising=False)
+    monkeypatch.setenv("PCCL_TUNING_FILE", str(tmp_path / "no_table.json"))
+    selector.clear_tuning_cache()
     assert isinstance(select_algorithm(2, 1 << 10), RingAllreduce)
     assert isinstance(select_algorithm(6, 1 << 10), RingAllreduce)
     assert isinstance(select_algorithm(8, 1 << 20), RingAllreduce)
@@ -179,6 +183,7 @@ def test_selector_reference_rule_and_switched_fabric(monkeypatch):
     assert isinstance(select_algorithm(8, 512 << 20, topology=no_nvls), TwoShotAllreduce)
     monkeypatch.setenv("PCCL_ALGO", "tree")
     assert select_algorithm(8, 1 << 30).name == "tree"
+    selector.clear_tuning_cache()
 
 
 def test_cost_based_selector_prefers_few_steps_for_small_and_bandwidth_for_large(monkeypatch):
