@@ -133,7 +133,10 @@ class GradientBuckets:
                 at += self.params[i].numel()
             self.offsets.append(row)
         self.bucket_of = {i: b for b, idxs in enumerate(self.buckets) for i in idxs}
-        self.stream = torch.cuda.Stream()
+        # High priority: when SMs free up under a running backward GEMM, the collective's CTAs are placed
+        # before the GEMM's remaining ones, so a bucket's reduction starts inside the kernel that follows
+        # its last gradient instead of after it.
+        self.stream = torch.cuda.Stream(priority=-1)
         self._native = None
         self._hooks: list = []
         self._pending = [0] * len(self.buckets)
@@ -165,6 +168,13 @@ class GradientBuckets:
         grads = self._grads(b)
         used = sum(g.numel() for g in grads)
         self.stream.wait_stream(torch.cuda.current_stream())
+        if len(grads) == 1 and used == self.sizes[b]:
+            # A bucket that is one gradient needs no packing: it is reduced where it lies.
+            with torch.cuda.stream(self.stream):
+                _c.all_reduce(grads[0].view(-1), op="avg", async_op=True)
+            grads[0].record_stream(self.stream)
+            self._launched[b] = True
+            return
         with torch.cuda.stream(self.stream):
             if used < self.sizes[b]:
                 flat[used:].zero_()
