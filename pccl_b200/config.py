@@ -63,6 +63,8 @@ OPTIONS: Dict[str, tuple] = {
                          "launch kernels whose CTAs wait on one another cooperatively (all CTAs resident)"),
     "PCCL_PUSH_MAX_BYTES": ("push_max_bytes", _size, 32 << 20,
                             "largest message taken by the fused push collectives (0 = never)"),
+    "PCCL_PUSH_LEAN_CTAS": ("push_lean_ctas", int, 12,
+                            "grid of the push kernel's second instance, used for collectives that overlap compute"),
     "PCCL_GEMM_SMS_PER_TILE": ("gemm_sms_per_tile", int, 2,
                                "2 = pairs of SMs on 256x256 tiles (tcgen05.mma.cta_group::2), 1 = one SM per 128x256 tile"),
     "PCCL_GEMM_TILE_N": ("gemm_tile_n", int, 0, "tile width of the paired GEMM (multiple of 32; 0 = 256)"),
@@ -103,6 +105,7 @@ class PcclConfig:
     trace: bool = False
     cooperative: bool = True
     push_max_bytes: int = 32 << 20
+    push_lean_ctas: int = 12
     gemm_sms_per_tile: int = 2
     gemm_tile_n: int = 0
     gemm_split_tail: bool = True

@@ -124,6 +124,31 @@ def _setup_push(group) -> None:
                       "counters": torch.zeros(2, dtype=torch.int32, device="cuda")}
 
 
+def ensure_lean_push(ctas: Optional[int] = None) -> bool:
+    """A second instance of the push kernel's buffers, run with few CTAs (``PCCL_PUSH_LEAN_CTAS``, default
+    12): for collectives that should hide under compute kernels (``all_reduce(..., overlap=True)``), where
+    a grid of 96 CTAs would take two thirds of the SMs from the GEMM it runs beside.  Posted NVLink stores
+    keep the link busy from a few hundred warps, so the lean grid loses little bandwidth.  Collective (it
+    allocates symmetric memory): every rank calls it at the same point.  True when the instance exists."""
+    if _state.get("push_lean") is not None:
+        return True
+    main = _state.get("push")
+    if main is None:
+        return False
+    eng = _engine.get_engine()
+    world = _state["world"]
+    slot = ((PUSH_MAX_BYTES // 16 + world - 1) // world) * 16
+    areas = eng.empty_symmetric((4 * world * slot,), torch.uint8)
+    flags = eng.empty_symmetric((2 * world,), torch.int32)
+    flags.zero_()
+    torch.cuda.synchronize()
+    dist.barrier(group=_state["group"])
+    _state["push_lean"] = {"areas": areas, "flags": flags, "epoch": 0, "native": main["native"],
+                           "counters": torch.zeros(2, dtype=torch.int32, device="cuda"),
+                           "ctas": int(ctas or os.environ.get("PCCL_PUSH_LEAN_CTAS", "12"))}
+    return True
+
+
 _NVLS_DTYPE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 
 
@@ -197,15 +222,15 @@ def _aligned(tensor: torch.Tensor, align: int = 16) -> torch.Tensor:
     return tensor.contiguous().clone() if tensor.is_contiguous() else tensor.contiguous()
 
 
-def _push(mode: int, input: torch.Tensor, output: torch.Tensor) -> None:
-    push = _state["push"]
+def _push(mode: int, input: torch.Tensor, output: torch.Tensor, lean: bool = False) -> None:
+    push = _state["push_lean"] if lean else _state["push"]
     push["epoch"] += 1
     src, dst = _aligned(input), _aligned(output)
     if mode == 0 and input.data_ptr() == output.data_ptr() and src is not input:
         dst = src                                  # in place on the staged copy
     push["native"].collective_push(mode, src, dst, push["areas"].heap_offset, PUSH_MAX_BYTES,
-                                   push["flags"].heap_offset, push["counters"], push["epoch"], _PUSH_CTAS,
-                                   _state["err_push"])
+                                   push["flags"].heap_offset, push["counters"], push["epoch"],
+                                   push.get("ctas", _PUSH_CTAS), _state["err_push"])
     if dst is not output:
         output.copy_(dst)
 
@@ -426,8 +451,12 @@ def _plan_from_cache(name: str, rank: int, world: int, compile_for) -> str:
 
 
 def all_reduce(tensor: torch.Tensor, op: str = "sum", algorithm: Optional[str] = None,
-               channels: Optional[int] = None, async_op: bool = False) -> torch.Tensor:
+               channels: Optional[int] = None, async_op: bool = False, overlap: bool = False) -> torch.Tensor:
     """In-place all-reduce of ``tensor`` (sum / max / min / avg).
+
+    ``overlap=True`` says the call runs beside compute kernels (gradient buckets under backward): sums
+    that fit the push kernel then run on its lean instance (see ``ensure_lean_push``), whatever the
+    table says is fastest on an idle GPU.
 
     Unless an algorithm is forced, sums of up to ``LL_MAX_BYTES`` go through the packet-protocol kernel
     and sums of up to ``PUSH_MAX_BYTES`` through the fused push kernel (both: no plan, no staging copy,
@@ -437,10 +466,13 @@ def all_reduce(tensor: torch.Tensor, op: str = "sum", algorithm: Optional[str] =
             and (_state.get("ll") or _state.get("push") or _state.get("nvls")):
         # The fused kernels sum; the average is the sum times 1 / world (one element-wise pass, as the
         # plans' own avg does).  Which kernel runs is decided exactly as for a sum.
-        all_reduce(tensor, "sum", algorithm, channels, async_op=True)
+        all_reduce(tensor, "sum", algorithm, channels, async_op=True, overlap=overlap)
         tensor.mul_(1.0 / _state["world"])
         if not async_op:
             synchronize()
+        return tensor
+    if overlap and algorithm is None and _state.get("push_lean") is not None and _push_eligible(tensor, op, None):
+        _push(0, tensor, tensor, lean=True)
         return tensor
     if algorithm is None and op == "sum":
         # A measured table, when one covers this world size, says which path wins at this size
@@ -595,6 +627,11 @@ def reset() -> None:
         push["flags"].zero_()
         push["counters"].zero_()
         push["epoch"] = 0
+    lean = _state.get("push_lean")
+    if lean is not None:
+        lean["flags"].zero_()
+        lean["counters"].zero_()
+        lean["epoch"] = 0
     nvls = _state.get("nvls")
     if nvls is not None:
         nvls["flags"].zero_()
