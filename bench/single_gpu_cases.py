@@ -91,7 +91,32 @@ def case_ar_rmsnorm(iters):
     return dict(tokens=tokens, hidden=hidden, us=us, gbs=round(4 * tokens * hidden * 2 / us / 1e3, 1))
 
 
+def case_bucket_pack(iters):
+    """64 gradients of mixed sizes (256 MB in all) gathered into one bucket and scattered back."""
+    import pccl_b200 as pccl
+    fused = pccl.engine.load_native().fused
+    sizes = [(4 << 20) + 1024 * (i % 5) for i in range(48)] + [65536 + 8 * i for i in range(16)]     # bf16 elements
+    grads = [torch.randn(n, device="cuda").to(torch.bfloat16) for n in sizes]
+    offsets, at = [], 0
+    for n in sizes:
+        offsets.append(at * 2)
+        at += n
+    bucket = torch.zeros(at, device="cuda", dtype=torch.bfloat16)
+    fused.bucket_pack(grads, offsets, bucket, False)
+    torch.cuda.synchronize()
+    if not torch.equal(bucket, torch.cat(grads)):
+        raise SystemExit("pack mismatch")
+    back = [torch.zeros_like(g) for g in grads]
+    fused.bucket_pack(back, offsets, bucket, True)
+    torch.cuda.synchronize()
+    if not all(torch.equal(a, b) for a, b in zip(back, grads)):
+        raise SystemExit("unpack mismatch")
+    us = _time(lambda: fused.bucket_pack(grads, offsets, bucket, False), iters)
+    return dict(tensors=len(sizes), bytes=at * 2, us=us, gbs=round(2 * at * 2 / us / 1e3, 1))
+
+
 CASES = {
+    "bucket_pack": case_bucket_pack,
     "gemm_rs": case_gemm_rs,
     "ag_gemm": case_ag_gemm,
     "ag_gemm_swiglu": lambda iters: case_ag_gemm(iters, swiglu=True),
