@@ -65,6 +65,8 @@ OPTIONS: Dict[str, tuple] = {
                             "largest message taken by the fused push collectives (0 = never)"),
     "PCCL_PUSH_LEAN_CTAS": ("push_lean_ctas", int, 12,
                             "grid of the push kernel's second instance, used for collectives that overlap compute"),
+    "PCCL_DP_TRANSPORT": ("dp_transport", str, "push",
+                          "hooked gradient buckets: push (lean push kernel) | ce (copy-engine all-gather + local sum)"),
     "PCCL_GEMM_SMS_PER_TILE": ("gemm_sms_per_tile", int, 2,
                                "2 = pairs of SMs on 256x256 tiles (tcgen05.mma.cta_group::2), 1 = one SM per 128x256 tile"),
     "PCCL_GEMM_TILE_N": ("gemm_tile_n", int, 0, "tile width of the paired GEMM (multiple of 32; 0 = 256)"),
@@ -106,6 +108,7 @@ class PcclConfig:
     cooperative: bool = True
     push_max_bytes: int = 32 << 20
     push_lean_ctas: int = 12
+    dp_transport: str = "push"
     gemm_sms_per_tile: int = 2
     gemm_tile_n: int = 0
     gemm_split_tail: bool = True
