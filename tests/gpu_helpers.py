@@ -21,9 +21,19 @@ def run_on_cluster(cluster, name, plans, xs, out_numel):
     texts = [p if isinstance(p, str) else json.dumps(p) for p in plans]
     cluster.regOp(name, texts)
     dev_in = [x.cuda() for x in xs]
-    dev_out = [torch.full((out_numel,), float("nan"), device="cuda", dtype=xs[0].dtype) for _ in xs]
+    # Outputs sit between guard elements that must come back untouched: a kernel that writes one vector
+    # too far (odd sizes, clamped tails) is caught here instead of corrupting a neighbour silently.
+    guard = 64
+    padded = [torch.full((out_numel + 2 * guard,), float("nan"), device="cuda", dtype=xs[0].dtype) for _ in xs]
+    for buf in padded:
+        buf[:guard] = 12345.0
+        buf[guard + out_numel:] = 12345.0
+    dev_out = [buf[guard:guard + out_numel] for buf in padded]
     cluster.exeOp(name, dev_in, dev_out)
     torch.cuda.synchronize()
+    for r, buf in enumerate(padded):
+        assert bool((buf[:guard] == 12345.0).all()) and bool((buf[guard + out_numel:] == 12345.0).all()), \
+            f"{name}: rank {r} wrote outside its output"
     return [o.cpu() for o in dev_out]
 
 
