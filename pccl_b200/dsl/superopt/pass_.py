@@ -75,7 +75,7 @@ class SuperoptPass:
     def _apply_fabric_rules(self, graph: PrimitiveIRGraph) -> bool:
         """Structural retargeting to a switched fabric (multi-source reduces, in-switch reduction
         and broadcast), each rewrite kept only if it lowers the plan's price."""
-        from .fabric_rules import apply_fabric_rules
+        from pccl_b200.dsl.superopt.fabric_rules import apply_fabric_rules
         self.fabric_rewrites = apply_fabric_rules(graph, self.profile, self.topology)
         return bool(self.fabric_rewrites)
 
