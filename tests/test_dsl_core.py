@@ -264,3 +264,27 @@ def test_packaged_tuning_matches_the_saved_sweeps():
             checked += 1
     assert checked > 100
     selector.clear_tuning_cache()
+
+
+def test_tuning_can_be_rebuilt_offline_from_saved_sweeps(tmp_path):
+    """`collective_sweep.py --tuning-from` needs no GPU: it reproduces the packaged table from bench/results."""
+    import glob
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    files = sorted(glob.glob(os.path.join(root, "bench", "results", "sweep_*gpu_allreduce.json")) +
+                   glob.glob(os.path.join(root, "bench", "results", "sweep_*gpu_shards.json")))
+    out = tmp_path / "tuning.json"
+    subprocess.run([sys.executable, os.path.join(root, "bench", "collective_sweep.py"), "--tuning-from", *files,
+                    "--write-tuning", str(out)], check=True, timeout=120)
+    rebuilt = json.loads(out.read_text())["routes"]
+    packaged = json.load(open(os.path.join(root, "pccl_b200", "dsl", "algorithms", "tuning_b200.json")))["routes"]
+    assert rebuilt == packaged
+    known = {"ll", "push", "nvls_kernel", "ring", "rhd", "tree", "oneshot", "twoshot", "nvls", "nvls_twopass", "hybrid"}
+    for kind in ("allreduce", "allgather", "reduce_scatter"):
+        assert {"2", "4", "8"} <= set(packaged[kind]), kind
+        for table in packaged[kind].values():
+            assert table[-1]["max_bytes"] is None
+            assert all(e["algorithm"] in known and e.get("plan_algorithm", "ring") in known for e in table)
