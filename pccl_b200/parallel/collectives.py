@@ -138,8 +138,13 @@ def ensure_lean_push(ctas: Optional[int] = None) -> bool:
     eng = _engine.get_engine()
     world = _state["world"]
     slot = ((PUSH_MAX_BYTES // 16 + world - 1) // world) * 16
-    areas = eng.empty_symmetric((4 * world * slot,), torch.uint8)
-    flags = eng.empty_symmetric((2 * world,), torch.int32)
+    try:
+        areas = eng.empty_symmetric((4 * world * slot,), torch.uint8)
+        flags = eng.empty_symmetric((2 * world,), torch.int32)
+    except RuntimeError:
+        # The symmetric arena is full (the same on every rank: they allocate alike): overlapped calls
+        # then share the main instance.
+        return False
     flags.zero_()
     torch.cuda.synchronize()
     dist.barrier(group=_state["group"])
