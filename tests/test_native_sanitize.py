@@ -83,3 +83,24 @@ def test_plan_pipeline_under_sanitizers(tmp_path):
     assert "ERROR: AddressSanitizer" not in done.stderr and "runtime error" not in done.stderr, done.stderr[-4000:]
     summary = dict(kv.split("=") for kv in done.stdout.strip().split()[1:])
     assert int(summary["good"]) == cases and int(summary["failures"]) == 0 and int(summary["refused"]) >= 4, done.stdout
+
+
+@pytest.mark.skipif(shutil.which("g++") is None or not os.path.isdir(CUDA_INCLUDE), reason="needs g++ and the NVTX headers")
+def test_fd_server_under_thread_sanitizer(tmp_path):
+    """The descriptor-passing server (one thread per rank, SCM_RIGHTS over abstract unix sockets) with
+    concurrent publishers and fetchers, under ThreadSanitizer."""
+    exe = tmp_path / "fd_server_tsan"
+    cmd = ["g++", "-std=c++17", "-O1", "-g", "-fno-omit-frame-pointer", "-fsanitize=thread", "-I", CSRC, "-I", CUDA_INCLUDE,
+           os.path.join(ROOT, "tests", "native", "fd_server_tsan_main.cc"), os.path.join(CSRC, "common", "fd_socket.cc"),
+           os.path.join(CSRC, "common", "util.cc"), "-ldl", "-lpthread", "-o", str(exe)]
+    done = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    if done.returncode != 0 and ("tsan" in done.stderr.lower() or "sanitize" in done.stderr.lower()):
+        pytest.skip("this toolchain has no ThreadSanitizer runtime")
+    assert done.returncode == 0, done.stderr[-3000:]
+    env = dict(os.environ, TSAN_OPTIONS="halt_on_error=0:second_deadlock_stack=1")
+    run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300, env=env)
+    if "FATAL: ThreadSanitizer" in run.stderr and "unexpected memory mapping" in run.stderr:
+        pytest.skip("ThreadSanitizer cannot map its shadow memory in this container")
+    assert run.returncode == 0, run.stdout[-1500:] + run.stderr[-4000:]
+    assert "WARNING: ThreadSanitizer" not in run.stderr, run.stderr[-4000:]
+    assert "FD_SERVER_TSAN failures=0" in run.stdout
