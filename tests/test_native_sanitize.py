@@ -104,3 +104,26 @@ def test_fd_server_under_thread_sanitizer(tmp_path):
     assert run.returncode == 0, run.stdout[-1500:] + run.stderr[-4000:]
     assert "WARNING: ThreadSanitizer" not in run.stderr, run.stderr[-4000:]
     assert "FD_SERVER_TSAN failures=0" in run.stdout
+
+
+@pytest.mark.skipif(shutil.which("g++") is None or not os.path.isdir(CUDA_INCLUDE), reason="needs g++ and the NVTX headers")
+def test_rdma_proxy_under_thread_sanitizer(tmp_path):
+    """The RDMA proxy's command queue and worker thread over the loopback fabric: concurrent submitters,
+    injected errors, dropped requests, shutdown with work queued, under ThreadSanitizer."""
+    exe = tmp_path / "rdma_proxy_tsan"
+    rdma = os.path.join(CSRC, "executors", "rdma")
+    cmd = ["g++", "-std=c++17", "-O1", "-g", "-fno-omit-frame-pointer", "-fsanitize=thread", "-I", CSRC, "-I", CUDA_INCLUDE,
+           os.path.join(ROOT, "tests", "native", "rdma_proxy_tsan_main.cc"), os.path.join(rdma, "rdma_proxy.cc"),
+           os.path.join(rdma, "verbs_transport.cc"), os.path.join(CSRC, "common", "json.cc"),
+           os.path.join(CSRC, "common", "util.cc"), "-ldl", "-lpthread", "-o", str(exe)]
+    done = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    if done.returncode != 0 and ("tsan" in done.stderr.lower() or "sanitize" in done.stderr.lower()):
+        pytest.skip("this toolchain has no ThreadSanitizer runtime")
+    assert done.returncode == 0, done.stderr[-3000:]
+    run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300,
+                         env=dict(os.environ, TSAN_OPTIONS="halt_on_error=0"))
+    if "FATAL: ThreadSanitizer" in run.stderr and "unexpected memory mapping" in run.stderr:
+        pytest.skip("ThreadSanitizer cannot map its shadow memory in this container")
+    assert run.returncode == 0, run.stdout[-1500:] + run.stderr[-4000:]
+    assert "WARNING: ThreadSanitizer" not in run.stderr, run.stderr[-4000:]
+    assert "RDMA_PROXY_TSAN failures=0" in run.stdout
