@@ -108,13 +108,13 @@ class GpuProfile:
 
 H100_PROFILE = GpuProfile(name="h100")
 
-# B200, calibrated on 512 MB fp32 all-reduces (GB/s per NVLink direction actually sustained):
-# two-shot moves 2 (W-1)/W of the message per direction in 0.859 ms on 2 GPUs and 1.527 ms on 8,
-# i.e. 615-625 GB/s through SM peer loads ("tma" plans execute on the same SM path: TMA never
-# touches peer memory); the one-pass in-switch all-reduce moves (W+1)/W of it in 1.355 ms on
-# 2 GPUs, i.e. 594 GB/s through multimem.  `plan_cost` multiplies a multimem step's slice by the
-# number of slices that cross this GPU's links while every rank runs that step.
-_B200_BW = {"sm": 620.0, "tma": 620.0, "ce": 740.0, "rdma": 50.0, "multimem": 590.0, "host": 25.0}
+# B200, calibrated on device timelines of 512 MB fp32 all-reduces (GB/s per NVLink direction actually
+# sustained).  SM peer loads: the two-shot plan's pull-reduce and gather phases move 646-655 GB/s on
+# 4 GPUs and 626 GB/s on 2 ("tma" plans execute on the same SM path: TMA never touches peer memory).
+# In-switch: the one-pass multimem all-reduce moves (W+1)/W of the message per direction at 571-575 GB/s
+# on 2, 4 and 8 GPUs alike.  Copy engines: 745 GB/s (cudaMemcpyPeer).  `plan_cost` multiplies a multimem
+# step's slice by the number of slices that cross this GPU's links while every rank runs that step.
+_B200_BW = {"sm": 640.0, "tma": 640.0, "ce": 745.0, "rdma": 50.0, "multimem": 572.0, "host": 25.0}
 B200_PROFILE = GpuProfile(
     name="b200",
     launch_overhead_us=0.6,
