@@ -463,9 +463,13 @@ def all_reduce(tensor: torch.Tensor, op: str = "sum", algorithm: Optional[str] =
     that fit the push kernel then run on its lean instance (see ``ensure_lean_push``), whatever the
     table says is fastest on an idle GPU.
 
-    Unless an algorithm is forced, sums of up to ``LL_MAX_BYTES`` go through the packet-protocol kernel
-    and sums of up to ``PUSH_MAX_BYTES`` through the fused push kernel (both: no plan, no staging copy,
-    asynchronous on the current stream); everything else runs as a plan.
+    Unless an algorithm is forced, the measured table for this world size picks the path: the
+    packet-protocol kernel (small sums), the fused push kernel (up to ``PUSH_MAX_BYTES``), the in-switch
+    kernel (tensors in symmetric memory, and anything above the push kernel's range when NVLS is up) or
+    a plan.  Without a table: packet kernel up to ``LL_MAX_BYTES``, push kernel up to ``PUSH_MAX_BYTES``,
+    then plans.  The kernels are asynchronous on the current stream and need no staging copy (the
+    in-switch kernel stages ordinary tensors through the working buffer).  An average is the same sum
+    followed by a scale.
     """
     if op == "avg" and algorithm in (None, "ll", "push", "nvls_kernel") and tensor.dtype in _NVLS_DTYPE \
             and (_state.get("ll") or _state.get("push") or _state.get("nvls")):
